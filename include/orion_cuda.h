@@ -1,0 +1,261 @@
+/*
+ * orion_cuda.h — C ABI of the B200 (sm_100a) implementation of OrionServe-RS's
+ * per-step transformer forward pass.
+ *
+ * The reference has no FFI for this path: its boundary is two Rust traits,
+ * `Backend` (crates/orion-core/src/traits.rs:159-183) and `LanguageModel`
+ * (crates/orion-core/src/traits.rs:297-309), plus the constructor convention of
+ * `TransformerModel::{new, from_directory}` (crates/orion-models/src/
+ * transformer.rs:148-205). Each entry point below names the trait method or
+ * function it stands in for; a Rust `orion-cuda` crate binds them one to one.
+ *
+ * Conventions: plain pointers and sizes, opaque handles, no exceptions across
+ * the boundary. Every function that can fail returns an OrionStatus; the text
+ * of the last failure on the calling thread is read with
+ * orion_cuda_last_error(). Host pointers unless a parameter is documented as a
+ * device pointer. One forward at a time per model handle (the reference's
+ * engine loop is a single thread, crates/orion-runtime/src/engine.rs:502-548).
+ * There is no CPU fallback: without a usable device every constructor fails.
+ */
+#ifndef ORION_CUDA_H
+#define ORION_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Error classes, mirroring the reference's error enums. */
+typedef enum OrionStatus {
+  ORION_OK = 0,
+  ORION_ERR_INTERNAL = 1,        /* EngineError::Internal (crates/orion-core/src/error.rs:78-135) */
+  ORION_ERR_BACKEND = 2,         /* EngineError::Backend{backend:"cuda",stage,reason} (error.rs:119-124) */
+  ORION_ERR_INVALID_REQUEST = 3, /* EngineError::InvalidRequest (orion-distributed/src/lib.rs:76-88) */
+  ORION_ERR_UNAVAILABLE = 4,     /* CudaUnavailable::{NoDriver,NoDevices,NoSuchDevice} (orion-cuda/src/lib.rs:40-49) */
+  ORION_ERR_MODEL = 5            /* ModelError::{Malformed,MissingTensor,UnsupportedDtype} (transformer.rs:62-120) */
+} OrionStatus;
+
+/* DType (crates/orion-core/src/traits.rs:21-29). */
+typedef enum OrionDType {
+  ORION_DTYPE_F32 = 0,
+  ORION_DTYPE_F16 = 1,
+  ORION_DTYPE_BF16 = 2,
+  ORION_DTYPE_I8 = 3,
+  ORION_DTYPE_I4 = 4
+} OrionDType;
+
+typedef struct OrionBackend OrionBackend;
+typedef struct OrionModel OrionModel;
+
+/* Text of the last error raised on the calling thread ("" when none). */
+const char *orion_cuda_last_error(void);
+
+/* ---- orion_cuda::{is_available, device_count}  (orion-cuda/src/lib.rs:78-95) ---- */
+int orion_cuda_is_available(void);
+int orion_cuda_device_count(void);
+
+/* ---- CudaBackend: Backend  (orion-cuda/src/lib.rs:104-179, traits.rs:159-183) ---- */
+
+/* CudaBackend::new(ordinal) (orion-cuda/src/lib.rs:116-132). */
+int orion_cuda_backend_create(int ordinal, OrionBackend **out);
+void orion_cuda_backend_destroy(OrionBackend *backend);
+/* Backend::name -> "cuda" (traits.rs:161). */
+const char *orion_cuda_backend_name(const OrionBackend *backend);
+/* Backend::device -> Device::Cuda(ordinal) (traits.rs:164). */
+int orion_cuda_backend_ordinal(const OrionBackend *backend);
+/* CudaBackend::device_name (orion-cuda/src/lib.rs:138-140). */
+const char *orion_cuda_backend_device_name(const OrionBackend *backend);
+/* Backend::total_memory / available_memory (traits.rs:167-173). */
+int orion_cuda_backend_total_memory(const OrionBackend *backend, uint64_t *bytes);
+int orion_cuda_backend_available_memory(const OrionBackend *backend, uint64_t *bytes);
+/* Backend::synchronize (traits.rs:179). */
+int orion_cuda_backend_synchronize(const OrionBackend *backend);
+/* Backend::supports_dtype (traits.rs:182): 1 for F32 and BF16, else 0. */
+int orion_cuda_backend_supports_dtype(const OrionBackend *backend, int dtype);
+
+/* ---- CudaTransformerModel: LanguageModel ---- */
+
+#define ORION_NCCL_ID_BYTES 128
+
+/* ModelMetadata numeric fields (traits.rs:95-123) + HfConfig::ffn_dim
+ * (orion-models/src/config.rs:238) + Architecture::has_qkv_bias (config.rs:134)
+ * + the tied-head rule (transformer.rs:108-112) + the num_blocks / block_size
+ * arguments of TransformerModel::new (transformer.rs:148-154) + the tensor-
+ * parallel rank (orion-distributed/src/lib.rs:74-90). */
+typedef struct OrionModelDesc {
+  uint32_t hidden_size;
+  uint32_t num_layers;
+  uint32_t num_attention_heads;
+  uint32_t num_kv_heads;
+  uint32_t head_dim;
+  uint32_t vocab_size;
+  uint32_t ffn_dim;
+  uint32_t max_position_embeddings;
+  float rope_theta;
+  float rms_norm_eps;
+  uint32_t has_qkv_bias;
+  uint32_t tied_lm_head;
+  uint32_t num_blocks;
+  uint32_t block_size;
+  /* Arithmetic of the build: ORION_DTYPE_F32 (correctness build, f32 storage
+   * and arithmetic) or ORION_DTYPE_BF16 (performance build: bf16 weights, KV
+   * arena and activations, f32 accumulation and residual stream). */
+  uint32_t compute_dtype;
+  /* Largest batch one forward may carry; device work buffers are sized from it. */
+  uint32_t max_batch_tokens;
+  uint32_t max_batch_sequences;
+  /* Tensor parallelism: rank index and world size; world 1 = single GPU. */
+  uint32_t tp_rank;
+  uint32_t tp_world;
+  /* ncclUniqueId shared by all ranks (from orion_cuda_tp_unique_id on rank 0);
+   * ignored when tp_world == 1. */
+  uint8_t nccl_unique_id[ORION_NCCL_ID_BYTES];
+} OrionModelDesc;
+
+/* TransformerModel::new (transformer.rs:148-177): allocates the zeroed KV
+ * arena for this rank's KV heads, the RoPE tables and the work buffers. */
+int orion_cuda_model_create(OrionBackend *backend, const OrionModelDesc *desc, OrionModel **out);
+void orion_cuda_model_destroy(OrionModel *model);
+
+/* ModelWeights::load, one tensor at a time (transformer.rs:62-120). `name` is
+ * the Hugging Face tensor name (transformer.rs:12-18); `dtype` the stored type
+ * (F32, F16 or BF16, widened or narrowed once at load like loader.rs:74-96);
+ * `shape` the FULL, unsharded shape. Under tensor parallelism the rank's
+ * column or row slice is taken here. */
+int orion_cuda_model_load_tensor(OrionModel *model, const char *name, int dtype,
+                                 const uint64_t *shape, int ndim, const void *data);
+/* Checks that every required tensor arrived (ModelWeights::load fails on the
+ * first missing tensor, transformer.rs:73-118) and resolves the tied head. */
+int orion_cuda_model_finalize(OrionModel *model);
+/* Seeded random initialisation on the device: every matrix N(0, std), every
+ * RMSNorm weight 1.0, biases zero; finalizes the model. Stands in for a
+ * checkpoint where none can be shipped (benchmarks at the 8B / 70B shapes). */
+int orion_cuda_model_init_random(OrionModel *model, uint64_t seed, float std);
+
+/* LanguageModel::forward (traits.rs:305; transformer.rs:359-442).
+ * The arguments are the fields of ForwardBatch (traits.rs:193-210) with the
+ * per-array lengths passed separately so that ForwardBatch::validate
+ * (traits.rs:232-261) can be applied. block_tables are flattened:
+ * table s = block_tables_flat[offsets[s] .. offsets[s+1]).
+ * On success writes num_sequences * vocab_size f32 logits, row-major
+ * (ForwardOutput, traits.rs:271-277). An empty batch succeeds and writes
+ * nothing. No KV slot is written when validation fails. */
+int orion_cuda_model_forward(OrionModel *model, const uint32_t *tokens, uint64_t num_tokens,
+                             const uint32_t *positions, uint64_t num_positions,
+                             const uint64_t *slot_token_counts, uint64_t num_slot_token_counts,
+                             const uint64_t *context_lens, uint64_t num_context_lens,
+                             const uint32_t *block_tables_flat,
+                             const uint64_t *block_table_offsets, uint64_t num_block_tables,
+                             uint64_t num_sequences, int has_prefill, float *logits_out,
+                             uint64_t logits_capacity);
+
+/* forward + greedy argmax on the device (orion-runtime/src/sampling.rs:196-206:
+ * first index of the strict maximum). Writes one token id per sequence; a row
+ * with no value above -inf yields UINT32_MAX. logits_out may be NULL. */
+int orion_cuda_model_forward_greedy(OrionModel *model, const uint32_t *tokens,
+                                    uint64_t num_tokens, const uint32_t *positions,
+                                    uint64_t num_positions, const uint64_t *slot_token_counts,
+                                    uint64_t num_slot_token_counts, const uint64_t *context_lens,
+                                    uint64_t num_context_lens, const uint32_t *block_tables_flat,
+                                    const uint64_t *block_table_offsets,
+                                    uint64_t num_block_tables, uint64_t num_sequences,
+                                    int has_prefill, uint32_t *token_ids_out, float *logits_out,
+                                    uint64_t logits_capacity);
+
+/* Replays the previous successful forward on the device without any host<->
+ * device copy (inputs and block tables stay resident). Used to time the
+ * device-resident step; results land in the model's device logits buffer. */
+int orion_cuda_model_replay(OrionModel *model, int iterations, float *elapsed_ms);
+/* Kernels launched by the most recent forward / replay iteration. */
+int orion_cuda_model_last_launch_count(const OrionModel *model, uint64_t *launches);
+/* Copies this rank's KV arena to the host in the reference's logical order
+ * [layer][block][k|v][slot][local kv head][dim] as f32 (attention.rs:9-22). */
+int orion_cuda_model_read_kv(OrionModel *model, float *out, uint64_t capacity);
+/* LanguageModel::metadata (traits.rs:299): returns the descriptor in use. */
+int orion_cuda_model_desc(const OrionModel *model, OrionModelDesc *out);
+
+/* Page-locked host memory for ForwardOutput buffers: a logits buffer allocated
+ * here is written by DMA directly, a pageable one goes through a bounce copy. */
+void *orion_cuda_host_alloc(uint64_t bytes);
+void orion_cuda_host_free(void *ptr);
+/* Tuning knob: number of CTAs the split-K planner aims for on small batches
+ * (0 restores the default of one per SM). */
+int orion_cuda_gemm_set_target_ctas(uint32_t ctas);
+
+/* ---- tensor parallelism (orion-distributed/src/lib.rs) ---- */
+
+/* Shard arithmetic of shard_dimension / ParallelLayout::compute
+ * (orion-distributed/src/lib.rs:139-152, 174-208). Each out array receives
+ * {start, len}. Refuses uneven splits and world > num_kv_heads. */
+int orion_cuda_tp_layout(uint32_t num_attention_heads, uint32_t num_kv_heads, uint32_t ffn_dim,
+                         uint32_t rank, uint32_t world, uint64_t query_heads[2],
+                         uint64_t kv_heads[2], uint64_t ffn[2]);
+/* ncclGetUniqueId for the Collective backing (docs/distributed.md:112-120). */
+int orion_cuda_tp_unique_id(uint8_t id[ORION_NCCL_ID_BYTES]);
+
+/* ---- op-level entry points (host buffers in, host buffers out) ----
+ * The functions of crates/orion-models/src/tensor.rs and attention.rs run
+ * through the same kernels the model uses. `dtype` selects the f32 or the
+ * bf16 kernels (bf16: operands are rounded to bf16 on upload, results widened
+ * to f32 on download). */
+
+/* tensor::linear (tensor.rs:96-130). */
+int orion_cuda_linear(OrionBackend *backend, int dtype, const float *x, uint64_t rows,
+                      uint64_t in_features, const float *weight, uint64_t out_features,
+                      uint64_t weight_in_features, const float *bias, uint64_t bias_len,
+                      float *out);
+/* tensor::rms_norm (tensor.rs:143-163), in place. */
+int orion_cuda_rms_norm(OrionBackend *backend, int dtype, float *x, uint64_t rows, uint64_t cols,
+                        const float *weight, uint64_t weight_len, float eps);
+/* tensor::swiglu (tensor.rs:175-189): gate = silu(gate) * up. */
+int orion_cuda_swiglu(OrionBackend *backend, int dtype, float *gate, uint64_t gate_rows,
+                      uint64_t gate_cols, const float *up, uint64_t up_rows, uint64_t up_cols);
+/* RopeTable::new + apply_rope over [rows, heads, head_dim] at positions[rows]
+ * (tensor.rs:228-298), in place. */
+int orion_cuda_rope(OrionBackend *backend, int dtype, float *x, uint64_t rows, uint64_t heads,
+                    uint64_t head_dim, const uint32_t *positions, uint64_t max_positions,
+                    float theta);
+/* attention::paged_attention for a batch of query rows (attention.rs:219-295).
+ * `kv` is an arena in the reference's order [block][k|v][slot][head][dim] for
+ * ONE layer; row r attends positions 0..=query_positions[r] through table
+ * seq_of_row[r]. */
+int orion_cuda_paged_attention(OrionBackend *backend, int dtype, const float *kv,
+                               uint64_t num_blocks, uint64_t block_size, uint64_t num_kv_heads,
+                               uint64_t head_dim, const float *query, uint64_t rows,
+                               uint64_t num_query_heads, const uint32_t *query_positions,
+                               const uint32_t *seq_of_row, const uint32_t *block_tables_flat,
+                               const uint64_t *block_table_offsets, uint64_t num_sequences,
+                               float *out);
+/* sampling::argmax per row (orion-runtime/src/sampling.rs:196-206). */
+int orion_cuda_argmax(OrionBackend *backend, const float *logits, uint64_t rows, uint64_t cols,
+                      uint32_t *out);
+
+/* ---- paged decode attention microbenchmark (device-resident) ----
+ * Builds a one-layer bf16 arena of `num_blocks` blocks filled with N(0,1)
+ * values from a counter-based generator, `batch` sequences whose block tables
+ * are consecutive slices of `block_ids` and whose context lengths are
+ * `context_lens`, runs `warmup` + `iterations` launches of the decode kernel
+ * and reports the mean launch time. When out/q_host/sample rows are given the
+ * result and the inputs of the sampled sequences are copied back for parity
+ * checks (the K/V rows of sequence s come back in logical order). */
+typedef struct OrionAttnBench OrionAttnBench;
+int orion_cuda_attn_bench_create(OrionBackend *backend, uint32_t num_query_heads,
+                                 uint32_t num_kv_heads, uint32_t head_dim, uint32_t block_size,
+                                 uint64_t num_blocks, const uint32_t *block_ids,
+                                 const uint64_t *context_lens, uint32_t batch, uint64_t seed,
+                                 OrionAttnBench **out);
+int orion_cuda_attn_bench_run(OrionAttnBench *bench, int warmup, int iterations,
+                              float *mean_ms, uint64_t *algorithmic_bytes);
+/* out: [batch][num_query_heads*head_dim] f32. */
+int orion_cuda_attn_bench_output(OrionAttnBench *bench, float *out);
+/* q: [num_query_heads*head_dim]; k, v: [context_len][num_kv_heads][head_dim] f32. */
+int orion_cuda_attn_bench_sequence(OrionAttnBench *bench, uint32_t seq, float *q, float *k,
+                                   float *v);
+void orion_cuda_attn_bench_destroy(OrionAttnBench *bench);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ORION_CUDA_H */

@@ -1,0 +1,28 @@
+"""Host-side mirror of the reference interface for the forward path, over the C ABI.
+
+Names, argument meaning and error behaviour follow the reference:
+``Backend`` / ``LanguageModel`` / ``ForwardBatch`` / ``ForwardOutput`` / ``ModelMetadata``
+(crates/orion-core/src/traits.rs), ``CudaBackend`` / ``Tolerance`` / ``validate``
+(crates/orion-cuda/src/lib.rs), ``TransformerModel::{new, from_directory}``
+(crates/orion-models/src/transformer.rs:148-205), ``Rank`` / ``ParallelLayout`` / ``Collective``
+(crates/orion-distributed/src/lib.rs). All arithmetic runs in ``liborion_cuda.so``.
+"""
+from .errors import (BackendError, CudaUnavailable, EngineError, InternalError, InvalidRequest,
+                     ModelError)
+from .types import DType, Device, ForwardBatch, ForwardOutput, ModelMetadata
+from .backend import CudaBackend, device_count, is_available
+from .model import CudaTransformerModel, HfConfig, read_safetensors, write_safetensors
+from .validate import Tolerance, ValidationReport, validate
+from .distributed import (Collective, CommunicationEstimate, NcclCollectiveId, ParallelLayout, Rank,
+                          Shard, ShardStrategy, SingleRank, shard_dimension)
+from . import ops
+from .attn_bench import PagedAttentionBench
+
+__all__ = [
+    "BackendError", "CudaUnavailable", "EngineError", "InternalError", "InvalidRequest", "ModelError",
+    "DType", "Device", "ForwardBatch", "ForwardOutput", "ModelMetadata", "CudaBackend",
+    "device_count", "is_available", "CudaTransformerModel", "HfConfig", "read_safetensors",
+    "write_safetensors", "Tolerance", "ValidationReport", "validate", "Collective",
+    "CommunicationEstimate", "NcclCollectiveId", "ParallelLayout", "Rank", "Shard", "ShardStrategy",
+    "SingleRank", "shard_dimension", "ops", "PagedAttentionBench",
+]

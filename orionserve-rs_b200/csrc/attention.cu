@@ -1,0 +1,482 @@
+// Paged GQA attention over the block-table-indexed KV arena
+// (crates/orion-models/src/attention.rs:219-295).
+//
+//  * paged_attention_generic_kernel: any head_dim / block size / storage type,
+//    any mix of prefill and decode rows; one CTA per (row, query head). This is
+//    the correctness tier (f32 build) and the fallback for shapes the tuned
+//    kernel does not cover.
+//  * paged_decode_kernel: bf16, head_dim 128, 16-token blocks, one query row
+//    per sequence. One CTA per (kv head, sequence, context split); each warp owns
+//    a private multi-stage ring of 8 KiB K/V chunks filled by bulk async copies
+//    (one copy per 16-token block of one head), computes Q.K^T and P.V with
+//    mma.sync m16n8k16 (tokens on M, the GQA group's query heads on N so the group
+//    shares every K/V tile) and keeps an online softmax in registers. Warps are
+//    merged in shared memory; context splits are merged by decode_combine_kernel.
+#include "kernels.h"
+
+namespace orion {
+namespace {
+
+// ---------------------------------------------------------------------------
+// Generic kernel
+// ---------------------------------------------------------------------------
+
+constexpr int kGenThreads = 128;
+constexpr int kGenChunk = 512;
+constexpr int kGenMaxDimsPerThread = 4;  // head_dim <= 512
+
+template <typename T>
+__global__ void __launch_bounds__(kGenThreads)
+paged_attention_generic_kernel(const T *__restrict__ q, const T *__restrict__ arena, KvLayout kv,
+                               uint32_t layer, AttnBatch batch, uint32_t q_heads,
+                               T *__restrict__ out) {
+  extern __shared__ float smem[];
+  const uint32_t hd = kv.head_dim;
+  float *q_s = smem;            // [hd]
+  float *scores = smem + hd;    // [kGenChunk]
+  __shared__ float red[kGenThreads / 32];
+  __shared__ float bcast;
+
+  const uint32_t row = blockIdx.x, head = blockIdx.y;
+  const uint32_t group = q_heads / kv.num_kv_heads;  // attention.rs:250
+  const uint32_t kvh = head / group;                 // attention.rs:258
+  const uint32_t qpos = batch.query_positions[row];
+  const uint32_t seq = batch.seq_of_row[row];
+  const uint32_t *table = batch.tables_flat + batch.table_offsets[seq];
+  const uint32_t B = kv.block_size;
+  const float scale = 1.0f / sqrtf((float)hd);  // attention.rs:251
+
+  for (uint32_t d = threadIdx.x; d < hd; d += blockDim.x)
+    q_s[d] = to_f32<T>(q[((size_t)row * q_heads + head) * hd + d]);
+  __syncthreads();
+
+  float m = -INFINITY, l = 0.0f;
+  float acc[kGenMaxDimsPerThread] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t attend = qpos + 1;  // attention.rs:253: positions 0..=query_position
+
+  for (uint32_t c0 = 0; c0 < attend; c0 += kGenChunk) {
+    const uint32_t n = min((uint32_t)kGenChunk, attend - c0);
+    float cmax = -INFINITY;
+    for (uint32_t p = threadIdx.x; p < n; p += blockDim.x) {
+      const uint32_t pos = c0 + p, slot = pos % B;
+      const T *k = arena + kv.row(layer, table[pos / B], kvh, 0, slot);
+      float dot = 0.0f;  // attention.rs:270-273: sequential, unfused
+      for (uint32_t d = 0; d < hd; ++d)
+        dot = __fadd_rn(dot, __fmul_rn(q_s[d], to_f32<T>(k[kv.col(slot, d)])));
+      const float s = __fmul_rn(dot, scale);
+      scores[p] = s;
+      cmax = fmaxf(cmax, s);
+    }
+    cmax = warp_max(cmax);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = cmax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float v = red[0];
+      for (int w = 1; w < kGenThreads / 32; ++w) v = fmaxf(v, red[w]);
+      bcast = v;
+    }
+    __syncthreads();
+    const float m_new = fmaxf(m, bcast);
+    float csum = 0.0f;
+    for (uint32_t p = threadIdx.x; p < n; p += blockDim.x) {
+      const float e = expf(scores[p] - m_new);  // tensor.rs:201
+      scores[p] = e;
+      csum += e;
+    }
+    csum = warp_sum(csum);
+    __syncthreads();  // everyone has read bcast; scores[] are final
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = csum;
+    __syncthreads();
+    float total = 0.0f;
+    for (int w = 0; w < kGenThreads / 32; ++w) total += red[w];
+    const float corr = (m == -INFINITY) ? 0.0f : expf(m - m_new);
+    l = l * corr + total;
+#pragma unroll
+    for (int j = 0; j < kGenMaxDimsPerThread; ++j) {
+      const uint32_t d = threadIdx.x + j * kGenThreads;
+      if (d >= hd) break;
+      float a = acc[j] * corr;
+      for (uint32_t p = 0; p < n; ++p) {
+        const float w = scores[p];
+        if (w == 0.0f) continue;  // attention.rs:283-285
+        const uint32_t pos = c0 + p, slot = pos % B;
+        const T *v = arena + kv.row(layer, table[pos / B], kvh, 1, slot);
+        a = __fadd_rn(a, __fmul_rn(w, to_f32<T>(v[kv.col(slot, d)])));
+      }
+      acc[j] = a;
+    }
+    m = m_new;
+    __syncthreads();
+  }
+#pragma unroll
+  for (int j = 0; j < kGenMaxDimsPerThread; ++j) {
+    const uint32_t d = threadIdx.x + j * kGenThreads;
+    if (d >= hd) break;
+    out[((size_t)row * q_heads + head) * hd + d] = from_f32<T>(l > 0.0f ? acc[j] / l : acc[j]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Tuned decode kernel
+// ---------------------------------------------------------------------------
+
+constexpr int kHd = 128;          // head_dim
+constexpr int kBlk = 16;          // tokens per KV block
+constexpr int kWarps = 4;         // warps per CTA, each with a private ring
+constexpr int kStages = 4;        // ring depth per warp
+constexpr int kChunkBytes = 2 * kBlk * kHd * 2;  // K rows + V rows of one (block, head): 8 KiB
+constexpr int kMaxGroup = 8;      // query heads per kv head (N of the MMA)
+constexpr uint32_t kDecodeSmem = kWarps * kStages * kChunkBytes + 1024;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// Device error word: bit 0 = a ring wait ran out of polls.
+__device__ uint32_t g_decode_error = 0;
+
+__global__ void __launch_bounds__(kWarps * 32, 1)
+paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, KvLayout kv,
+                    uint32_t layer, AttnBatch batch, uint32_t q_heads, uint32_t splits,
+                    DecodeScratch scratch, bf16 *__restrict__ out) {
+  extern __shared__ __align__(1024) uint8_t dsmem[];
+  uint8_t *ring = dsmem;  // [kWarps][kStages][kChunkBytes]
+  uint64_t *bars = reinterpret_cast<uint64_t *>(dsmem + kWarps * kStages * kChunkBytes);
+
+  const uint32_t kvh = blockIdx.x, row = blockIdx.y, split = blockIdx.z;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t group = q_heads / kv.num_kv_heads;
+  const uint32_t ctx = batch.query_positions[row] + 1;  // attention.rs:253
+  const uint32_t *table = batch.tables_flat + batch.table_offsets[batch.seq_of_row[row]];
+  const uint32_t nblocks = (ctx + kBlk - 1) / kBlk;
+  // Context split: a contiguous range of blocks; warps interleave inside it.
+  const uint32_t per_split = (nblocks + splits - 1) / splits;
+  const uint32_t b_begin = min(split * per_split, nblocks);
+  const uint32_t b_end = min(b_begin + per_split, nblocks);
+
+  if (threadIdx.x < kWarps * kStages) mbar_init(&bars[threadIdx.x], 1);
+  mbar_fence_init();
+  __syncthreads();
+
+  uint8_t *my_ring = ring + warp * kStages * kChunkBytes;
+  uint64_t *my_bars = bars + warp * kStages;
+  const size_t layer_base = (size_t)layer * kv.layer_elems();
+  // Block i of this warp (i = 0, 1, ...) is logical block b_begin + warp + i*kWarps.
+  const uint32_t my_count = (b_end > b_begin + warp) ? (b_end - b_begin - warp + kWarps - 1) / kWarps : 0;
+
+  // Block-table entries are prefetched 32 at a time into one register per lane
+  // (two groups in flight) so that issuing a copy never waits on a global load.
+  auto load_group = [&](uint32_t g) -> uint32_t {
+    const uint32_t idx = g * 32 + lane;
+    return idx < my_count ? table[b_begin + warp + idx * kWarps] : 0u;
+  };
+  uint32_t tgroup = 0, tbl_a = load_group(0), tbl_b = load_group(1);
+  auto entry = [&](uint32_t i) -> uint32_t {  // warp-uniform i, called by all lanes
+    return __shfl_sync(0xffffffffu, (i >> 5) == tgroup ? tbl_a : tbl_b, i & 31);
+  };
+  auto issue = [&](uint32_t i, uint32_t pb) {  // lane 0 only
+    const bf16 *src = arena + layer_base + ((size_t)pb * kv.num_kv_heads + kvh) * kv.chunk_elems();
+    uint64_t *bar = &my_bars[i % kStages];
+    mbar_arrive_expect_tx(bar, kChunkBytes);
+    bulk_copy_g2s(my_ring + (i % kStages) * kChunkBytes, src, kChunkBytes, bar);
+  };
+  for (uint32_t i = 0; i < min(my_count, (uint32_t)kStages); ++i) {
+    const uint32_t pb = entry(i);
+    if (lane == 0) issue(i, pb);
+  }
+
+  // Q^T as the B operand (k = dim, n = head): per 16-dim chunk two packed regs.
+  uint32_t qb[kHd / 16][2];
+  {
+    const uint32_t g = lane >> 2;
+    const bf16 *qrow = q + ((size_t)row * q_heads + (size_t)kvh * group + g) * kHd;
+#pragma unroll
+    for (int c = 0; c < kHd / 16; ++c) {
+      if (g < group) {
+        qb[c][0] = *reinterpret_cast<const uint32_t *>(qrow + c * 16 + (lane & 3) * 2);
+        qb[c][1] = *reinterpret_cast<const uint32_t *>(qrow + c * 16 + 8 + (lane & 3) * 2);
+      } else {
+        qb[c][0] = 0u;
+        qb[c][1] = 0u;
+      }
+    }
+  }
+
+  // Online softmax state for the two heads this lane sees in the C fragment
+  // (columns 2*(lane%4) and +1), in the log2 domain.
+  const float sl2 = 1.4426950408889634f / sqrtf((float)kHd);
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[kHd / 16][4];
+#pragma unroll
+  for (int t = 0; t < kHd / 16; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+
+  const uint32_t t_lo = lane >> 2, t_hi = t_lo + 8;  // token rows of this lane in the C fragment
+  bool ok = true;
+  for (uint32_t i = 0; i < my_count; ++i) {
+    const uint32_t stage = i % kStages;
+    if ((i >> 5) > tgroup) {  // entering the next group of 32 blocks
+      tbl_a = tbl_b;
+      ++tgroup;
+      tbl_b = load_group(tgroup + 1);
+    }
+    if (!mbar_wait(&my_bars[stage], (i / kStages) & 1)) {
+      ok = false;
+      break;
+    }
+    const uint32_t kbase = smem_u32(my_ring + stage * kChunkBytes);
+    const uint32_t vbase = kbase + kBlk * kHd * 2;
+    const uint32_t lb = b_begin + warp + i * kWarps;
+    const uint32_t valid = min((uint32_t)kBlk, ctx - lb * kBlk);  // tokens of this block in context
+
+    // S^T[t][g] = sum_d K[t][d] * Q[g][d]
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      const uint32_t mi = lane >> 3, r = lane & 7;
+      const uint32_t t = r + (mi & 1) * 8;
+#pragma unroll
+      for (int c = 0; c < kHd / 16; ++c) {
+        uint32_t a[4];
+        const uint32_t chunk = (uint32_t)c * 2 + (mi >> 1);
+        ldmatrix_x4(a, kbase + t * (kHd * 2) + ((chunk ^ (t & 7)) << 4));
+        mma_bf16_16816(s, a, qb[c][0], qb[c][1]);
+      }
+    }
+    // scale into the log2 domain and mask slots beyond the context
+    s[0] = (t_lo < valid) ? s[0] * sl2 : -INFINITY;
+    s[1] = (t_lo < valid) ? s[1] * sl2 : -INFINITY;
+    s[2] = (t_hi < valid) ? s[2] * sl2 : -INFINITY;
+    s[3] = (t_hi < valid) ? s[3] * sl2 : -INFINITY;
+    float bm0 = fmaxf(s[0], s[2]), bm1 = fmaxf(s[1], s[3]);
+#pragma unroll
+    for (int off = 4; off <= 16; off <<= 1) {
+      bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, off));
+      bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, off));
+    }
+    const float mn0 = fmaxf(m0, bm0), mn1 = fmaxf(m1, bm1);  // finite: token 0 is always valid
+    const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
+    const float p0 = fast_exp2(s[0] - mn0), p1 = fast_exp2(s[1] - mn1);
+    const float p2 = fast_exp2(s[2] - mn0), p3 = fast_exp2(s[3] - mn1);
+    l0 = l0 * c0 + p0 + p2;  // per-lane partial sums, reduced across lanes at the end
+    l1 = l1 * c1 + p1 + p3;
+    m0 = mn0;
+    m1 = mn1;
+    // P^T as the B operand (k = token, n = head)
+    const uint32_t pb0 = movmatrix_trans(pack_bf16x2(p0, p1));
+    const uint32_t pb1 = movmatrix_trans(pack_bf16x2(p2, p3));
+    // O^T[d][g] = O^T*corr + sum_t V[t][d] * P[t][g]
+    {
+      const uint32_t mi = lane >> 3, r = lane & 7;
+      const uint32_t t = r + (mi >> 1) * 8;
+#pragma unroll
+      for (int mt = 0; mt < kHd / 16; ++mt) {
+        uint32_t a[4];
+        const uint32_t chunk = (uint32_t)mt * 2 + (mi & 1);
+        ldmatrix_x4_trans(a, vbase + t * (kHd * 2) + ((chunk ^ (t & 7)) << 4));
+        o[mt][0] *= c0;
+        o[mt][1] *= c1;
+        o[mt][2] *= c0;
+        o[mt][3] *= c1;
+        mma_bf16_16816(o[mt], a, pb0, pb1);
+      }
+    }
+    __syncwarp();
+    if (i + kStages < my_count) {
+      const uint32_t pb = entry(i + kStages);
+      if (lane == 0) issue(i + kStages, pb);
+    }
+  }
+  if (!ok && lane == 0) atomicOr(&g_decode_error, 1u);
+
+  // Reduce the per-lane partial sums over the 8 lanes that share a head pair.
+#pragma unroll
+  for (int off = 4; off <= 16; off <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+  }
+  __syncthreads();  // every warp is done with its ring: reuse it for the merge
+
+  float *mo = reinterpret_cast<float *>(dsmem);            // [kWarps][kMaxGroup][kHd]
+  float *mml = mo + kWarps * kMaxGroup * kHd;              // [kWarps][kMaxGroup][2]
+  {
+    const uint32_t g0 = (lane & 3) * 2;
+#pragma unroll
+    for (int mt = 0; mt < kHd / 16; ++mt) {
+      const uint32_t d = mt * 16 + (lane >> 2);
+      float *base = mo + ((size_t)warp * kMaxGroup) * kHd;
+      base[(g0 + 0) * kHd + d] = o[mt][0];
+      base[(g0 + 1) * kHd + d] = o[mt][1];
+      base[(g0 + 0) * kHd + d + 8] = o[mt][2];
+      base[(g0 + 1) * kHd + d + 8] = o[mt][3];
+    }
+    if (lane < 4) {
+      float *ml = mml + ((size_t)warp * kMaxGroup + g0) * 2;
+      ml[0] = m0; ml[1] = l0; ml[2] = m1; ml[3] = l1;
+    }
+  }
+  __syncthreads();
+  {
+    const uint32_t d = threadIdx.x;  // kWarps*32 == kHd threads: one output dim each
+    for (uint32_t g = 0; g < group; ++g) {
+      float mall = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) mall = fmaxf(mall, mml[(w * kMaxGroup + g) * 2]);
+      float acc = 0.f, L = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float mw = mml[(w * kMaxGroup + g) * 2];
+        const float wgt = (mw == -INFINITY) ? 0.f : fast_exp2(mw - mall);
+        acc += wgt * mo[((size_t)w * kMaxGroup + g) * kHd + d];
+        L += wgt * mml[(w * kMaxGroup + g) * 2 + 1];
+      }
+      const uint32_t head = kvh * group + g;
+      if (splits == 1) {
+        out[((size_t)row * q_heads + head) * kHd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      } else {
+        const size_t pi = ((size_t)row * q_heads + head) * scratch.max_splits + split;
+        scratch.partial_out[pi * kHd + d] = acc;
+        if (d == 0) {
+          scratch.partial_ml[pi * 2] = mall;
+          scratch.partial_ml[pi * 2 + 1] = L;
+        }
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kHd)
+decode_combine_kernel(DecodeScratch scratch, uint32_t splits, uint32_t q_heads,
+                      bf16 *__restrict__ out) {
+  const uint32_t row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+  const size_t base = ((size_t)row * q_heads + head) * scratch.max_splits;
+  float mall = -INFINITY;
+  for (uint32_t s = 0; s < splits; ++s) mall = fmaxf(mall, scratch.partial_ml[(base + s) * 2]);
+  float acc = 0.f, L = 0.f;
+  for (uint32_t s = 0; s < splits; ++s) {
+    const float ms = scratch.partial_ml[(base + s) * 2];
+    const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - mall);
+    acc += w * scratch.partial_out[(base + s) * kHd + d];
+    L += w * scratch.partial_ml[(base + s) * 2 + 1];
+  }
+  out[((size_t)row * q_heads + head) * kHd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+}
+
+inline int after_launch(const char *stage) {
+  count_launch();
+  ORION_CUDA_CHECK(stage, cudaGetLastError());
+  return ORION_OK;
+}
+
+}  // namespace
+
+template <typename T>
+int launch_paged_attention_generic(const T *q, const T *arena, KvLayout kv, uint32_t layer,
+                                   AttnBatch batch, uint32_t q_heads, T *out,
+                                   cudaStream_t stream) {
+  if (batch.rows == 0) return ORION_OK;
+  if (kv.head_dim > kGenThreads * kGenMaxDimsPerThread)
+    return set_error(ORION_ERR_INTERNAL, "head_dim %u exceeds the attention kernel limit of %d",
+                     kv.head_dim, kGenThreads * kGenMaxDimsPerThread);
+  const size_t smem = (kv.head_dim + kGenChunk) * sizeof(float);
+  paged_attention_generic_kernel<T><<<dim3(batch.rows, q_heads), kGenThreads, smem, stream>>>(
+      q, arena, kv, layer, batch, q_heads, out);
+  return after_launch("paged_attention");
+}
+template int launch_paged_attention_generic<float>(const float *, const float *, KvLayout, uint32_t,
+                                                   AttnBatch, uint32_t, float *, cudaStream_t);
+template int launch_paged_attention_generic<bf16>(const bf16 *, const bf16 *, KvLayout, uint32_t,
+                                                  AttnBatch, uint32_t, bf16 *, cudaStream_t);
+
+bool decode_attention_supported(KvLayout kv, uint32_t q_heads) {
+  return kv.head_dim == kHd && kv.block_size == kBlk && kv.swizzle == 1 && kv.num_kv_heads > 0 &&
+         q_heads % kv.num_kv_heads == 0 && q_heads / kv.num_kv_heads <= kMaxGroup;
+}
+
+size_t decode_scratch_floats(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
+                             uint32_t max_splits) {
+  return (size_t)rows * q_heads * max_splits * (head_dim + 2);
+}
+
+uint32_t decode_choose_splits(uint32_t rows, uint32_t kv_heads, uint32_t max_position,
+                              uint32_t block_size, uint32_t max_splits) {
+  // Aim for about four CTAs per SM so the block scheduler can even out ragged
+  // contexts, but keep at least 16 blocks (4 per warp) in every split.
+  const uint32_t ctas = rows * kv_heads;
+  if (ctas == 0) return 1;
+  uint32_t want = (4 * 148 + ctas - 1) / ctas;
+  const uint32_t nblocks = max_position / block_size + 1;
+  const uint32_t cap = nblocks / 16 > 0 ? nblocks / 16 : 1;
+  if (want > cap) want = cap;
+  if (want > max_splits) want = max_splits;
+  return want < 1 ? 1 : want;
+}
+
+int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer,
+                                  AttnBatch batch, uint32_t q_heads, uint32_t splits,
+                                  DecodeScratch scratch, bf16 *out, cudaStream_t stream) {
+  if (batch.rows == 0) return ORION_OK;
+  if (!decode_attention_supported(kv, q_heads))
+    return set_error(ORION_ERR_INTERNAL, "decode attention kernel does not cover this shape");
+  if (splits < 1) splits = 1;
+  if (splits > 1 && (scratch.partial_out == nullptr || splits > scratch.max_splits))
+    return set_error(ORION_ERR_INTERNAL, "decode attention scratch too small for %u splits",
+                     splits);
+  static bool attr_set = false;
+  if (!attr_set) {
+    ORION_CUDA_CHECK("paged_decode attr",
+                     cudaFuncSetAttribute(paged_decode_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)kDecodeSmem));
+    attr_set = true;
+  }
+  paged_decode_kernel<<<dim3(kv.num_kv_heads, batch.rows, splits), kWarps * 32, kDecodeSmem,
+                        stream>>>(q, arena, kv, layer, batch, q_heads, splits, scratch, out);
+  ORION_TRY(after_launch("paged_decode"));
+  if (splits > 1) {
+    decode_combine_kernel<<<dim3(batch.rows, q_heads), kHd, 0, stream>>>(scratch, splits, q_heads,
+                                                                         out);
+    ORION_TRY(after_launch("decode_combine"));
+  }
+  return ORION_OK;
+}
+
+int decode_poll_error(uint32_t *code) {
+  uint32_t v = 0;
+  ORION_CUDA_CHECK("decode error word", cudaMemcpyFromSymbol(&v, g_decode_error, sizeof v));
+  if (v) {
+    uint32_t zero = 0;
+    ORION_CUDA_CHECK("decode error word", cudaMemcpyToSymbol(g_decode_error, &zero, sizeof zero));
+  }
+  *code = v;
+  return ORION_OK;
+}
+
+}  // namespace orion

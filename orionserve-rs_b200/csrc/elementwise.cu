@@ -1,0 +1,491 @@
+// Bandwidth-bound elementwise kernels of the forward pass: embedding gather +
+// RMSNorm, residual add + RMSNorm (which also sums the split-K slabs of the
+// preceding projection), RoPE + KV-slot write, SwiGLU, greedy argmax, and the
+// conversion / layout helpers used at load time and by the parity tests.
+#include "kernels.h"
+
+#include <cfloat>
+
+namespace orion {
+
+thread_local uint64_t g_launch_count = 0;
+
+namespace {
+
+constexpr int kNormThreads = 256;
+
+// Sum of squares accumulates in f64 for the f32 build (the reference does,
+// tensor.rs:155) and in f32 for bf16 storage.
+template <typename T>
+struct NormAcc { using type = float; };
+template <>
+struct NormAcc<float> { using type = double; };
+
+template <typename Acc>
+__device__ __forceinline__ Acc block_sum(Acc v, Acc *shared) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) shared[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  Acc total = Acc(0);
+  for (int i = 0; i < nwarps; ++i) total += shared[i];  // fixed order: deterministic
+  __syncthreads();
+  return total;
+}
+
+template <typename Acc>
+__device__ __forceinline__ float norm_scale(Acc sum_sq, uint32_t cols, float eps);
+template <>
+__device__ __forceinline__ float norm_scale<double>(double sum_sq, uint32_t cols, float eps) {
+  // tensor.rs:156-157: rms in f64, scale = (1/rms) as f32
+  return (float)(1.0 / sqrt(sum_sq / (double)cols + (double)eps));
+}
+template <>
+__device__ __forceinline__ float norm_scale<float>(float sum_sq, uint32_t cols, float eps) {
+  return rsqrtf(sum_sq / (float)cols + eps);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNormThreads)
+embed_rmsnorm_kernel(const T *__restrict__ embed, const uint32_t *__restrict__ tokens,
+                     const float *__restrict__ w, float eps, float *__restrict__ hidden,
+                     T *__restrict__ normed, uint32_t H) {
+  using Acc = typename NormAcc<T>::type;
+  __shared__ Acc red[32];
+  const uint32_t row = blockIdx.x;
+  const T *src = embed + (size_t)tokens[row] * H;
+  float *h = hidden + (size_t)row * H;
+  Acc ss = Acc(0);
+  for (uint32_t c = threadIdx.x; c < H; c += blockDim.x) {
+    const float v = to_f32<T>(src[c]);
+    h[c] = v;
+    ss += (Acc)v * (Acc)v;
+  }
+  const float scale = norm_scale<Acc>(block_sum<Acc>(ss, red), H, eps);
+  T *o = normed + (size_t)row * H;
+  for (uint32_t c = threadIdx.x; c < H; c += blockDim.x)
+    o[c] = from_f32<T>(__fmul_rn(__fmul_rn(h[c], scale), w[c]));  // (v*scale)*w, tensor.rs:159
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNormThreads)
+residual_rmsnorm_kernel(const float *__restrict__ partial, uint32_t splits, size_t split_stride,
+                        float *__restrict__ hidden, const float *__restrict__ w, float eps,
+                        T *__restrict__ out, const uint32_t *__restrict__ row_map, uint32_t H) {
+  using Acc = typename NormAcc<T>::type;
+  __shared__ Acc red[32];
+  extern __shared__ float row_cache[];  // H floats: the updated residual row
+  const uint32_t src_row = row_map ? row_map[blockIdx.x] : blockIdx.x;
+  float *h = hidden + (size_t)src_row * H;
+  Acc ss = Acc(0);
+  for (uint32_t c = threadIdx.x; c < H; c += blockDim.x) {
+    float v = h[c];
+    if (partial) {
+      const float *p = partial + (size_t)src_row * H + c;
+      float add = p[0];
+      for (uint32_t s = 1; s < splits; ++s) add += p[s * split_stride];
+      v = __fadd_rn(v, add);  // hidden += proj, transformer.rs:330-332
+      if (!row_map) h[c] = v;
+    }
+    row_cache[c] = v;
+    ss += (Acc)v * (Acc)v;
+  }
+  const float scale = norm_scale<Acc>(block_sum<Acc>(ss, red), H, eps);
+  T *o = out + (size_t)blockIdx.x * H;
+  for (uint32_t c = threadIdx.x; c < H; c += blockDim.x)
+    o[c] = from_f32<T>(__fmul_rn(__fmul_rn(row_cache[c], scale), w[c]));
+}
+
+template <typename T>
+__global__ void rope_kvwrite_kernel(const float *__restrict__ partial, uint32_t splits,
+                                    size_t split_stride, const float *__restrict__ bias,
+                                    const uint32_t *__restrict__ positions,
+                                    const uint32_t *__restrict__ slot_block,
+                                    const uint32_t *__restrict__ slot_slot,
+                                    const float *__restrict__ rope_cos,
+                                    const float *__restrict__ rope_sin, T *__restrict__ q_out,
+                                    T *__restrict__ arena, KvLayout kv, uint32_t layer,
+                                    uint32_t q_heads) {
+  const uint32_t row = blockIdx.x, head = blockIdx.y;
+  const uint32_t hd = kv.head_dim, half = hd / 2;
+  const uint32_t n_total = (q_heads + 2 * kv.num_kv_heads) * hd;
+  const float *p = partial + (size_t)row * n_total + (size_t)head * hd;
+  const float *b = bias ? bias + (size_t)head * hd : nullptr;
+  const uint32_t pos = positions[row];
+  const float *cs = rope_cos + (size_t)pos * half, *sn = rope_sin + (size_t)pos * half;
+  const bool is_q = head < q_heads;
+  const bool is_k = !is_q && head < q_heads + kv.num_kv_heads;
+  T *dst;
+  uint32_t slot = 0;
+  KvLayout lay = kv;
+  if (is_q) {
+    dst = q_out + ((size_t)row * q_heads + head) * hd;
+    lay.swizzle = 0;  // q rows are plain
+  } else {
+    const uint32_t kvh = is_k ? head - q_heads : head - q_heads - kv.num_kv_heads;
+    slot = slot_slot[row];
+    dst = arena + kv.row(layer, slot_block[row], kvh, is_k ? 0u : 1u, slot);
+  }
+  for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
+    float x0 = p[i], x1 = p[i + half];
+    for (uint32_t s = 1; s < splits; ++s) {
+      x0 += p[s * split_stride + i];
+      x1 += p[s * split_stride + i + half];
+    }
+    if (b) {  // acc + bias, tensor.rs:126
+      x0 = __fadd_rn(x0, b[i]);
+      x1 = __fadd_rn(x1, b[i + half]);
+    }
+    if (is_q || is_k) {  // tensor.rs:291-296, unfused like the reference
+      const float c = cs[i], s = sn[i];
+      const float r0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+      const float r1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+      x0 = r0;
+      x1 = r1;
+    }
+    dst[lay.col(slot, i)] = from_f32<T>(x0);
+    dst[lay.col(slot, i + half)] = from_f32<T>(x1);
+  }
+}
+
+template <typename T>
+__global__ void rope_rows_kernel(T *__restrict__ x, const uint32_t *__restrict__ positions,
+                                 const float *__restrict__ rope_cos,
+                                 const float *__restrict__ rope_sin, uint32_t heads, uint32_t hd) {
+  const uint32_t row = blockIdx.x, head = blockIdx.y, half = hd / 2;
+  T *v = x + ((size_t)row * heads + head) * hd;
+  const float *cs = rope_cos + (size_t)positions[row] * half;
+  const float *sn = rope_sin + (size_t)positions[row] * half;
+  for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
+    const float x0 = to_f32<T>(v[i]), x1 = to_f32<T>(v[i + half]);
+    v[i] = from_f32<T>(__fsub_rn(__fmul_rn(x0, cs[i]), __fmul_rn(x1, sn[i])));
+    v[i + half] = from_f32<T>(__fadd_rn(__fmul_rn(x0, sn[i]), __fmul_rn(x1, cs[i])));
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float silu_f(float g);
+template <>
+__device__ __forceinline__ float silu_f<float>(float g) { return g / (1.0f + expf(-g)); }
+template <>
+__device__ __forceinline__ float silu_f<bf16>(float g) { return g / (1.0f + __expf(-g)); }
+
+template <typename T>
+__global__ void swiglu_kernel(const float *__restrict__ partial, uint32_t splits,
+                              size_t split_stride, T *__restrict__ act, uint32_t rows,
+                              uint32_t ffn) {
+  const size_t total = (size_t)rows * ffn;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = idx / ffn, f = idx % ffn;
+    const float *pg = partial + r * 2 * ffn + f;
+    float g = pg[0], u = pg[ffn];
+    for (uint32_t s = 1; s < splits; ++s) {
+      g += pg[s * split_stride];
+      u += pg[s * split_stride + ffn];
+    }
+    act[idx] = from_f32<T>(__fmul_rn(silu_f<T>(g), u));  // tensor.rs:186
+  }
+}
+
+__global__ void finish_linear_kernel(const float *__restrict__ partial, uint32_t splits,
+                                     size_t split_stride, const float *__restrict__ bias,
+                                     float *__restrict__ out, uint32_t rows, uint32_t n) {
+  const size_t total = (size_t)rows * n;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    float v = partial[idx];
+    for (uint32_t s = 1; s < splits; ++s) v += partial[s * split_stride + idx];
+    out[idx] = __fadd_rn(v, bias ? bias[idx % n] : 0.0f);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+argmax_kernel(const float *__restrict__ logits, uint32_t cols, uint32_t *__restrict__ out) {
+  __shared__ float s_val[8];
+  __shared__ uint32_t s_idx[8];
+  const float *row = logits + (size_t)blockIdx.x * cols;
+  float best = -INFINITY;
+  uint32_t best_i = UINT32_MAX;
+  for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = row[c];
+    if (v > best) {  // strict: the lowest index of equal maxima survives; NaN never wins
+      best = v;
+      best_i = c;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) {
+      best = ov;
+      best_i = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s_val[threadIdx.x >> 5] = best;
+    s_idx[threadIdx.x >> 5] = best_i;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) {
+      if (s_val[w] > best || (s_val[w] == best && s_idx[w] < best_i)) {
+        best = s_val[w];
+        best_i = s_idx[w];
+      }
+    }
+    out[blockIdx.x] = best_i;
+  }
+}
+
+template <typename T>
+__global__ void convert_from_f32_kernel(const float *__restrict__ src, T *__restrict__ dst,
+                                        size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = from_f32<T>(src[i]);
+}
+template <typename T>
+__global__ void convert_to_f32_kernel(const T *__restrict__ src, float *__restrict__ dst,
+                                      size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = to_f32<T>(src[i]);
+}
+template <typename T>
+__global__ void scale_convert_kernel(const float *__restrict__ src, T *__restrict__ dst, size_t n,
+                                     float scale) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = from_f32<T>(src[i] * scale);
+}
+__global__ void f16_to_f32_kernel(const uint16_t *__restrict__ src, float *__restrict__ dst,
+                                  size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = __half2float(__ushort_as_half(src[i]));
+}
+
+// One thread per arena element, indexed in reference order.
+template <typename T, bool kToReference>
+__global__ void arena_reorder_kernel(T *__restrict__ arena, KvLayout kv, float *__restrict__ ref,
+                                     size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    size_t r = idx;
+    const uint32_t d = r % kv.head_dim; r /= kv.head_dim;
+    const uint32_t head = r % kv.num_kv_heads; r /= kv.num_kv_heads;
+    const uint32_t slot = r % kv.block_size; r /= kv.block_size;
+    const uint32_t is_v = r % 2; r /= 2;
+    const uint32_t block = r % kv.num_blocks; r /= kv.num_blocks;
+    const uint32_t layer = (uint32_t)r;
+    const size_t a = kv.row(layer, block, head, is_v, slot) + kv.col(slot, d);
+    if (kToReference) ref[idx] = to_f32<T>(arena[a]);
+    else arena[a] = from_f32<T>(ref[idx]);
+  }
+}
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+template <typename T>
+__global__ void fill_normal_kernel(T *__restrict__ dst, size_t n, uint64_t seed) {
+  // Box-Muller on a counter-based stream: element pair (2i, 2i+1) from counter i.
+  const size_t pairs = (n + 1) / 2;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < pairs;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const uint64_t bits = splitmix64(seed ^ (i * 0xD1B54A32D192ED03ull));
+    const float u1 = ((uint32_t)(bits >> 40) + 1.0f) * (1.0f / 16777217.0f);
+    const float u2 = (uint32_t)(bits & 0xffffffu) * (1.0f / 16777216.0f);
+    const float r = sqrtf(-2.0f * __logf(u1));
+    float s, c;
+    __sincosf(6.28318530718f * u2, &s, &c);
+    dst[2 * i] = from_f32<T>(r * c);
+    if (2 * i + 1 < n) dst[2 * i + 1] = from_f32<T>(r * s);
+  }
+}
+
+inline uint32_t grid_for(size_t n, int threads) {
+  size_t g = (n + threads - 1) / threads;
+  const size_t cap = 148 * 16;  // a few waves over the 148 SMs; grid-stride covers the rest
+  return (uint32_t)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+inline int after_launch(const char *stage) {
+  count_launch();
+  ORION_CUDA_CHECK(stage, cudaGetLastError());
+  return ORION_OK;
+}
+
+}  // namespace
+
+template <typename T>
+int launch_embed_rmsnorm(const T *embed, const uint32_t *tokens, const float *norm_w, float eps,
+                         float *hidden, T *normed, uint32_t rows, uint32_t hidden_size,
+                         cudaStream_t stream) {
+  if (rows == 0) return ORION_OK;
+  embed_rmsnorm_kernel<T><<<rows, kNormThreads, 0, stream>>>(embed, tokens, norm_w, eps, hidden,
+                                                             normed, hidden_size);
+  return after_launch("embed_rmsnorm");
+}
+
+template <typename T>
+int launch_residual_rmsnorm(const float *partial, uint32_t splits, size_t split_stride,
+                            float *hidden, const float *norm_w, float eps, T *out,
+                            const uint32_t *row_map, uint32_t out_rows, uint32_t hidden_size,
+                            cudaStream_t stream) {
+  if (out_rows == 0) return ORION_OK;
+  const size_t smem = (size_t)hidden_size * sizeof(float);
+  if (smem > 200 * 1024)
+    return set_error(ORION_ERR_INTERNAL, "hidden size %u too large for the fused norm kernel",
+                     hidden_size);
+  if (smem > 48 * 1024)
+    ORION_CUDA_CHECK("residual_rmsnorm attr",
+                     cudaFuncSetAttribute(residual_rmsnorm_kernel<T>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  residual_rmsnorm_kernel<T><<<out_rows, kNormThreads, smem, stream>>>(
+      partial, splits, split_stride, hidden, norm_w, eps, out, row_map, hidden_size);
+  return after_launch("residual_rmsnorm");
+}
+
+template <typename T>
+int launch_rmsnorm_rows(const float *x, const float *norm_w, float eps, T *out, uint32_t rows,
+                        uint32_t cols, cudaStream_t stream) {
+  return launch_residual_rmsnorm<T>(nullptr, 0, 0, const_cast<float *>(x), norm_w, eps, out,
+                                    nullptr, rows, cols, stream);
+}
+
+template <typename T>
+int launch_rope_kvwrite(const float *partial, uint32_t splits, size_t split_stride,
+                        const float *bias, const uint32_t *positions, const uint32_t *slot_block,
+                        const uint32_t *slot_slot, const float *rope_cos, const float *rope_sin,
+                        T *q_out, T *arena, KvLayout kv, uint32_t layer, uint32_t rows,
+                        uint32_t q_heads, cudaStream_t stream) {
+  if (rows == 0) return ORION_OK;
+  const uint32_t half = kv.head_dim / 2;
+  const uint32_t threads = half >= 128 ? 128 : (half < 32 ? 32 : ((half + 31) / 32) * 32);
+  dim3 grid(rows, q_heads + 2 * kv.num_kv_heads);
+  rope_kvwrite_kernel<T><<<grid, threads, 0, stream>>>(partial, splits, split_stride, bias,
+                                                       positions, slot_block, slot_slot, rope_cos,
+                                                       rope_sin, q_out, arena, kv, layer, q_heads);
+  return after_launch("rope_kvwrite");
+}
+
+template <typename T>
+int launch_rope_rows(T *x, const uint32_t *positions, const float *rope_cos, const float *rope_sin,
+                     uint32_t rows, uint32_t heads, uint32_t head_dim, cudaStream_t stream) {
+  if (rows == 0 || heads == 0) return ORION_OK;
+  rope_rows_kernel<T><<<dim3(rows, heads), 64, 0, stream>>>(x, positions, rope_cos, rope_sin, heads,
+                                                            head_dim);
+  return after_launch("rope");
+}
+
+template <typename T>
+int launch_swiglu(const float *partial, uint32_t splits, size_t split_stride, T *act, uint32_t rows,
+                  uint32_t ffn, cudaStream_t stream) {
+  if (rows == 0 || ffn == 0) return ORION_OK;
+  swiglu_kernel<T><<<grid_for((size_t)rows * ffn, 256), 256, 0, stream>>>(partial, splits,
+                                                                          split_stride, act, rows,
+                                                                          ffn);
+  return after_launch("swiglu");
+}
+
+int launch_finish_linear(const float *partial, uint32_t splits, size_t split_stride,
+                         const float *bias, float *out, uint32_t rows, uint32_t n,
+                         cudaStream_t stream) {
+  if (rows == 0 || n == 0) return ORION_OK;
+  finish_linear_kernel<<<grid_for((size_t)rows * n, 256), 256, 0, stream>>>(
+      partial, splits, split_stride, bias, out, rows, n);
+  return after_launch("finish_linear");
+}
+
+int launch_argmax(const float *logits, uint32_t rows, uint32_t cols, uint32_t *out,
+                  cudaStream_t stream) {
+  if (rows == 0) return ORION_OK;
+  argmax_kernel<<<rows, 256, 0, stream>>>(logits, cols, out);
+  return after_launch("argmax");
+}
+
+template <typename T>
+int launch_convert_from_f32(const float *src, T *dst, size_t n, cudaStream_t stream) {
+  if (n == 0) return ORION_OK;
+  convert_from_f32_kernel<T><<<grid_for(n, 256), 256, 0, stream>>>(src, dst, n);
+  return after_launch("convert_from_f32");
+}
+template <typename T>
+int launch_convert_to_f32(const T *src, float *dst, size_t n, cudaStream_t stream) {
+  if (n == 0) return ORION_OK;
+  convert_to_f32_kernel<T><<<grid_for(n, 256), 256, 0, stream>>>(src, dst, n);
+  return after_launch("convert_to_f32");
+}
+int launch_f16_to_f32(const uint16_t *src, float *dst, size_t n, cudaStream_t stream) {
+  if (n == 0) return ORION_OK;
+  f16_to_f32_kernel<<<grid_for(n, 256), 256, 0, stream>>>(src, dst, n);
+  return after_launch("f16_to_f32");
+}
+
+template <typename T>
+int launch_scale_convert(const float *src, T *dst, size_t n, float scale, cudaStream_t stream) {
+  if (n == 0) return ORION_OK;
+  scale_convert_kernel<T><<<grid_for(n, 256), 256, 0, stream>>>(src, dst, n, scale);
+  return after_launch("scale_convert");
+}
+
+template <typename T>
+int launch_arena_to_reference_order(const T *arena, KvLayout kv, float *out, cudaStream_t stream) {
+  const size_t total = kv.layer_elems() * kv.num_layers;
+  if (total == 0) return ORION_OK;
+  arena_reorder_kernel<T, true><<<grid_for(total, 256), 256, 0, stream>>>(const_cast<T *>(arena),
+                                                                          kv, out, total);
+  return after_launch("arena_to_reference_order");
+}
+template <typename T>
+int launch_arena_from_reference_order(const float *ref, KvLayout kv, T *arena,
+                                      cudaStream_t stream) {
+  const size_t total = kv.layer_elems() * kv.num_layers;
+  if (total == 0) return ORION_OK;
+  arena_reorder_kernel<T, false><<<grid_for(total, 256), 256, 0, stream>>>(
+      arena, kv, const_cast<float *>(ref), total);
+  return after_launch("arena_from_reference_order");
+}
+
+template <typename T>
+int launch_fill_normal(T *dst, size_t n, uint64_t seed, cudaStream_t stream) {
+  if (n == 0) return ORION_OK;
+  fill_normal_kernel<T><<<grid_for((n + 1) / 2, 256), 256, 0, stream>>>(dst, n, seed);
+  return after_launch("fill_normal");
+}
+
+#define ORION_INSTANTIATE(T)                                                                      \
+  template int launch_embed_rmsnorm<T>(const T *, const uint32_t *, const float *, float, float *, \
+                                       T *, uint32_t, uint32_t, cudaStream_t);                    \
+  template int launch_residual_rmsnorm<T>(const float *, uint32_t, size_t, float *, const float *, \
+                                          float, T *, const uint32_t *, uint32_t, uint32_t,       \
+                                          cudaStream_t);                                          \
+  template int launch_rmsnorm_rows<T>(const float *, const float *, float, T *, uint32_t,         \
+                                      uint32_t, cudaStream_t);                                    \
+  template int launch_rope_kvwrite<T>(const float *, uint32_t, size_t, const float *,             \
+                                      const uint32_t *, const uint32_t *, const uint32_t *,       \
+                                      const float *, const float *, T *, T *, KvLayout, uint32_t, \
+                                      uint32_t, uint32_t, cudaStream_t);                          \
+  template int launch_rope_rows<T>(T *, const uint32_t *, const float *, const float *, uint32_t, \
+                                   uint32_t, uint32_t, cudaStream_t);                             \
+  template int launch_swiglu<T>(const float *, uint32_t, size_t, T *, uint32_t, uint32_t,         \
+                                cudaStream_t);                                                    \
+  template int launch_convert_from_f32<T>(const float *, T *, size_t, cudaStream_t);              \
+  template int launch_convert_to_f32<T>(const T *, float *, size_t, cudaStream_t);                \
+  template int launch_arena_to_reference_order<T>(const T *, KvLayout, float *, cudaStream_t);    \
+  template int launch_arena_from_reference_order<T>(const float *, KvLayout, T *, cudaStream_t);  \
+  template int launch_scale_convert<T>(const float *, T *, size_t, float, cudaStream_t);           \
+  template int launch_fill_normal<T>(T *, size_t, uint64_t, cudaStream_t);
+
+ORION_INSTANTIATE(float)
+ORION_INSTANTIATE(bf16)
+
+}  // namespace orion

@@ -1,0 +1,412 @@
+// bf16 GEMM on the 5th-generation tensor cores:  partial[s][r][n] = sum_k x[r][k] * w[n][k]
+// (tensor.rs:114-128 without the bias), f32 accumulation in tensor memory.
+//
+// The weight matrix is the M operand of the MMA ("swap A/B"): a CTA owns a tile
+// of 128 weight rows x TOKN tokens, so the batch size only changes the N extent
+// of the instruction and a decode step (1..256 tokens) streams every weight
+// byte exactly once. W [n][k] and x [r][k] are both K-major as stored, so no
+// transposition is needed.
+//
+// Per CTA (192 threads):
+//   warp 0   one lane issues TMA tensor loads (128B-swizzled 64-wide k slabs of
+//            the W tile and the x tile) into a multi-stage ring, completion
+//            counted on "full" mbarriers;
+//   warp 1   allocates tensor memory, one lane issues tcgen05.mma (128 x TOKN x 16,
+//            four per k slab) and commits to the "empty" barrier of the stage;
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (lane = weight row, column =
+//            token) and store f32 partials, 128 contiguous bytes per warp store.
+// Split-K: blockIdx.z owns a contiguous range of k slabs and writes its own slab
+// of the partial buffer; the consumer kernel sums the slabs.
+// No cluster launch and no multicast: every CTA loads its own tiles.
+// Every wait is bounded; a wait that runs out sets a device error word and the
+// CTA still releases its tensor memory before returning.
+#include "kernels.h"
+
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace orion {
+namespace {
+
+constexpr int kTileN = 128;   // weight rows per CTA (M of the MMA)
+constexpr int kSlabK = 64;    // k elements per stage: 128 bytes = one swizzle atom
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+
+__device__ uint32_t g_gemm_error = 0;
+
+template <int TOKN>
+struct TcConfig {
+  static constexpr int kWBytes = kTileN * kSlabK * 2;
+  static constexpr int kXBytes = TOKN * kSlabK * 2;
+  static constexpr int kStageBytes = kWBytes + kXBytes;
+  // <= 64 tokens: ~96 KiB so two CTAs share an SM; larger tiles take the SM alone.
+  static constexpr int kStages = TOKN <= 16 ? 5 : (TOKN <= 64 ? 4 : (TOKN == 128 ? 6 : 4));
+  static constexpr int kTmemCols = TOKN < 32 ? 32 : TOKN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(dst_smem)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes
+// with the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride offset),
+// the leading offset is unused for swizzled K-major tiles (encoded 1),
+// descriptor version 1, layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor: f32 accumulate, bf16 x bf16, both operands K-major,
+// N = TOKN (>>3 at bit 17), M = 128 (>>4 at bit 24).
+template <int TOKN>
+__device__ __forceinline__ constexpr uint32_t instr_desc() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TOKN >> 3) << 17) |
+         ((uint32_t)(kTileN >> 4) << 24);
+}
+
+template <int TOKN>
+__global__ void __launch_bounds__(kThreads)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               float *__restrict__ partial, uint32_t M, uint32_t N, uint32_t K, uint32_t splits) {
+  using Cfg = TcConfig<TOKN>;
+  extern __shared__ uint8_t raw_smem[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
+                                              ~uintptr_t(1023));
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t *empty = full + Cfg::kStages;
+  uint64_t *acc_ready = empty + Cfg::kStages;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t n0 = blockIdx.x * kTileN, t0 = blockIdx.y * TOKN, split = blockIdx.z;
+  const uint32_t nkb = (K + kSlabK - 1) / kSlabK;
+  const uint32_t kb_begin = (uint32_t)((uint64_t)split * nkb / splits);
+  const uint32_t kb_end = (uint32_t)((uint64_t)(split + 1) * nkb / splits);
+  const uint32_t my_kb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_ready, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (uint32_t i = 0; i < my_kb; ++i) {
+        const uint32_t s = i % Cfg::kStages, use = i / Cfg::kStages;
+        if (!mbar_wait(&empty[s], (use & 1) ^ 1)) { ok = false; break; }
+        uint8_t *wt = smem + s * Cfg::kStageBytes;
+        uint8_t *xt = wt + Cfg::kWBytes;
+        mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+        const int kc = (int)((kb_begin + i) * kSlabK);
+        tma_load_2d(wt, &map_w, kc, (int)n0, &full[s]);
+        tma_load_2d(xt, &map_x, kc, (int)t0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc<TOKN>();
+      for (uint32_t i = 0; i < my_kb; ++i) {
+        const uint32_t s = i % Cfg::kStages, use = i / Cfg::kStages;
+        if (!mbar_wait(&full[s], use & 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t wt = smem_u32(smem + s * Cfg::kStageBytes);
+        const uint32_t xt = wt + Cfg::kWBytes;
+#pragma unroll
+        for (int k = 0; k < kSlabK / kUmmaK; ++k) {
+          // advancing 16 k elements inside the swizzle atom = +32 bytes on the start address
+          const uint64_t a = smem_desc_sw128(wt + k * kUmmaK * 2);
+          const uint64_t b = smem_desc_sw128(xt + k * kUmmaK * 2);
+          umma_bf16(tmem_base, a, b, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+      }
+      umma_commit(acc_ready);    // arrives when every MMA above has completed
+    }
+  } else {
+    // Epilogue warps: warp w may touch tensor-memory lanes 32*(w%4) .. +31.
+    const uint32_t lq = warp & 3;
+    if (my_kb > 0) {
+      if (!mbar_wait(acc_ready, 0)) ok = false;
+    }
+    tc_fence_after();
+    const uint32_t n = n0 + lq * 32 + lane;
+    float *dst = partial + (size_t)split * M * N;
+#pragma unroll 1
+    for (int c = 0; c < TOKN; c += 16) {
+      if (t0 + c >= M) break;  // warp-uniform
+      uint32_t r[16];
+      if (ok && my_kb > 0) {
+        tmem_ld16(tmem_base + ((lq * 32u) << 16) + (uint32_t)c, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r[j] = 0u;
+      }
+      if (n < N) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t tok = t0 + c + j;
+          if (tok < M) dst[(size_t)tok * N + n] = __uint_as_float(r[j]);
+        }
+      }
+    }
+  }
+  if (!ok) atomicOr(&g_gemm_error, 1u);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+// ---- host side -----------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                              const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                              const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return (EncodeFn) nullptr;
+    return (EncodeFn)p;
+  }();
+  return fn;
+}
+
+// [rows][k] bf16 matrix with row stride ld; box = 64 k x box_rows, 128-byte swizzle.
+int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t k, uint64_t ld,
+             uint32_t box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return set_error(ORION_ERR_BACKEND, "backend cuda failed at tensor map: driver entry point missing");
+  const cuuint64_t dims[2] = {k, rows};
+  const cuuint64_t strides[1] = {ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kSlabK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(ORION_ERR_BACKEND, "backend cuda failed at tensor map: encode returned %d (rows %llu k %llu ld %llu)",
+                     (int)r, (unsigned long long)rows, (unsigned long long)k, (unsigned long long)ld);
+  return ORION_OK;
+}
+
+struct MapKey {
+  const void *base;
+  uint64_t rows, k, ld;
+  uint32_t box_rows;
+  bool operator<(const MapKey &o) const {
+    return std::tie(base, rows, k, ld, box_rows) < std::tie(o.base, o.rows, o.k, o.ld, o.box_rows);
+  }
+};
+
+int cached_map(const void *base, uint64_t rows, uint64_t k, uint64_t ld, uint32_t box_rows,
+               const CUtensorMap **out) {
+  static std::mutex mu;
+  static std::map<MapKey, CUtensorMap> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  MapKey key{base, rows, k, ld, box_rows};
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    if (cache.size() > 65536) cache.clear();
+    CUtensorMap m;
+    ORION_TRY(make_map(&m, base, rows, k, ld, box_rows));
+    it = cache.emplace(key, m).first;
+  }
+  *out = &it->second;
+  return ORION_OK;
+}
+
+template <int TOKN>
+int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
+              uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream) {
+  using Cfg = TcConfig<TOKN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    ORION_CUDA_CHECK("gemm_tc attr",
+                     cudaFuncSetAttribute(gemm_tc_kernel<TOKN>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          Cfg::kSmemBytes));
+    attr_set = true;
+  }
+  const CUtensorMap *mw, *mx;
+  ORION_TRY(cached_map(w, n, k, ldw, kTileN, &mw));
+  ORION_TRY(cached_map(x, rows, k, ldx, TOKN, &mx));
+  dim3 grid((n + kTileN - 1) / kTileN, (rows + TOKN - 1) / TOKN, splits);
+  gemm_tc_kernel<TOKN><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(*mw, *mx, partial, rows, n, k,
+                                                                    splits);
+  count_launch();
+  ORION_CUDA_CHECK("gemm_tc", cudaGetLastError());
+  return ORION_OK;
+}
+
+uint32_t token_tile(uint32_t rows) {
+  if (rows <= 16) return 16;
+  if (rows <= 32) return 32;
+  if (rows <= 64) return 64;
+  if (rows <= 128) return 128;
+  return 256;
+}
+
+}  // namespace
+
+bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint32_t ldw,
+                       const void *x, const void *w) {
+  return rows > 0 && n > 0 && k >= (uint32_t)kSlabK && k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 &&
+         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
+         encode_fn() != nullptr;
+}
+
+int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
+                   uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream) {
+  const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
+  if (splits < 1 || splits > nkb)
+    return set_error(ORION_ERR_INTERNAL, "gemm split count %u outside 1..%u", splits, nkb);
+  switch (token_tile(rows)) {
+    case 16: return launch_tc<16>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+    case 32: return launch_tc<32>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+    case 64: return launch_tc<64>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+    case 128: return launch_tc<128>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+    default: return launch_tc<256>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+  }
+}
+
+int gemm_tc_poll_error(uint32_t *code) {
+  uint32_t v = 0;
+  ORION_CUDA_CHECK("gemm error word", cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof v));
+  if (v) {
+    uint32_t zero = 0;
+    ORION_CUDA_CHECK("gemm error word", cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof zero));
+  }
+  *code = v;
+  return ORION_OK;
+}
+
+// ---- planning and dispatch -------------------------------------------------------
+
+namespace {
+uint32_t g_target_ctas = 148;  // one wave of the 148 SMs
+}
+
+void gemm_set_target_ctas(uint32_t v) { g_target_ctas = v ? v : 148; }
+
+GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx,
+                   uint32_t ldw) {
+  GemmPlan p{1, false};
+  if (!is_bf16) return p;
+  // alignment of the pointers is checked at launch; shapes decide the plan
+  if (!(rows > 0 && n > 0 && k >= (uint32_t)kSlabK && k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 &&
+        encode_fn() != nullptr))
+    return p;
+  p.tensor_core = true;
+  if (rows > 256) return p;  // many token tiles already fill the machine
+  const uint32_t tiles = ((n + kTileN - 1) / kTileN) * ((rows + token_tile(rows) - 1) / token_tile(rows));
+  const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
+  uint32_t s = g_target_ctas / (tiles ? tiles : 1);
+  const uint32_t cap = nkb / 4 ? nkb / 4 : 1;  // at least four k slabs per split
+  if (s > cap) s = cap;
+  if (s > 16) s = 16;
+  p.splits = s < 1 ? 1 : s;
+  return p;
+}
+
+size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t k) {
+  size_t best = (size_t)max_rows * n;
+  if (!is_bf16) return best;
+  const uint32_t lim = max_rows < 256 ? max_rows : 256;
+  for (uint32_t r = 1; r <= lim; ++r) {
+    const GemmPlan p = gemm_plan(true, r, n, k, k, k);
+    const size_t need = (size_t)p.splits * r * n;
+    if (need > best) best = need;
+  }
+  return best;
+}
+
+template <>
+int launch_gemm<float>(const float *x, uint32_t ldx, const float *w, uint32_t ldw, float *partial,
+                       uint32_t rows, uint32_t n, uint32_t k, GemmPlan, cudaStream_t stream) {
+  return launch_gemm_simt<float>(x, ldx, w, ldw, partial, rows, n, k, stream);
+}
+
+template <>
+int launch_gemm<bf16>(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
+                      uint32_t rows, uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream) {
+  if (plan.tensor_core) {
+    if (!gemm_tc_supported(rows, n, k, ldx, ldw, x, w))
+      return set_error(ORION_ERR_INTERNAL, "tensor-core GEMM planned for an unaligned operand");
+    return launch_gemm_tc(x, ldx, w, ldw, partial, rows, n, k, plan.splits, stream);
+  }
+  return launch_gemm_simt<bf16>(x, ldx, w, ldw, partial, rows, n, k, stream);
+}
+
+}  // namespace orion

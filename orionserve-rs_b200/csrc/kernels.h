@@ -1,0 +1,177 @@
+// Launchers of the device kernels. Every pointer is a device pointer; every
+// launcher enqueues on `stream` and returns an OrionStatus. `T` is the storage
+// type of weights, activations and the KV arena (float for the correctness
+// build, bf16 for the performance build). GEMM results are always f32
+// "partials": `splits` slabs of [rows][n] that the consuming kernel sums, which
+// fuses the split-K reduction into the next elementwise step.
+#pragma once
+
+#include "common.cuh"
+
+namespace orion {
+
+// Shape of the paged KV arena of one rank:
+// [layer][block][local kv head][k|v][slot][dim]. Each (block, head) owns one
+// contiguous chunk holding its K rows followed by its V rows, so a decode CTA
+// fetches a 16-token block of one head with a single bulk copy.
+// With `swizzle` set (16-bit storage, head_dim a multiple of 64) the 16-byte
+// groups of every row are XOR-permuted by (slot & 7): the linear bulk copy then
+// lands in shared memory in a layout ldmatrix reads without bank conflicts.
+struct KvLayout {
+  uint32_t num_layers, num_blocks, num_kv_heads, block_size, head_dim, swizzle;
+  __host__ __device__ size_t chunk_elems() const { return size_t(2) * block_size * head_dim; }
+  __host__ __device__ size_t layer_elems() const {
+    return size_t(num_blocks) * num_kv_heads * chunk_elems();
+  }
+  // Start of the row holding (layer, block, head, k|v, slot).
+  __host__ __device__ size_t row(uint32_t layer, uint32_t block, uint32_t head, uint32_t is_v,
+                                 uint32_t slot) const {
+    return layer * layer_elems() + (size_t(block) * num_kv_heads + head) * chunk_elems() +
+           (size_t(is_v) * block_size + slot) * head_dim;
+  }
+  // Position of logical dim `d` inside the row of `slot`.
+  __host__ __device__ uint32_t col(uint32_t slot, uint32_t d) const {
+    return swizzle ? ((((d >> 3) ^ (slot & 7u)) << 3) | (d & 7u)) : d;
+  }
+};
+
+// hidden[r] = embed[tokens[r]] (f32); normed[r] = rms_norm(hidden[r]) * w.
+// (transformer.rs:208-223 fused with tensor.rs:143-163)
+template <typename T>
+int launch_embed_rmsnorm(const T *embed, const uint32_t *tokens, const float *norm_w, float eps,
+                         float *hidden, T *normed, uint32_t rows, uint32_t hidden_size,
+                         cudaStream_t stream);
+
+// hidden[r] += sum_s partial[s][r] (+ nothing else); out[i] = rms_norm(hidden[src(i)]) * w,
+// src(i) = row_map ? row_map[i] : i. With row_map the residual is not written
+// back (used for the final norm over the last row of each sequence).
+// (transformer.rs:330-336, 343-345, 401-428)
+template <typename T>
+int launch_residual_rmsnorm(const float *partial, uint32_t splits, size_t split_stride,
+                            float *hidden, const float *norm_w, float eps, T *out,
+                            const uint32_t *row_map, uint32_t out_rows, uint32_t hidden_size,
+                            cudaStream_t stream);
+
+// Plain rms_norm of f32 rows into T (tensor.rs:143-163) for the op-level API.
+template <typename T>
+int launch_rmsnorm_rows(const float *x, const float *norm_w, float eps, T *out, uint32_t rows,
+                        uint32_t cols, cudaStream_t stream);
+
+// Sums the QKV partials (+bias), applies RoPE to q and k heads by table lookup
+// at positions[r], writes q to `q_out` [rows][q_heads*hd] and k, v into the
+// arena at (slot_block[r], slot_slot[r]). (transformer.rs:248-297, tensor.rs:283-298)
+template <typename T>
+int launch_rope_kvwrite(const float *partial, uint32_t splits, size_t split_stride,
+                        const float *bias, const uint32_t *positions, const uint32_t *slot_block,
+                        const uint32_t *slot_slot, const float *rope_cos, const float *rope_sin,
+                        T *q_out, T *arena, KvLayout kv, uint32_t layer, uint32_t rows,
+                        uint32_t q_heads, cudaStream_t stream);
+
+// In-place RoPE over [rows][heads][hd] of T (op-level API; tensor.rs:283-298).
+template <typename T>
+int launch_rope_rows(T *x, const uint32_t *positions, const float *rope_cos, const float *rope_sin,
+                     uint32_t rows, uint32_t heads, uint32_t head_dim, cudaStream_t stream);
+
+// act[r][f] = silu(g) * u with g = sum_s partial[s][r][f], u = sum_s partial[s][r][ffn + f].
+// (tensor.rs:167-189)
+template <typename T>
+int launch_swiglu(const float *partial, uint32_t splits, size_t split_stride, T *act, uint32_t rows,
+                  uint32_t ffn, cudaStream_t stream);
+
+// out[r][n] = sum_s partial[s][r][n] + bias[n]  (finishes tensor::linear, tensor.rs:126).
+int launch_finish_linear(const float *partial, uint32_t splits, size_t split_stride,
+                         const float *bias, float *out, uint32_t rows, uint32_t n,
+                         cudaStream_t stream);
+
+// First index of the strict row maximum; UINT32_MAX when nothing exceeds -inf.
+// (orion-runtime/src/sampling.rs:196-206)
+int launch_argmax(const float *logits, uint32_t rows, uint32_t cols, uint32_t *out,
+                  cudaStream_t stream);
+
+// Converts between f32 and T on the device (weight upload, arena read-back).
+template <typename T>
+int launch_convert_from_f32(const float *src, T *dst, size_t n, cudaStream_t stream);
+template <typename T>
+int launch_convert_to_f32(const T *src, float *dst, size_t n, cudaStream_t stream);
+int launch_f16_to_f32(const uint16_t *src, float *dst, size_t n, cudaStream_t stream);
+// dst[i] = T(src[i] * scale)
+template <typename T>
+int launch_scale_convert(const float *src, T *dst, size_t n, float scale, cudaStream_t stream);
+
+// Arena -> the reference's logical order [layer][block][k|v][slot][head][dim], f32.
+template <typename T>
+int launch_arena_to_reference_order(const T *arena, KvLayout kv, float *out, cudaStream_t stream);
+// The reverse, for one layer given in reference order (op-level attention API).
+template <typename T>
+int launch_arena_from_reference_order(const float *ref, KvLayout kv, T *arena, cudaStream_t stream);
+
+// Fills `n` elements with N(0, 1) values from a counter-based generator.
+template <typename T>
+int launch_fill_normal(T *dst, size_t n, uint64_t seed, cudaStream_t stream);
+
+// ---- attention ---------------------------------------------------------------
+
+struct AttnBatch {
+  const uint32_t *query_positions;  // [rows] absolute position of each query row
+  const uint32_t *seq_of_row;       // [rows]
+  const uint32_t *tables_flat;      // concatenated block tables
+  const uint32_t *table_offsets;    // [sequences + 1]
+  uint32_t rows;
+  uint32_t max_position;            // largest query position in the batch
+};
+
+// Any shape, any mix of prefill and decode rows: one CTA per (row, query head),
+// causal by absolute position (attention.rs:219-295).
+template <typename T>
+int launch_paged_attention_generic(const T *q, const T *arena, KvLayout kv, uint32_t layer,
+                                   AttnBatch batch, uint32_t q_heads, T *out, cudaStream_t stream);
+
+// Tuned decode path (bf16, head_dim 128, block 16, one query row per sequence):
+// one CTA per (sequence, kv head, context split); the query heads of a GQA group
+// share every K/V tile. `scratch` holds the per-split partial outputs.
+struct DecodeScratch {
+  float *partial_out;  // [rows][q_heads][max_splits][head_dim]
+  float *partial_ml;   // [rows][q_heads][max_splits][2]  (running max, running sum)
+  uint32_t max_splits;
+};
+bool decode_attention_supported(KvLayout kv, uint32_t q_heads);
+size_t decode_scratch_floats(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
+                             uint32_t max_splits);
+uint32_t decode_choose_splits(uint32_t rows, uint32_t kv_heads, uint32_t max_position,
+                              uint32_t block_size, uint32_t max_splits);
+int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer,
+                                  AttnBatch batch, uint32_t q_heads, uint32_t splits,
+                                  DecodeScratch scratch, bf16 *out, cudaStream_t stream);
+// Device error word of the decode kernel (0 = none); reading clears it.
+int decode_poll_error(uint32_t *code);
+
+// ---- GEMM ----------------------------------------------------------------------
+
+// partial[s][r][n] = sum over the k-range of split s of x[r][k] * w[n][k]
+// (tensor.rs:114-128 without the bias). x: [rows][k] (row stride ldx),
+// w: [n][k] row-major (row stride ldw).
+struct GemmPlan {
+  uint32_t splits;
+  bool tensor_core;  // tcgen05 path (bf16 only)
+};
+GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint32_t ldw);
+template <typename T>
+int launch_gemm(const T *x, uint32_t ldx, const T *w, uint32_t ldw, float *partial, uint32_t rows,
+                uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream);
+size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t k);
+// Number of CTAs split-K aims for on small batches (default 148, one per SM).
+void gemm_set_target_ctas(uint32_t ctas);
+
+// SIMT GEMM: exact k-ascending accumulation per output, no FMA for f32.
+template <typename T>
+int launch_gemm_simt(const T *x, uint32_t ldx, const T *w, uint32_t ldw, float *out, uint32_t rows,
+                     uint32_t n, uint32_t k, cudaStream_t stream);
+// tcgen05 / TMEM / TMA GEMM (bf16).
+bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint32_t ldw,
+                       const void *x, const void *w);
+int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
+                   uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream);
+// Device error word set by kernels whose bounded waits ran out (0 = none).
+int gemm_tc_poll_error(uint32_t *code);
+
+}  // namespace orion

@@ -1,0 +1,756 @@
+// Device model: weights, paged KV arena, RoPE tables, work buffers and the
+// per-step kernel sequence. Mirrors TransformerModel::{new, forward}
+// (crates/orion-models/src/transformer.rs:148-177, 230-442) with every tensor
+// operation on the GPU; the host only validates the batch, resolves slots
+// (attention.rs:182-186) and launches.
+#include "model.h"
+
+#include <cmath>
+#include <cstring>
+
+namespace orion {
+
+int compute_layout(uint32_t heads, uint32_t kv_heads, uint32_t ffn, uint32_t rank, uint32_t world,
+                   ParallelLayout *out) {
+  // Rank::new (orion-distributed/src/lib.rs:74-90)
+  if (world == 0) return set_error(ORION_ERR_INVALID_REQUEST, "world_size must be at least 1");
+  if (rank >= world)
+    return set_error(ORION_ERR_INVALID_REQUEST, "rank %u is out of range for world size %u", rank,
+                     world);
+  if (world == 1) {  // lib.rs:175-190
+    *out = ParallelLayout{{0, heads}, {0, kv_heads}, {0, ffn}};
+    return ORION_OK;
+  }
+  if (kv_heads < world)  // lib.rs:193-200
+    return set_error(ORION_ERR_INVALID_REQUEST,
+                     "model has %u KV heads but world size is %u; tensor parallelism beyond the KV "
+                     "head count would require replicating them, which is not implemented",
+                     kv_heads, world);
+  auto shard = [&](uint32_t total, Shard *s) -> int {  // shard_dimension, lib.rs:139-152
+    if (total % world != 0)
+      return set_error(ORION_ERR_INVALID_REQUEST,
+                       "cannot split %u evenly across %u ranks; tensor parallelism requires the "
+                       "dimension to be divisible by the world size",
+                       total, world);
+    s->len = total / world;
+    s->start = (uint64_t)rank * s->len;
+    return ORION_OK;
+  };
+  ORION_TRY(shard(heads, &out->query_heads));
+  ORION_TRY(shard(kv_heads, &out->kv_heads));
+  ORION_TRY(shard(ffn, &out->ffn));
+  return ORION_OK;
+}
+
+namespace {
+
+template <typename T>
+struct DTypeOf;
+template <>
+struct DTypeOf<float> { static constexpr int value = ORION_DTYPE_F32; static constexpr bool is_bf16 = false; };
+template <>
+struct DTypeOf<bf16> { static constexpr int value = ORION_DTYPE_BF16; static constexpr bool is_bf16 = true; };
+
+size_t dtype_size(int dtype) {
+  switch (dtype) {
+    case ORION_DTYPE_F32: return 4;
+    case ORION_DTYPE_F16:
+    case ORION_DTYPE_BF16: return 2;
+    default: return 0;
+  }
+}
+
+enum : uint32_t {
+  kGotInNorm = 1u << 0, kGotPostNorm = 1u << 1, kGotQ = 1u << 2, kGotK = 1u << 3, kGotV = 1u << 4,
+  kGotO = 1u << 5, kGotGate = 1u << 6, kGotUp = 1u << 7, kGotDown = 1u << 8,
+  kGotAllLayer = (1u << 9) - 1,
+};
+
+template <typename T>
+class Model final : public ModelBase {
+ public:
+  Model(OrionBackend *backend, const OrionModelDesc &d) : backend_(backend), d_(d) {}
+  ~Model() override {
+    cudaSetDevice(backend_->ordinal);
+    if (stream_) cudaStreamSynchronize(stream_);
+    for (void *p : allocs_) cudaFree(p);
+    if (h_meta_) cudaFreeHost(h_meta_);
+    if (stage_raw_) cudaFree(stage_raw_);
+    if (stage_f32_) cudaFree(stage_f32_);
+    if (ev0_) cudaEventDestroy(ev0_);
+    if (ev1_) cudaEventDestroy(ev1_);
+    if (stream_) cudaStreamDestroy(stream_);
+  }
+
+  int init();
+  int load_tensor(const char *name, int dtype, const uint64_t *shape, int ndim,
+                  const void *data) override;
+  int init_random(uint64_t seed, float std) override;
+  int finalize() override;
+  int forward(const BatchView &b, float *logits_out, uint64_t logits_capacity,
+              uint32_t *token_ids_out) override;
+  int replay(int iterations, float *elapsed_ms) override;
+  int read_kv(float *out, uint64_t capacity) override;
+  uint64_t last_launch_count() const override { return last_launches_; }
+  const OrionModelDesc &desc() const override { return d_; }
+
+ private:
+  struct Layer {
+    T *w_qkv = nullptr, *w_o = nullptr, *w_gu = nullptr, *w_down = nullptr;
+    float *b_qkv = nullptr, *in_norm = nullptr, *post_norm = nullptr;
+    uint32_t got = 0;
+    bool any_bias = false;
+  };
+
+  template <typename U>
+  int alloc(U **p, size_t count) {
+    void *raw = nullptr;
+    ORION_CUDA_CHECK("allocate", cudaMalloc(&raw, (count ? count : 1) * sizeof(U)));
+    allocs_.push_back(raw);
+    *p = static_cast<U *>(raw);
+    return ORION_OK;
+  }
+  int ensure_stage(void **buf, size_t *cap, size_t bytes) {
+    if (*cap >= bytes) return ORION_OK;
+    if (*buf) cudaFree(*buf);
+    *buf = nullptr;
+    *cap = 0;
+    ORION_CUDA_CHECK("allocate staging", cudaMalloc(buf, bytes));
+    *cap = bytes;
+    return ORION_OK;
+  }
+  // Copies rows [r0,r1) x cols [c0,c1) of a host [R][C] tensor of `dtype` into a
+  // contiguous device destination (`dst_t` of T or `dst_f`, whichever is non-null),
+  // converting once at load like the reference's loader (loader.rs:74-96).
+  int upload_slice(T *dst_t, float *dst_f, const void *src, int dtype, uint64_t C, uint64_t r0,
+                   uint64_t r1, uint64_t c0, uint64_t c1);
+  int run_step(bool want_argmax);
+  int tp_reduce(uint32_t *splits, size_t slab);
+
+  OrionBackend *backend_;
+  OrionModelDesc d_;
+  cudaStream_t stream_ = nullptr;
+  cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+  std::vector<void *> allocs_;
+  ParallelLayout lay_;
+  uint32_t lq_ = 0, lkv_ = 0, lf_ = 0;
+  KvLayout kv_{};
+
+  std::vector<Layer> layers_;
+  T *embed_ = nullptr, *lm_head_ = nullptr, *lm_head_own_ = nullptr;
+  float *final_norm_ = nullptr;
+  bool got_embed_ = false, got_head_ = false, got_final_norm_ = false, finalized_ = false;
+  T *arena_ = nullptr;
+  float *rope_cos_ = nullptr, *rope_sin_ = nullptr;
+
+  // work buffers
+  float *hidden_ = nullptr, *partial_ = nullptr, *logits_ = nullptr, *dscratch_ = nullptr;
+  T *normed_ = nullptr, *qbuf_ = nullptr, *attn_ = nullptr, *act_ = nullptr, *tail_ = nullptr;
+  uint32_t *argmax_ = nullptr;
+  size_t partial_floats_ = 0, dscratch_floats_ = 0;
+
+  // batch metadata: one u32 array on the device, filled from a pinned mirror
+  uint32_t *d_meta_ = nullptr, *h_meta_ = nullptr;
+  size_t meta_cap_ = 0;
+  struct Meta {
+    uint32_t rows = 0, seqs = 0, max_position = 0;
+    bool decode = false, zero_count = false;
+    size_t tokens = 0, positions = 0, slot_block = 0, slot_slot = 0, seq_of_row = 0, last_rows = 0,
+           offsets = 0, tables = 0, total = 0;
+  } meta_;
+
+  void *stage_raw_ = nullptr, *stage_f32_ = nullptr;
+  size_t stage_raw_cap_ = 0, stage_f32_cap_ = 0;
+  std::unique_ptr<NcclCollective> nccl_;
+  uint64_t last_launches_ = 0;
+};
+
+template <typename T>
+int Model<T>::init() {
+  const OrionModelDesc &d = d_;
+  if (d.hidden_size == 0 || d.num_layers == 0 || d.num_attention_heads == 0 ||
+      d.num_kv_heads == 0 || d.head_dim == 0 || d.vocab_size == 0 || d.ffn_dim == 0)
+    return set_error(ORION_ERR_MODEL, "config.json is malformed: a model dimension is zero");
+  if (d.num_attention_heads % d.num_kv_heads != 0)  // config.rs:203-208
+    return set_error(ORION_ERR_MODEL,
+                     "config.json is malformed: num_attention_heads (%u) must be a multiple of "
+                     "num_key_value_heads (%u)",
+                     d.num_attention_heads, d.num_kv_heads);
+  if (d.head_dim % 2 != 0)  // tensor.rs:229-233
+    return set_error(ORION_ERR_MODEL, "config.json is malformed: RoPE requires an even head_dim, got %u",
+                     d.head_dim);
+  if (d.block_size == 0 || d.max_batch_tokens == 0 || d.max_batch_sequences == 0)
+    return set_error(ORION_ERR_INVALID_REQUEST,
+                     "block_size, max_batch_tokens and max_batch_sequences must be non-zero");
+  ORION_TRY(compute_layout(d.num_attention_heads, d.num_kv_heads, d.ffn_dim, d.tp_rank, d.tp_world,
+                           &lay_));
+  lq_ = (uint32_t)lay_.query_heads.len;
+  lkv_ = (uint32_t)lay_.kv_heads.len;
+  lf_ = (uint32_t)lay_.ffn.len;
+
+  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  ORION_CUDA_CHECK("create stream", cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+  ORION_CUDA_CHECK("create event", cudaEventCreate(&ev0_));
+  ORION_CUDA_CHECK("create event", cudaEventCreate(&ev1_));
+
+  const size_t H = d.hidden_size, hd = d.head_dim, V = d.vocab_size;
+  const size_t nqkv = (size_t)(lq_ + 2 * lkv_) * hd;
+  layers_.resize(d.num_layers);
+  for (Layer &L : layers_) {
+    ORION_TRY(alloc(&L.w_qkv, nqkv * H));
+    ORION_TRY(alloc(&L.w_o, H * lq_ * hd));
+    ORION_TRY(alloc(&L.w_gu, (size_t)2 * lf_ * H));
+    ORION_TRY(alloc(&L.w_down, H * lf_));
+    ORION_TRY(alloc(&L.in_norm, H));
+    ORION_TRY(alloc(&L.post_norm, H));
+    if (d.has_qkv_bias) {
+      ORION_TRY(alloc(&L.b_qkv, nqkv));
+      ORION_CUDA_CHECK("clear bias", cudaMemsetAsync(L.b_qkv, 0, nqkv * sizeof(float), stream_));
+    }
+  }
+  ORION_TRY(alloc(&embed_, V * H));
+  ORION_TRY(alloc(&final_norm_, H));
+  if (!d.tied_lm_head) ORION_TRY(alloc(&lm_head_own_, V * H));
+
+  // Zero-initialised arena for this rank's KV heads (attention.rs:53-56).
+  kv_ = KvLayout{d.num_layers, d.num_blocks, lkv_, d.block_size, d.head_dim,
+                 (sizeof(T) == 2 && d.head_dim % 64 == 0) ? 1u : 0u};
+  const size_t arena_elems = kv_.layer_elems() * d.num_layers;
+  ORION_TRY(alloc(&arena_, arena_elems));
+  ORION_CUDA_CHECK("clear arena", cudaMemsetAsync(arena_, 0, arena_elems * sizeof(T), stream_));
+
+  // RopeTable::new (tensor.rs:228-253), same f32 recipe, computed on the host.
+  {
+    const size_t half = hd / 2, n = (size_t)d.max_position_embeddings * half;
+    std::vector<float> c(n ? n : 1), s(n ? n : 1);
+    for (size_t pos = 0; pos < d.max_position_embeddings; ++pos)
+      for (size_t i = 0; i < half; ++i) {
+        const float inv_freq = 1.0f / powf(d.rope_theta, 2.0f * (float)i / (float)hd);
+        const float angle = (float)pos * inv_freq;
+        c[pos * half + i] = cosf(angle);
+        s[pos * half + i] = sinf(angle);
+      }
+    ORION_TRY(alloc(&rope_cos_, n));
+    ORION_TRY(alloc(&rope_sin_, n));
+    ORION_CUDA_CHECK("upload rope", cudaMemcpy(rope_cos_, c.data(), n * sizeof(float), cudaMemcpyHostToDevice));
+    ORION_CUDA_CHECK("upload rope", cudaMemcpy(rope_sin_, s.data(), n * sizeof(float), cudaMemcpyHostToDevice));
+  }
+
+  // Work buffers sized for the largest batch.
+  const size_t Tm = d.max_batch_tokens, Sm = d.max_batch_sequences;
+  constexpr bool kBf16 = DTypeOf<T>::is_bf16;
+  ORION_TRY(alloc(&hidden_, Tm * H));
+  ORION_TRY(alloc(&normed_, Tm * H));
+  ORION_TRY(alloc(&qbuf_, Tm * lq_ * hd));
+  ORION_TRY(alloc(&attn_, Tm * lq_ * hd));
+  ORION_TRY(alloc(&act_, Tm * lf_));
+  ORION_TRY(alloc(&tail_, Sm * H));
+  ORION_TRY(alloc(&logits_, Sm * V));
+  ORION_TRY(alloc(&argmax_, Sm));
+  partial_floats_ = gemm_partial_floats(kBf16, (uint32_t)Tm, (uint32_t)nqkv, (uint32_t)H);
+  partial_floats_ = std::max(partial_floats_, gemm_partial_floats(kBf16, (uint32_t)Tm, (uint32_t)H, (uint32_t)(lq_ * hd)));
+  partial_floats_ = std::max(partial_floats_, gemm_partial_floats(kBf16, (uint32_t)Tm, 2 * lf_, (uint32_t)H));
+  partial_floats_ = std::max(partial_floats_, gemm_partial_floats(kBf16, (uint32_t)Tm, (uint32_t)H, lf_));
+  ORION_TRY(alloc(&partial_, partial_floats_));
+  if (kBf16 && decode_attention_supported(kv_, lq_)) {
+    for (uint32_t r = 1; r <= Sm; ++r) {
+      const uint32_t s = decode_choose_splits(r, lkv_, d.max_position_embeddings, d.block_size, 32);
+      dscratch_floats_ = std::max(dscratch_floats_, decode_scratch_floats(r, lq_, d.head_dim, s));
+    }
+    ORION_TRY(alloc(&dscratch_, dscratch_floats_));
+  }
+
+  if (d.tp_world > 1) {
+    nccl_.reset(new NcclCollective());
+    ORION_TRY(nccl_->init(d.nccl_unique_id, (int)d.tp_rank, (int)d.tp_world));
+  }
+  ORION_CUDA_CHECK("model init", cudaStreamSynchronize(stream_));
+  return ORION_OK;
+}
+
+template <typename T>
+int Model<T>::upload_slice(T *dst_t, float *dst_f, const void *src, int dtype, uint64_t C,
+                           uint64_t r0, uint64_t r1, uint64_t c0, uint64_t c1) {
+  const size_t es = dtype_size(dtype);
+  const uint64_t rows = r1 - r0, cols = c1 - c0;
+  if (rows == 0 || cols == 0) return ORION_OK;
+  const bool direct = dst_t ? (dtype == DTypeOf<T>::value) : (dtype == ORION_DTYPE_F32);
+  const size_t row_bytes = cols * es;
+  uint64_t chunk_rows = std::max<uint64_t>(1, (64ull << 20) / std::max<size_t>(row_bytes, 1));
+  for (uint64_t r = 0; r < rows; r += chunk_rows) {
+    const uint64_t nr = std::min(chunk_rows, rows - r);
+    const uint8_t *s = static_cast<const uint8_t *>(src) + ((r0 + r) * C + c0) * es;
+    const size_t n = nr * cols;
+    void *direct_dst = dst_t ? static_cast<void *>(dst_t + r * cols) : static_cast<void *>(dst_f + r * cols);
+    if (direct) {
+      ORION_CUDA_CHECK("upload tensor", cudaMemcpy2DAsync(direct_dst, row_bytes, s, C * es, row_bytes, nr,
+                                                          cudaMemcpyHostToDevice, stream_));
+      ORION_CUDA_CHECK("upload tensor", cudaStreamSynchronize(stream_));
+      continue;
+    }
+    ORION_TRY(ensure_stage(&stage_raw_, &stage_raw_cap_, n * es));
+    ORION_CUDA_CHECK("upload tensor", cudaMemcpy2DAsync(stage_raw_, row_bytes, s, C * es, row_bytes, nr,
+                                                        cudaMemcpyHostToDevice, stream_));
+    // widen to f32 unless the source already is
+    const float *as_f32 = nullptr;
+    if (dtype == ORION_DTYPE_F32) {
+      as_f32 = static_cast<const float *>(stage_raw_);
+    } else {
+      float *wide = nullptr;
+      if (dst_f) {
+        wide = dst_f + r * cols;
+      } else {
+        ORION_TRY(ensure_stage(&stage_f32_, &stage_f32_cap_, n * sizeof(float)));
+        wide = static_cast<float *>(stage_f32_);
+      }
+      if (dtype == ORION_DTYPE_BF16)
+        ORION_TRY(launch_convert_to_f32<bf16>(static_cast<const bf16 *>(stage_raw_), wide, n, stream_));
+      else
+        ORION_TRY(launch_f16_to_f32(static_cast<const uint16_t *>(stage_raw_), wide, n, stream_));
+      as_f32 = wide;
+    }
+    if (dst_t) ORION_TRY(launch_convert_from_f32<T>(as_f32, dst_t + r * cols, n, stream_));
+    ORION_CUDA_CHECK("upload tensor", cudaStreamSynchronize(stream_));
+  }
+  return ORION_OK;
+}
+
+template <typename T>
+int Model<T>::load_tensor(const char *name, int dtype, const uint64_t *shape, int ndim,
+                          const void *data) {
+  const OrionModelDesc &d = d_;
+  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  if (dtype_size(dtype) == 0 || dtype == ORION_DTYPE_I8 || dtype == ORION_DTYPE_I4)
+    return set_error(ORION_ERR_MODEL, "unsupported dtype %d (tensor `%s`)", dtype, name);  // loader.rs:89-93
+  if (!data || ndim < 1 || ndim > 2) return set_error(ORION_ERR_MODEL, "tensor `%s` has rank %d", name, ndim);
+  const uint64_t R = ndim == 2 ? shape[0] : 1, C = ndim == 2 ? shape[1] : shape[0];
+  const uint64_t H = d.hidden_size, hd = d.head_dim, V = d.vocab_size, F = d.ffn_dim;
+  const uint64_t qd = (uint64_t)d.num_attention_heads * hd, kvd = (uint64_t)d.num_kv_heads * hd;
+  auto expect = [&](uint64_t er, uint64_t ec) -> int {
+    if (R != er || C != ec)
+      return set_error(ORION_ERR_MODEL, "tensor `%s` has shape [%llu, %llu], expected [%llu, %llu]", name,
+                       (unsigned long long)R, (unsigned long long)C, (unsigned long long)er,
+                       (unsigned long long)ec);
+    return ORION_OK;
+  };
+  const uint64_t q0 = lay_.query_heads.start * hd, q1 = q0 + lq_ * hd;
+  const uint64_t k0 = lay_.kv_heads.start * hd, k1 = k0 + lkv_ * hd;
+  const uint64_t f0 = lay_.ffn.start, f1 = f0 + lf_;
+  finalized_ = false;
+
+  if (!strcmp(name, "model.embed_tokens.weight")) {
+    ORION_TRY(expect(V, H));
+    got_embed_ = true;
+    return upload_slice(embed_, nullptr, data, dtype, C, 0, V, 0, H);
+  }
+  if (!strcmp(name, "model.norm.weight")) {
+    ORION_TRY(expect(1, H));
+    got_final_norm_ = true;
+    return upload_slice(nullptr, final_norm_, data, dtype, C, 0, 1, 0, H);
+  }
+  if (!strcmp(name, "lm_head.weight")) {
+    if (d.tied_lm_head) return ORION_OK;  // transformer.rs:108-110
+    ORION_TRY(expect(V, H));
+    got_head_ = true;
+    return upload_slice(lm_head_own_, nullptr, data, dtype, C, 0, V, 0, H);
+  }
+  unsigned li = 0;
+  char rest[96];
+  if (sscanf(name, "model.layers.%u.%95s", &li, rest) == 2 && li < d.num_layers) {
+    Layer &L = layers_[li];
+    const size_t lqd = (size_t)lq_ * hd, lkvd = (size_t)lkv_ * hd;
+    if (!strcmp(rest, "input_layernorm.weight")) {
+      ORION_TRY(expect(1, H));
+      L.got |= kGotInNorm;
+      return upload_slice(nullptr, L.in_norm, data, dtype, C, 0, 1, 0, H);
+    }
+    if (!strcmp(rest, "post_attention_layernorm.weight")) {
+      ORION_TRY(expect(1, H));
+      L.got |= kGotPostNorm;
+      return upload_slice(nullptr, L.post_norm, data, dtype, C, 0, 1, 0, H);
+    }
+    if (!strcmp(rest, "self_attn.q_proj.weight")) {  // column-parallel: this rank's query heads
+      ORION_TRY(expect(qd, H));
+      L.got |= kGotQ;
+      return upload_slice(L.w_qkv, nullptr, data, dtype, C, q0, q1, 0, H);
+    }
+    if (!strcmp(rest, "self_attn.k_proj.weight")) {
+      ORION_TRY(expect(kvd, H));
+      L.got |= kGotK;
+      return upload_slice(L.w_qkv + lqd * H, nullptr, data, dtype, C, k0, k1, 0, H);
+    }
+    if (!strcmp(rest, "self_attn.v_proj.weight")) {
+      ORION_TRY(expect(kvd, H));
+      L.got |= kGotV;
+      return upload_slice(L.w_qkv + (lqd + lkvd) * H, nullptr, data, dtype, C, k0, k1, 0, H);
+    }
+    if (!strcmp(rest, "self_attn.o_proj.weight")) {  // row-parallel: columns of this rank's heads
+      ORION_TRY(expect(H, qd));
+      L.got |= kGotO;
+      return upload_slice(L.w_o, nullptr, data, dtype, C, 0, H, q0, q1);
+    }
+    if (!strcmp(rest, "mlp.gate_proj.weight")) {
+      ORION_TRY(expect(F, H));
+      L.got |= kGotGate;
+      return upload_slice(L.w_gu, nullptr, data, dtype, C, f0, f1, 0, H);
+    }
+    if (!strcmp(rest, "mlp.up_proj.weight")) {
+      ORION_TRY(expect(F, H));
+      L.got |= kGotUp;
+      return upload_slice(L.w_gu + (size_t)lf_ * H, nullptr, data, dtype, C, f0, f1, 0, H);
+    }
+    if (!strcmp(rest, "mlp.down_proj.weight")) {
+      ORION_TRY(expect(H, F));
+      L.got |= kGotDown;
+      return upload_slice(L.w_down, nullptr, data, dtype, C, 0, H, f0, f1);
+    }
+    const bool is_bias = !strcmp(rest, "self_attn.q_proj.bias") || !strcmp(rest, "self_attn.k_proj.bias") ||
+                         !strcmp(rest, "self_attn.v_proj.bias");
+    if (is_bias) {
+      if (!d.has_qkv_bias) return ORION_OK;  // transformer.rs:84-86: Llama never reads biases
+      const char which = rest[10];
+      if (which == 'q') {
+        ORION_TRY(expect(1, qd));
+        return upload_slice(nullptr, L.b_qkv, data, dtype, C, 0, 1, q0, q1);
+      }
+      ORION_TRY(expect(1, kvd));
+      float *dst = L.b_qkv + lqd + (which == 'v' ? lkvd : 0);
+      return upload_slice(nullptr, dst, data, dtype, C, 0, 1, k0, k1);
+    }
+  }
+  return set_error(ORION_ERR_MODEL, "tensor `%s` is not part of the Llama/Qwen2 layout", name);
+}
+
+template <typename T>
+int Model<T>::init_random(uint64_t seed, float std) {
+  // N(0, std) matrices, RMSNorm weights 1.0, zero biases. Values are drawn on
+  // the device; they depend on (seed, tensor index) only.
+  const OrionModelDesc &d = d_;
+  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  const size_t H = d.hidden_size, hd = d.head_dim, V = d.vocab_size;
+  uint64_t tensor = 0;
+  auto fill = [&](T *p, size_t n) -> int {
+    ORION_TRY(ensure_stage(&stage_f32_, &stage_f32_cap_, std::min<size_t>(n, 64u << 20) * sizeof(float)));
+    for (size_t off = 0; off < n; off += (64u << 20)) {
+      const size_t m = std::min<size_t>(64u << 20, n - off);
+      float *tmp = static_cast<float *>(stage_f32_);
+      ORION_TRY(launch_fill_normal<float>(tmp, m, seed * 0x9E3779B97F4A7C15ull + (++tensor), stream_));
+      ORION_TRY(launch_scale_convert<T>(tmp, p + off, m, std, stream_));  // N(0,1) -> N(0,std), narrowed to T
+    }
+    return ORION_OK;
+  };
+  std::vector<float> ones(H, 1.0f);
+  auto set_ones = [&](float *p) -> int {
+    ORION_CUDA_CHECK("init norm", cudaMemcpyAsync(p, ones.data(), H * sizeof(float), cudaMemcpyHostToDevice, stream_));
+    return ORION_OK;
+  };
+  ORION_TRY(fill(embed_, V * H));
+  if (lm_head_own_) ORION_TRY(fill(lm_head_own_, V * H));
+  ORION_TRY(set_ones(final_norm_));
+  for (Layer &L : layers_) {
+    ORION_TRY(fill(L.w_qkv, (size_t)(lq_ + 2 * lkv_) * hd * H));
+    ORION_TRY(fill(L.w_o, H * lq_ * hd));
+    ORION_TRY(fill(L.w_gu, (size_t)2 * lf_ * H));
+    ORION_TRY(fill(L.w_down, H * lf_));
+    ORION_TRY(set_ones(L.in_norm));
+    ORION_TRY(set_ones(L.post_norm));
+    L.got = kGotAllLayer;
+  }
+  got_embed_ = got_final_norm_ = true;
+  got_head_ = lm_head_own_ != nullptr;
+  ORION_CUDA_CHECK("init_random", cudaStreamSynchronize(stream_));
+  return finalize();
+}
+
+template <typename T>
+int Model<T>::finalize() {
+  // ModelWeights::load fails on the first missing tensor (transformer.rs:73-118).
+  if (!got_embed_) return set_error(ORION_ERR_MODEL, "missing tensor `model.embed_tokens.weight`");
+  if (!got_final_norm_) return set_error(ORION_ERR_MODEL, "missing tensor `model.norm.weight`");
+  static const char *names[] = {"input_layernorm.weight", "post_attention_layernorm.weight",
+                                "self_attn.q_proj.weight", "self_attn.k_proj.weight",
+                                "self_attn.v_proj.weight", "self_attn.o_proj.weight",
+                                "mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight"};
+  for (size_t i = 0; i < layers_.size(); ++i)
+    for (int b = 0; b < 9; ++b)
+      if (!(layers_[i].got & (1u << b)))
+        return set_error(ORION_ERR_MODEL, "missing tensor `model.layers.%zu.%s`", i, names[b]);
+  // transformer.rs:108-112: the head falls back to the embedding when tied or absent.
+  lm_head_ = (d_.tied_lm_head || !got_head_) ? embed_ : lm_head_own_;
+  finalized_ = true;
+  return ORION_OK;
+}
+
+template <typename T>
+int Model<T>::tp_reduce(uint32_t *splits, size_t slab) {
+  if (!nccl_) return ORION_OK;
+  // Row-parallel projection: sum this rank's split-K slabs, then the one
+  // all-reduce of the half-layer (orion-distributed/src/lib.rs:317-319).
+  if (*splits > 1) ORION_TRY(launch_finish_linear(partial_, *splits, slab, nullptr, partial_, 1, (uint32_t)slab, stream_));
+  *splits = 1;
+  return nccl_->all_reduce_sum(partial_, slab, stream_);
+}
+
+template <typename T>
+int Model<T>::run_step(bool want_argmax) {
+  const OrionModelDesc &d = d_;
+  constexpr bool kBf16 = DTypeOf<T>::is_bf16;
+  const uint32_t Tn = meta_.rows, S = meta_.seqs, H = d.hidden_size, hd = d.head_dim;
+  const uint32_t nqkv = (lq_ + 2 * lkv_) * hd, qd = lq_ * hd;
+  const uint32_t *m = d_meta_;
+  const uint32_t *tokens = m + meta_.tokens, *positions = m + meta_.positions;
+  const uint32_t *slot_block = m + meta_.slot_block, *slot_slot = m + meta_.slot_slot;
+  const uint32_t *last_rows = m + meta_.last_rows;
+  AttnBatch ab{positions, m + meta_.seq_of_row, m + meta_.tables, m + meta_.offsets, Tn, meta_.max_position};
+  const bool tuned_decode = kBf16 && meta_.decode && decode_attention_supported(kv_, lq_);
+  const uint32_t dsplits = tuned_decode ? decode_choose_splits(Tn, lkv_, meta_.max_position, d.block_size, 32) : 1;
+
+  ORION_TRY(launch_embed_rmsnorm<T>(embed_, tokens, layers_[0].in_norm, d.rms_norm_eps, hidden_, normed_, Tn, H, stream_));
+  for (uint32_t l = 0; l < d.num_layers; ++l) {
+    const Layer &L = layers_[l];
+    GemmPlan p = gemm_plan(kBf16, Tn, nqkv, H, H, H);
+    ORION_TRY(launch_gemm<T>(normed_, H, L.w_qkv, H, partial_, Tn, nqkv, H, p, stream_));
+    ORION_TRY(launch_rope_kvwrite<T>(partial_, p.splits, (size_t)Tn * nqkv, L.b_qkv, positions, slot_block,
+                                     slot_slot, rope_cos_, rope_sin_, qbuf_, arena_, kv_, l, Tn, lq_, stream_));
+    if (tuned_decode) {
+      if constexpr (kBf16) {
+        DecodeScratch sc{dscratch_, dscratch_ + (size_t)Tn * lq_ * dsplits * hd, dsplits};
+        ORION_TRY(launch_paged_attention_decode(qbuf_, arena_, kv_, l, ab, lq_, dsplits, sc, attn_, stream_));
+      }
+    } else {
+      ORION_TRY(launch_paged_attention_generic<T>(qbuf_, arena_, kv_, l, ab, lq_, attn_, stream_));
+    }
+    p = gemm_plan(kBf16, Tn, H, qd, qd, qd);
+    ORION_TRY(launch_gemm<T>(attn_, qd, L.w_o, qd, partial_, Tn, H, qd, p, stream_));
+    ORION_TRY(tp_reduce(&p.splits, (size_t)Tn * H));
+    ORION_TRY(launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, L.post_norm, d.rms_norm_eps,
+                                         normed_, nullptr, Tn, H, stream_));
+    p = gemm_plan(kBf16, Tn, 2 * lf_, H, H, H);
+    ORION_TRY(launch_gemm<T>(normed_, H, L.w_gu, H, partial_, Tn, 2 * lf_, H, p, stream_));
+    ORION_TRY(launch_swiglu<T>(partial_, p.splits, (size_t)Tn * 2 * lf_, act_, Tn, lf_, stream_));
+    p = gemm_plan(kBf16, Tn, H, lf_, lf_, lf_);
+    ORION_TRY(launch_gemm<T>(act_, lf_, L.w_down, lf_, partial_, Tn, H, lf_, p, stream_));
+    ORION_TRY(tp_reduce(&p.splits, (size_t)Tn * H));
+    if (l + 1 < d.num_layers) {
+      ORION_TRY(launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, layers_[l + 1].in_norm,
+                                           d.rms_norm_eps, normed_, nullptr, Tn, H, stream_));
+    } else if (!meta_.zero_count) {
+      // Final norm over the last row of every sequence (transformer.rs:401-428;
+      // the norm is row-wise, so gathering first gives the same rows).
+      ORION_TRY(launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, final_norm_, d.rms_norm_eps,
+                                           tail_, last_rows, S, H, stream_));
+    }
+  }
+  if (meta_.zero_count) return ORION_OK;
+  GemmPlan hp = gemm_plan(kBf16, S, d.vocab_size, H, H, H);
+  hp.splits = 1;  // logits are written in place, row-major [S][V]
+  ORION_TRY(launch_gemm<T>(tail_, H, lm_head_, H, logits_, S, d.vocab_size, H, hp, stream_));
+  if (want_argmax) ORION_TRY(launch_argmax(logits_, S, d.vocab_size, argmax_, stream_));
+  return ORION_OK;
+}
+
+template <typename T>
+int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_capacity,
+                      uint32_t *token_ids_out) {
+  const OrionModelDesc &d = d_;
+  if (!finalized_) return set_error(ORION_ERR_MODEL, "model weights are not finalized");
+  // ForwardBatch::validate (orion-core/src/traits.rs:232-261)
+  const uint64_t S = b.num_sequences;
+  if (b.num_slot_token_counts != S || b.num_context_lens != S || b.num_block_tables != S)
+    return set_error(ORION_ERR_INTERNAL,
+                     "ForwardBatch arrays disagree: %llu sequence ids, %llu token counts, %llu context "
+                     "lens, %llu block tables",
+                     (unsigned long long)S, (unsigned long long)b.num_slot_token_counts,
+                     (unsigned long long)b.num_context_lens, (unsigned long long)b.num_block_tables);
+  if (b.num_positions != b.num_tokens)
+    return set_error(ORION_ERR_INTERNAL, "ForwardBatch has %llu tokens but %llu positions",
+                     (unsigned long long)b.num_tokens, (unsigned long long)b.num_positions);
+  uint64_t summed = 0;
+  for (uint64_t s = 0; s < S; ++s) summed += b.slot_token_counts[s];
+  if (summed != b.num_tokens)
+    return set_error(ORION_ERR_INTERNAL,
+                     "ForwardBatch slot token counts sum to %llu but there are %llu tokens",
+                     (unsigned long long)summed, (unsigned long long)b.num_tokens);
+  last_launches_ = 0;
+  if (b.num_tokens == 0) return ORION_OK;  // transformer.rs:361-367: empty batch, empty output
+  const uint64_t Tn = b.num_tokens;
+  if (Tn > d.max_batch_tokens || S > d.max_batch_sequences)
+    return set_error(ORION_ERR_INVALID_REQUEST,
+                     "batch of %llu tokens / %llu sequences exceeds the configured capacity (%u / %u)",
+                     (unsigned long long)Tn, (unsigned long long)S, d.max_batch_tokens,
+                     d.max_batch_sequences);
+  if (logits_out && logits_capacity < S * (uint64_t)d.vocab_size)
+    return set_error(ORION_ERR_INVALID_REQUEST, "logits buffer holds %llu floats, %llu needed",
+                     (unsigned long long)logits_capacity, (unsigned long long)(S * (uint64_t)d.vocab_size));
+
+  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  const uint64_t table_entries = b.block_table_offsets[S];
+  Meta mt;
+  mt.rows = (uint32_t)Tn;
+  mt.seqs = (uint32_t)S;
+  mt.tokens = 0;
+  mt.positions = Tn;
+  mt.slot_block = 2 * Tn;
+  mt.slot_slot = 3 * Tn;
+  mt.seq_of_row = 4 * Tn;
+  mt.last_rows = 5 * Tn;
+  mt.offsets = 5 * Tn + S;
+  mt.tables = 5 * Tn + 2 * S + 1;
+  mt.total = mt.tables + table_entries;
+  if (table_entries > UINT32_MAX) return set_error(ORION_ERR_INVALID_REQUEST, "block tables too large");
+  if (mt.total > meta_cap_) {
+    const size_t cap = mt.total * 2 + 1024;
+    if (h_meta_) cudaFreeHost(h_meta_);
+    h_meta_ = nullptr;
+    meta_cap_ = 0;
+    ORION_CUDA_CHECK("allocate batch mirror", cudaMallocHost(reinterpret_cast<void **>(&h_meta_), cap * sizeof(uint32_t)));
+    ORION_TRY(alloc(&d_meta_, cap));  // the previous device array stays owned until destruction
+    meta_cap_ = cap;
+  }
+  uint32_t *h = h_meta_;
+  // seq_of_row and slot resolution BEFORE any compute or KV write (transformer.rs:371-387).
+  {
+    uint64_t row = 0;
+    for (uint64_t s = 0; s < S; ++s) {
+      for (uint64_t c = 0; c < b.slot_token_counts[s]; ++c) h[mt.seq_of_row + row++] = (uint32_t)s;
+      if (b.slot_token_counts[s] == 0) mt.zero_count = true;
+    }
+  }
+  const uint32_t B = d.block_size;
+  bool all_single = true;
+  for (uint64_t s = 0; s < S; ++s) all_single &= (b.slot_token_counts[s] == 1);
+  for (uint64_t row = 0; row < Tn; ++row) {
+    const uint32_t seq = h[mt.seq_of_row + row], pos = b.positions[row];
+    const uint64_t t0 = b.block_table_offsets[seq], tlen = b.block_table_offsets[seq + 1] - t0;
+    const uint64_t logical = pos / B;  // locate, attention.rs:182-186
+    if (logical >= tlen)
+      return set_error(ORION_ERR_INTERNAL, "position %u has no block in the table for sequence %u", pos, seq);
+    h[mt.slot_block + row] = b.block_tables_flat[t0 + logical];
+    h[mt.slot_slot + row] = pos % B;
+    mt.max_position = std::max(mt.max_position, pos);
+  }
+  for (uint64_t row = 0; row < Tn; ++row)  // embed, transformer.rs:211-217
+    if (b.tokens[row] >= d.vocab_size)
+      return set_error(ORION_ERR_INTERNAL, "token id %u is outside the vocabulary of %u", b.tokens[row],
+                       d.vocab_size);
+  for (uint64_t row = 0; row < Tn; ++row)  // RoPE range, transformer.rs:255-262
+    if (b.positions[row] >= d.max_position_embeddings)
+      return set_error(ORION_ERR_INTERNAL, "position %u exceeds the RoPE table (%u entries)", b.positions[row],
+                       d.max_position_embeddings);
+  // Every block a query row will read must exist in the arena (attention.rs:150-155);
+  // checked here so that no kernel ever sees an out-of-range block id.
+  for (uint64_t row = 0; row < Tn; ++row) {
+    const uint32_t seq = h[mt.seq_of_row + row];
+    const uint64_t t0 = b.block_table_offsets[seq];
+    const uint64_t used = (uint64_t)b.positions[row] / B + 1;
+    for (uint64_t e = 0; e < used; ++e)
+      if (b.block_tables_flat[t0 + e] >= d.num_blocks)
+        return set_error(ORION_ERR_INTERNAL, "block %u out of range (have %u)", b.block_tables_flat[t0 + e],
+                         d.num_blocks);
+  }
+  std::memcpy(h + mt.tokens, b.tokens, Tn * sizeof(uint32_t));
+  std::memcpy(h + mt.positions, b.positions, Tn * sizeof(uint32_t));
+  {
+    uint64_t cursor = 0;
+    for (uint64_t s = 0; s < S; ++s) {  // transformer.rs:410-420
+      cursor += b.slot_token_counts[s];
+      h[mt.last_rows + s] = (uint32_t)(cursor ? cursor - 1 : 0);
+      h[mt.offsets + s] = (uint32_t)b.block_table_offsets[s];
+    }
+    h[mt.offsets + S] = (uint32_t)table_entries;
+  }
+  if (table_entries) std::memcpy(h + mt.tables, b.block_tables_flat, table_entries * sizeof(uint32_t));
+  mt.decode = all_single;
+  meta_ = mt;
+
+  g_launch_count = 0;
+  ORION_CUDA_CHECK("upload batch", cudaMemcpyAsync(d_meta_, h, mt.total * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));
+  ORION_TRY(run_step(token_ids_out != nullptr));
+  last_launches_ = g_launch_count;
+  if (mt.zero_count) {
+    cudaStreamSynchronize(stream_);
+    // transformer.rs:413-417: detected after the layers ran, so KV slots were written.
+    return set_error(ORION_ERR_INTERNAL, "a scheduled sequence contributed zero tokens");
+  }
+  if (d.tp_world > 1 && d.tp_rank != 0) {  // only the leader returns logits (Rank::is_leader)
+    ORION_CUDA_CHECK("forward", cudaStreamSynchronize(stream_));
+  } else {
+    if (logits_out)
+      ORION_CUDA_CHECK("download logits", cudaMemcpyAsync(logits_out, logits_, S * (size_t)d.vocab_size * sizeof(float),
+                                                          cudaMemcpyDeviceToHost, stream_));
+    if (token_ids_out)
+      ORION_CUDA_CHECK("download tokens", cudaMemcpyAsync(token_ids_out, argmax_, S * sizeof(uint32_t),
+                                                          cudaMemcpyDeviceToHost, stream_));
+    ORION_CUDA_CHECK("forward", cudaStreamSynchronize(stream_));
+  }
+  uint32_t code = 0;
+  if (DTypeOf<T>::is_bf16) {
+    ORION_TRY(gemm_tc_poll_error(&code));
+    if (code) return set_error(ORION_ERR_BACKEND, "backend cuda failed at gemm: a bounded pipeline wait ran out (code %u)", code);
+    ORION_TRY(decode_poll_error(&code));
+    if (code) return set_error(ORION_ERR_BACKEND, "backend cuda failed at attention: a bounded pipeline wait ran out (code %u)", code);
+  }
+  return ORION_OK;
+}
+
+template <typename T>
+int Model<T>::replay(int iterations, float *elapsed_ms) {
+  if (meta_.rows == 0 || meta_.zero_count)
+    return set_error(ORION_ERR_INVALID_REQUEST, "replay needs a preceding successful forward");
+  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  ORION_CUDA_CHECK("replay", cudaStreamSynchronize(stream_));
+  ORION_CUDA_CHECK("replay", cudaEventRecord(ev0_, stream_));
+  for (int i = 0; i < iterations; ++i) {
+    g_launch_count = 0;
+    ORION_TRY(run_step(false));
+    last_launches_ = g_launch_count;
+  }
+  ORION_CUDA_CHECK("replay", cudaEventRecord(ev1_, stream_));
+  ORION_CUDA_CHECK("replay", cudaEventSynchronize(ev1_));
+  float ms = 0.f;
+  ORION_CUDA_CHECK("replay", cudaEventElapsedTime(&ms, ev0_, ev1_));
+  if (elapsed_ms) *elapsed_ms = ms;
+  return ORION_OK;
+}
+
+template <typename T>
+int Model<T>::read_kv(float *out, uint64_t capacity) {
+  const size_t total = kv_.layer_elems() * d_.num_layers;
+  if (capacity < total)
+    return set_error(ORION_ERR_INVALID_REQUEST, "KV read-back buffer holds %llu floats, %zu needed",
+                     (unsigned long long)capacity, total);
+  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  float *tmp = nullptr;
+  ORION_CUDA_CHECK("allocate", cudaMalloc(&tmp, (total ? total : 1) * sizeof(float)));
+  int rc = launch_arena_to_reference_order<T>(arena_, kv_, tmp, stream_);
+  if (rc == ORION_OK) {
+    cudaError_t e = cudaMemcpyAsync(out, tmp, total * sizeof(float), cudaMemcpyDeviceToHost, stream_);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream_);
+    if (e != cudaSuccess) rc = set_error(ORION_ERR_BACKEND, "backend cuda failed at read_kv: %s", cudaGetErrorString(e));
+  }
+  cudaFree(tmp);
+  return rc;
+}
+
+}  // namespace
+
+int create_model(OrionBackend *backend, const OrionModelDesc *desc, ModelBase **out) {
+  *out = nullptr;
+  if (desc->compute_dtype == ORION_DTYPE_F32) {
+    auto *m = new Model<float>(backend, *desc);
+    int rc = m->init();
+    if (rc != ORION_OK) { delete m; return rc; }
+    *out = m;
+    return ORION_OK;
+  }
+  if (desc->compute_dtype == ORION_DTYPE_BF16) {
+    auto *m = new Model<bf16>(backend, *desc);
+    int rc = m->init();
+    if (rc != ORION_OK) { delete m; return rc; }
+    *out = m;
+    return ORION_OK;
+  }
+  return set_error(ORION_ERR_MODEL, "unsupported compute dtype %u (f32 and bf16 are implemented)", desc->compute_dtype);
+}
+
+}  // namespace orion

@@ -1,0 +1,381 @@
+"""Parity of the CUDA path against the CPU oracle, through the C ABI (B200 only).
+
+Tolerances: integer / index results are bit-exact; the f32 build must match logits
+within 1e-3 relative error; the bf16 build within 2e-2 max-abs after softmax with
+identical greedy tokens.
+"""
+import numpy as np
+import pytest
+
+from conftest import SMALL_META, TINY_SIN_META, random_tensors, tiny_sin_tensors
+from drivers import C1_META, GreedyDriver, c1_tensors, softmax_rows
+
+pytestmark = pytest.mark.gpu
+
+F32_REL = 1e-3      # f32 build: logits relative error
+BF16_SOFTMAX = 2e-2  # bf16 build: max-abs after softmax
+
+
+@pytest.fixture(scope="module")
+def backend(pkg):
+    return pkg.CudaBackend(0)
+
+
+def rel_err(got, exp):
+    return float(np.max(np.abs(got - exp)) / max(1e-12, float(np.max(np.abs(exp)))))
+
+
+# ---- Backend trait -------------------------------------------------------------
+
+def test_backend_reports_the_device(pkg, backend):
+    assert backend.name() == "cuda"
+    assert str(backend.device()) == "cuda:0" and not backend.device().is_cpu()
+    assert backend.total_memory() > 100 * 2 ** 30
+    assert 0 < backend.available_memory() <= backend.total_memory()
+    backend.synchronize()
+    assert backend.supports_dtype(pkg.DType.F32) and backend.supports_dtype(pkg.DType.BF16)
+    assert not backend.supports_dtype(pkg.DType.I4)
+    with pytest.raises(pkg.CudaUnavailable):
+        pkg.CudaBackend(pkg.device_count())
+
+
+# ---- op-level parity: tensor.rs ---------------------------------------------------
+
+def test_linear_f32_is_bit_exact(pkg, backend, oracle, kats):
+    for k in kats["linear"]:
+        out = pkg.ops.linear(backend, np.array(k["x"]), np.array(k["w"]), k["bias"])
+        assert np.array_equal(out, np.array(k["out"], np.float32)), k["cite"]
+    rng = np.random.default_rng(0)
+    for rows, n, kk in ((1, 7, 5), (9, 130, 257), (70, 65, 688), (33, 1024, 256)):
+        x = rng.standard_normal((rows, kk)).astype(np.float32)
+        w = rng.standard_normal((n, kk)).astype(np.float32)
+        b = rng.standard_normal(n).astype(np.float32)
+        assert np.array_equal(pkg.ops.linear(backend, x, w, b), oracle.linear(x, w, b))
+    for k in kats["linear_errors"]:
+        bias = None if k["bias_len"] is None else np.ones(k["bias_len"])
+        with pytest.raises(pkg.InternalError):
+            pkg.ops.linear(backend, np.ones(k["x_shape"]), np.ones(k["w_shape"]), bias)
+
+
+@pytest.mark.parametrize("rows,n,k", [(1, 128, 64), (3, 256, 4096), (16, 384, 512), (17, 1000, 1024),
+                                      (64, 6144, 4096), (64, 4096, 14336), (100, 512, 256),
+                                      (129, 640, 1024), (300, 1152, 2048), (8, 200, 72)])
+def test_linear_bf16_tensor_core_matches_the_oracle(pkg, backend, oracle, rows, n, k):
+    rng = np.random.default_rng(rows * 7 + n)
+    x = oracle.round_to_bf16(rng.standard_normal((rows, k)).astype(np.float32))
+    w = oracle.round_to_bf16((rng.standard_normal((n, k)) * 0.05).astype(np.float32))
+    b = rng.standard_normal(n).astype(np.float32)
+    oracle.set_threads(8)
+    exp = oracle.linear(x, w, b)
+    oracle.set_threads(1)
+    got = pkg.ops.linear(backend, x, w, b, dtype=pkg.DType.BF16)
+    # same bf16 operands, f32 accumulation in a different order
+    assert rel_err(got, exp) < 2e-5
+
+
+def test_rms_norm_swiglu_rope(pkg, backend, oracle, kats):
+    for k in kats["rms_norm"]:
+        out = pkg.ops.rms_norm(backend, np.array(k["x"]), k["w"], k["eps"])
+        assert np.allclose(out, k["out"], atol=k["tol"]), k["cite"]
+    rng = np.random.default_rng(1)
+    for cols in (4, 256, 4096, 8192):
+        x = rng.standard_normal((5, cols)).astype(np.float32) * 3
+        w = rng.standard_normal(cols).astype(np.float32)
+        rep = pkg.validate("rms_norm", oracle.rms_norm(x, w, 1e-5), pkg.ops.rms_norm(backend, x, w, 1e-5),
+                           pkg.Tolerance.F32)
+        assert rep.passed(), rep.render()
+        xb = oracle.round_to_bf16(x)
+        rep = pkg.validate("rms_norm_bf16", oracle.rms_norm(xb, w, 1e-5),
+                           pkg.ops.rms_norm(backend, xb, w, 1e-5, dtype=pkg.DType.BF16), pkg.Tolerance.F16)
+        assert rep.passed(), rep.render()
+    assert np.all(np.isfinite(pkg.ops.rms_norm(backend, np.zeros((1, 2)), [1, 1], 1e-5)))
+    with pytest.raises(pkg.InternalError):
+        pkg.ops.rms_norm(backend, np.ones((1, 4)), [1.0, 1.0], 1e-5)
+
+    k = kats["swiglu"]
+    assert np.allclose(pkg.ops.swiglu(backend, np.array(k["gate"]), np.array(k["up"])), k["out"], atol=k["tol"])
+    g = rng.standard_normal((7, 688)).astype(np.float32) * 4
+    u = rng.standard_normal((7, 688)).astype(np.float32)
+    rep = pkg.validate("swiglu", oracle.swiglu(g, u), pkg.ops.swiglu(backend, g, u), pkg.Tolerance.F32)
+    assert rep.passed(), rep.render()
+    rep = pkg.validate("swiglu_bf16", oracle.swiglu(g, u), pkg.ops.swiglu(backend, g, u, dtype=pkg.DType.BF16),
+                       pkg.Tolerance.F16)
+    assert rep.passed(), rep.render()
+    with pytest.raises(pkg.InternalError):
+        pkg.ops.swiglu(backend, np.zeros((1, 2)), np.zeros((1, 3)))
+
+    # RoPE: rotate-half pairing (tensor.rs:478-493) and table parity
+    cos, sin = oracle.rope_table(64, 300, 10000.0)
+    x = rng.standard_normal((6, 3, 64)).astype(np.float32)
+    pos = np.array([0, 1, 17, 255, 299, 128])
+    exp = np.stack([[oracle.apply_rope(x[r, h], cos[pos[r]], sin[pos[r]]) for h in range(3)] for r in range(6)])
+    got = pkg.ops.rope(backend, x, pos, 300, 10000.0)
+    assert np.array_equal(got, exp), "same table, same unfused arithmetic: bit-exact"
+    assert np.array_equal(got[0], x[0]), "position 0 is the identity"
+    with pytest.raises(pkg.InternalError):
+        pkg.ops.rope(backend, x, [0, 1, 2, 3, 4, 300], 300, 10000.0)
+
+
+def test_argmax_is_bit_exact(pkg, backend, oracle, kats):
+    for k in kats["argmax"]:
+        got = int(pkg.ops.argmax(backend, [float(v) for v in k["logits"]])[0])
+        assert (None if got == 0xFFFFFFFF else got) == k["index"], k["cite"]
+    rng = np.random.default_rng(2)
+    logits = rng.standard_normal((9, 128256)).astype(np.float32)
+    logits[3, 100] = logits[3, 90000] = 99.0   # tie -> lowest index
+    logits[4, :] = 1.0
+    exp = [oracle.argmax(r) for r in logits]
+    assert pkg.ops.argmax(backend, logits).tolist() == exp
+
+
+# ---- op-level parity: attention.rs ----------------------------------------------
+
+def _store_to_array(oracle, k):
+    s = oracle.KvStore(*k["store"])
+    for layer, block, slot, head, is_v, vec in k.get("writes", []):
+        s.write(layer, block, slot, head, is_v, vec)
+    return s
+
+
+def test_attention_kats(pkg, backend, oracle, kats):
+    for k in kats["attention"]:
+        s = _store_to_array(oracle, k)
+        hq, hd = k["hq"], k["hd"]
+        got = pkg.ops.paged_attention(backend, s.array()[0], np.array(k["query"]).reshape(1, hq, hd),
+                                      [k["query_position"]], [0], [k["table"]])
+        if k.get("exact"):
+            assert got.reshape(-1).tolist() == k["out"], k["cite"]
+        else:
+            assert np.allclose(got.reshape(-1), k["out"], atol=k["tol"]), k["cite"]
+    for k in kats["attention_errors"]:
+        s = oracle.KvStore(*k["store"])
+        if k["hq"] % k["hkv"] == 0:
+            q = np.zeros((1, k["hq"], k["hd"]))
+        else:
+            q = np.zeros((1, k["hq"], k["hd"]))
+        with pytest.raises(pkg.InternalError):
+            pkg.ops.paged_attention(backend, s.array()[0], q, [k["query_position"]], [0], [k["table"]])
+
+
+@pytest.mark.parametrize("dtype_name,hq,hkv,hd,bs", [("F32", 4, 2, 64, 16), ("F32", 6, 3, 20, 8),
+                                                     ("BF16", 4, 2, 64, 16), ("BF16", 32, 8, 128, 16),
+                                                     ("BF16", 28, 4, 128, 16), ("BF16", 8, 8, 128, 16)])
+def test_attention_ragged_batches(pkg, backend, oracle, dtype_name, hq, hkv, hd, bs):
+    """Decode rows and prefill rows through scattered tables; the 128/16 bf16 cases take the
+    tuned decode kernel (one row per sequence), the rest the generic kernel."""
+    dtype = getattr(pkg.DType, dtype_name)
+    rng = np.random.default_rng(hq * 31 + hd)
+    ctxs = [1, 15, 16, 17, 33, 200, 513, 1030]
+    nblocks = sum((c + bs - 1) // bs for c in ctxs) + 5
+    store = oracle.KvStore(1, nblocks, bs, hkv, hd)
+    arr = store.array()
+    arr[...] = rng.standard_normal(arr.shape).astype(np.float32)
+    if dtype == pkg.DType.BF16:
+        arr[...] = oracle.round_to_bf16(arr)
+    perm = rng.permutation(nblocks)
+    tables, cur = [], 0
+    for c in ctxs:
+        n = (c + bs - 1) // bs
+        tables.append(perm[cur:cur + n].tolist())
+        cur += n
+    q = rng.standard_normal((len(ctxs), hq, hd)).astype(np.float32)
+    if dtype == pkg.DType.BF16:
+        q = oracle.round_to_bf16(q)
+    pos = [c - 1 for c in ctxs]
+    got = pkg.ops.paged_attention(backend, arr[0], q, pos, list(range(len(ctxs))), tables, dtype=dtype)
+    exp = np.stack([oracle.paged_attention(store, q[i].reshape(-1), tables[i], pos[i], 0, hq, hkv, hd, bs)
+                    for i in range(len(ctxs))]).reshape(got.shape)
+    tol = pkg.Tolerance.F32 if dtype == pkg.DType.F32 else pkg.Tolerance.F16
+    rep = pkg.validate(f"paged_attention_{dtype_name}", exp, got, tol)
+    assert rep.passed(), rep.render()
+    # prefill-style rows: several rows of one sequence at different positions (generic kernel)
+    rows_pos = [0, 5, 199]
+    qs = q[:3]
+    got = pkg.ops.paged_attention(backend, arr[0], qs, rows_pos, [5, 5, 5], tables, dtype=dtype)
+    exp = np.stack([oracle.paged_attention(store, qs[i].reshape(-1), tables[5], rows_pos[i], 0, hq, hkv, hd, bs)
+                    for i in range(3)]).reshape(got.shape)
+    rep = pkg.validate(f"paged_attention_rows_{dtype_name}", exp, got, tol)
+    assert rep.passed(), rep.render()
+
+
+def test_decode_attention_long_contexts_with_splits(pkg, backend, oracle):
+    """Small batch, long contexts: the context is split across CTAs and recombined."""
+    rng = np.random.default_rng(5)
+    hq, hkv, hd, bs = 32, 8, 128, 16
+    ctxs = [8192, 4099]
+    nblocks = sum((c + bs - 1) // bs for c in ctxs)
+    store = oracle.KvStore(1, nblocks, bs, hkv, hd)
+    arr = store.array()
+    arr[...] = oracle.round_to_bf16(rng.standard_normal(arr.shape).astype(np.float32))
+    perm = rng.permutation(nblocks)
+    tables = [perm[:512].tolist(), perm[512:].tolist()]
+    q = oracle.round_to_bf16(rng.standard_normal((2, hq, hd)).astype(np.float32))
+    got = pkg.ops.paged_attention(backend, arr[0], q, [c - 1 for c in ctxs], [0, 1], tables, dtype=pkg.DType.BF16)
+    exp = np.stack([oracle.paged_attention(store, q[i].reshape(-1), tables[i], ctxs[i] - 1, 0, hq, hkv, hd, bs)
+                    for i in range(2)]).reshape(got.shape)
+    rep = pkg.validate("paged_decode_split", exp, got, pkg.Tolerance.F16)
+    assert rep.passed(), rep.render()
+
+
+def test_attention_microbench_matches_the_oracle_on_sampled_sequences(pkg, backend, oracle):
+    rng = np.random.default_rng(9)
+    ctxs = rng.integers(512, 8193, 8)
+    bench = pkg.PagedAttentionBench(backend, ctxs, num_blocks=8192, seed=3)
+    ms, nbytes = bench.run(1, 2)
+    assert ms > 0 and nbytes >= int(ctxs.sum()) * 4096
+    out = bench.output()
+    for s in (0, 5):
+        q, k, v = bench.sequence(s)
+        ctx = int(ctxs[s])
+        store = oracle.KvStore(1, (ctx + 15) // 16, 16, 8, 128)
+        a = store.array()[0]  # [block][k|v][slot][head][dim]
+        pad = (-ctx) % 16
+        kk = np.concatenate([k, np.zeros((pad, 8, 128), np.float32)]).reshape(-1, 16, 8, 128)
+        vv = np.concatenate([v, np.zeros((pad, 8, 128), np.float32)]).reshape(-1, 16, 8, 128)
+        a[:, 0], a[:, 1] = kk, vv
+        exp = oracle.paged_attention(store, q.reshape(-1), list(range((ctx + 15) // 16)), ctx - 1, 0, 32, 8, 128, 16)
+        rep = pkg.validate("attn_bench", exp, out[s].reshape(-1), pkg.Tolerance.F16)
+        assert rep.passed(), rep.render()
+
+
+# ---- transformer.rs: invariants on the reference's tiny model ---------------------
+
+def _tiny(pkg, backend, layers, dtype):
+    meta = pkg.ModelMetadata(architecture="llama", name="tiny", num_layers=layers,
+                             **{k: v for k, v in TINY_SIN_META.items() if k not in ("num_blocks", "block_size")})
+    return pkg.CudaTransformerModel.new(meta, tiny_sin_tensors(layers), 16, 4, backend, compute_dtype=dtype,
+                                        max_batch_tokens=32, max_batch_sequences=4)
+
+
+def _one(pkg, tokens, positions, blocks, ctx=None, prefill=True):
+    n = len(tokens)
+    return pkg.ForwardBatch(tokens, positions, [1], [n], [ctx or n], [blocks], has_prefill=prefill)
+
+
+def test_tiny_model_matches_the_oracle_and_keeps_its_invariants(pkg, backend, oracle):
+    f32 = pkg.DType.F32
+    ref = oracle.Model(num_layers=2, **TINY_SIN_META).load(tiny_sin_tensors(2))
+    m = _tiny(pkg, backend, 2, f32)
+    got = m.forward(_one(pkg, [1, 2, 3], [0, 1, 2], [0]))
+    exp = ref.forward(oracle.Batch([1, 2, 3], [0, 1, 2], [3], [3], [[0]]))
+    assert got.vocab_size == 8 and got.num_sequences() == 1 and got.logits.shape == (1, 8)
+    assert rel_err(got.logits, exp) < F32_REL
+    assert got.row(0) is not None and got.row(1) is None
+    # empty batch (transformer.rs:564-578)
+    empty = m.forward(pkg.ForwardBatch([], [], [], [], [], [], has_prefill=False))
+    assert empty.logits.size == 0 and empty.num_sequences() == 0
+    # batch independence (transformer.rs:601-638)
+    m = _tiny(pkg, backend, 2, f32)
+    alone = m.forward(_one(pkg, [1, 2], [0, 1], [0])).row(0).copy()
+    together = m.forward(pkg.ForwardBatch([1, 2, 5, 6, 7], [0, 1, 0, 1, 2], [1, 2], [2, 3], [2, 3], [[0], [4]])).row(0)
+    assert np.max(np.abs(alone - together)) < 1e-4
+    # incremental decode == full prefill (transformer.rs:641-677)
+    full = _tiny(pkg, backend, 2, f32).forward(_one(pkg, [1, 2, 3], [0, 1, 2], [0])).row(0).copy()
+    m = _tiny(pkg, backend, 2, f32)
+    m.forward(_one(pkg, [1, 2], [0, 1], [0]))
+    inc = m.forward(_one(pkg, [3], [2], [0], ctx=3, prefill=False)).row(0)
+    assert np.max(np.abs(full - inc)) < 1e-4
+    # chunked prefill == single pass (transformer.rs:680-713)
+    whole = _tiny(pkg, backend, 2, f32).forward(_one(pkg, [1, 2, 3, 4], [0, 1, 2, 3], [0])).row(0).copy()
+    m = _tiny(pkg, backend, 2, f32)
+    m.forward(_one(pkg, [1, 2], [0, 1], [0]))
+    chunked = m.forward(_one(pkg, [3, 4], [2, 3], [0], ctx=4)).row(0)
+    assert np.max(np.abs(whole - chunked)) < 1e-4
+    # scattered table (transformer.rs:716-746)
+    a = _tiny(pkg, backend, 2, f32).forward(_one(pkg, [1, 2, 3, 4, 5], [0, 1, 2, 3, 4], [0, 1])).row(0).copy()
+    b = _tiny(pkg, backend, 2, f32).forward(_one(pkg, [1, 2, 3, 4, 5], [0, 1, 2, 3, 4], [11, 3])).row(0)
+    assert np.max(np.abs(a - b)) < 1e-5
+
+
+def test_forward_errors_precede_any_kv_write(pkg, backend):
+    m = _tiny(pkg, backend, 1, pkg.DType.F32)
+    with pytest.raises(pkg.InternalError, match="outside the vocabulary"):
+        m.forward(_one(pkg, [999], [0], [0]))
+    with pytest.raises(pkg.InternalError, match="RoPE table"):
+        m.forward(_one(pkg, [1], [100], list(range(26))))
+    bad = _one(pkg, [1, 2], [0, 1], [0])
+    bad.slot_token_counts = [5]
+    with pytest.raises(pkg.InternalError, match="sum to"):
+        m.forward(bad)
+    with pytest.raises(pkg.InternalError, match="has no block"):
+        m.forward(_one(pkg, [1, 2], [3, 4], [0]))
+    with pytest.raises(pkg.InternalError, match="out of range"):
+        m.forward(_one(pkg, [1], [0], [16]))
+    assert not m.read_kv().any(), "a rejected batch must not touch the arena"
+    with pytest.raises(pkg.InternalError, match="zero tokens"):
+        m.forward(pkg.ForwardBatch([1], [0], [1, 2], [1, 0], [1, 0], [[0], [1]]))
+    with pytest.raises(pkg.InvalidRequest):
+        m.forward(pkg.ForwardBatch(list(range(8)) * 5, list(range(8)) * 5, [1], [40], [40], [[0]]))
+
+
+def test_missing_and_misshapen_tensors_are_model_errors(pkg, backend):
+    meta = pkg.ModelMetadata(architecture="llama", name="t", num_layers=1,
+                             **{k: v for k, v in TINY_SIN_META.items() if k not in ("num_blocks", "block_size")})
+    t = tiny_sin_tensors(1)
+    m = pkg.CudaTransformerModel(meta, 4, 4, backend, compute_dtype=pkg.DType.F32)
+    for name, w in t.items():
+        if name != "model.layers.0.mlp.up_proj.weight":
+            m.load_tensor(name, w)
+    with pytest.raises(pkg.ModelError, match="up_proj"):
+        m.finalize()
+    with pytest.raises(pkg.ModelError, match="shape"):
+        m.load_tensor("model.layers.0.mlp.up_proj.weight", np.zeros((3, 3), np.float32))
+    with pytest.raises(pkg.ModelError):
+        m.load_tensor("model.layers.0.mlp.sideways.weight", np.zeros((3, 3), np.float32))
+    with pytest.raises(pkg.ModelError):
+        m.forward(_one(pkg, [1], [0], [0]))
+
+
+# ---- config 1: tiny Llama, 8 sequences, 32 greedy steps ---------------------------
+
+@pytest.mark.parametrize("dtype_name", ["F32", "BF16"])
+def test_config1_greedy_decode_matches_the_oracle(pkg, backend, oracle, dtype_name):
+    dtype = getattr(pkg.DType, dtype_name)
+    weights = c1_tensors(seed=1234, bf16_round=oracle.round_to_bf16 if dtype == pkg.DType.BF16 else None)
+    meta = pkg.ModelMetadata(architecture="llama", name="c1", **C1_META)
+    dev = pkg.CudaTransformerModel.new(meta, weights, 160, 16, backend, compute_dtype=dtype,
+                                       max_batch_tokens=1024, max_batch_sequences=8)
+    ref = oracle.Model(num_blocks=160, block_size=16, **C1_META).load(weights)
+    oracle.set_threads(8)
+    drv = GreedyDriver(num_blocks=160, block_size=16, seed=7, num_sequences=8, prompt_range=(32, 128),
+                       vocab=C1_META["vocab_size"])
+    worst = 0.0
+    for step in range(33):  # one prefill step + 32 decode steps
+        batch = drv.next_batch()
+        exp = ref.forward(oracle.Batch(batch.tokens, batch.positions, batch.slot_token_counts,
+                                       batch.context_lens, batch.block_tables))
+        ids, got = dev.forward_greedy(batch, want_logits=True)
+        exp_ids = [oracle.argmax(r) for r in exp]
+        assert ids.tolist() == exp_ids, f"greedy tokens diverged at step {step}"
+        if dtype == pkg.DType.F32:
+            worst = max(worst, rel_err(got, exp))
+            assert worst < F32_REL, f"step {step}: logits relative error {worst}"
+        else:
+            worst = max(worst, float(np.max(np.abs(softmax_rows(got) - softmax_rows(exp)))))
+            assert worst < BF16_SOFTMAX, f"step {step}: softmax max-abs {worst}"
+        drv.accept(exp_ids)
+    oracle.set_threads(1)
+    # the arenas agree slot for slot (block tables and slot mapping are bit-exact by construction)
+    kv_dev, kv_ref = dev.read_kv(), ref.kv().array()
+    tol = pkg.Tolerance.F32 if dtype == pkg.DType.F32 else pkg.Tolerance.F16
+    written = kv_ref != 0
+    assert np.array_equal(kv_dev != 0, written), "exactly the same slots were written"
+    rep = pkg.validate("kv_arena", kv_ref, kv_dev, pkg.Tolerance(tol.abs * 10, tol.rel * 10))
+    assert rep.passed(), rep.render()
+
+
+def test_qwen2_shape_with_qkv_bias(pkg, backend, oracle):
+    meta_d = dict(SMALL_META, hidden_size=128, head_dim=64, num_attention_heads=4, num_kv_heads=2,
+                  ffn_dim=256, vocab_size=300, has_qkv_bias=True, num_blocks=16, block_size=16,
+                  max_position_embeddings=256)
+    t = random_tensors(np.random.default_rng(3), meta_d, std=0.08)
+    ref = oracle.Model(**meta_d).load(t)
+    meta = pkg.ModelMetadata(architecture="qwen2", name="q",
+                             **{k: v for k, v in meta_d.items() if k not in ("num_blocks", "block_size")})
+    for dtype, check in ((pkg.DType.F32, lambda g, e: rel_err(g, e) < F32_REL),):
+        dev = pkg.CudaTransformerModel.new(meta, t, 16, 16, backend, compute_dtype=dtype, max_batch_tokens=64,
+                                           max_batch_sequences=4)
+        toks = np.arange(40) % 300
+        b = pkg.ForwardBatch(toks, np.arange(40), [1], [40], [40], [[9, 2, 7]])
+        exp = ref.forward(oracle.Batch(toks, np.arange(40), [40], [40], [[9, 2, 7]]))
+        assert check(dev.forward(b).logits, exp)
