@@ -168,6 +168,15 @@ int orion_cuda_model_forward_greedy(OrionModel *model, const uint32_t *tokens,
  * device copy (inputs and block tables stay resident). Used to time the
  * device-resident step; results land in the model's device logits buffer. */
 int orion_cuda_model_replay(OrionModel *model, int iterations, float *elapsed_ms);
+/* Replays the previous batch with an event pair around every kernel launch and
+ * sums device time and launch counts per category: [0] projection GEMMs,
+ * [1] paged attention, [2] fused elementwise kernels, [3] tensor-parallel
+ * reductions. Accumulated over `iterations` steps. */
+int orion_cuda_model_profile(OrionModel *model, int iterations, float category_ms[4],
+                             uint64_t category_launches[4]);
+/* Fills this rank's KV arena with N(0, std) values (synthetic contexts for
+ * benchmarks whose prefill would take too long to run). */
+int orion_cuda_model_fill_kv_random(OrionModel *model, uint64_t seed, float std);
 /* Kernels launched by the most recent forward / replay iteration. */
 int orion_cuda_model_last_launch_count(const OrionModel *model, uint64_t *launches);
 /* Copies this rank's KV arena to the host in the reference's logical order

@@ -375,6 +375,20 @@ int orion_cuda_model_replay(OrionModel *model, int iterations, float *elapsed_ms
   return model->impl->replay(iterations, elapsed_ms);
 }
 
+int orion_cuda_model_profile(OrionModel *model, int iterations, float category_ms[4],
+                             uint64_t category_launches[4]) {
+  clear_error();
+  if (!model || !category_ms || !category_launches)
+    return set_error(ORION_ERR_INVALID_REQUEST, "null pointer argument");
+  return model->impl->profile(iterations, category_ms, category_launches);
+}
+
+int orion_cuda_model_fill_kv_random(OrionModel *model, uint64_t seed, float std) {
+  clear_error();
+  if (!model) return set_error(ORION_ERR_INVALID_REQUEST, "null model handle");
+  return model->impl->fill_kv_random(seed, std);
+}
+
 int orion_cuda_model_last_launch_count(const OrionModel *model, uint64_t *launches) {
   clear_error();
   if (!model || !launches) return set_error(ORION_ERR_INVALID_REQUEST, "null pointer argument");

@@ -79,6 +79,7 @@ class Model final : public ModelBase {
     if (stage_f32_) cudaFree(stage_f32_);
     if (ev0_) cudaEventDestroy(ev0_);
     if (ev1_) cudaEventDestroy(ev1_);
+    for (cudaEvent_t e : prof_pool_) cudaEventDestroy(e);
     if (stream_) cudaStreamDestroy(stream_);
   }
 
@@ -90,6 +91,9 @@ class Model final : public ModelBase {
   int forward(const BatchView &b, float *logits_out, uint64_t logits_capacity,
               uint32_t *token_ids_out) override;
   int replay(int iterations, float *elapsed_ms) override;
+  int profile(int iterations, float category_ms[kProfCategories],
+              uint64_t category_launches[kProfCategories]) override;
+  int fill_kv_random(uint64_t seed, float std) override;
   int read_kv(float *out, uint64_t capacity) override;
   uint64_t last_launch_count() const override { return last_launches_; }
   const OrionModelDesc &desc() const override { return d_; }
@@ -126,6 +130,30 @@ class Model final : public ModelBase {
                    uint64_t r1, uint64_t c0, uint64_t c1);
   int run_step(bool want_argmax);
   int tp_reduce(uint32_t *splits, size_t slab);
+  // Per-launch event pairs of a profiled step, resolved after the stream drains.
+  struct ProfRec { int cat; cudaEvent_t a, b; };
+  std::vector<ProfRec> prof_recs_;
+  std::vector<cudaEvent_t> prof_pool_;
+  size_t prof_used_ = 0;
+  bool prof_on_ = false;
+  cudaEvent_t prof_event() {
+    if (prof_used_ == prof_pool_.size()) {
+      cudaEvent_t e = nullptr;
+      cudaEventCreate(&e);
+      prof_pool_.push_back(e);
+    }
+    return prof_pool_[prof_used_++];
+  }
+  template <typename F>
+  int timed(int cat, F &&fn) {
+    if (!prof_on_) return fn();
+    cudaEvent_t a = prof_event(), b = prof_event();
+    cudaEventRecord(a, stream_);
+    const int rc = fn();
+    cudaEventRecord(b, stream_);
+    prof_recs_.push_back({cat, a, b});
+    return rc;
+  }
 
   OrionBackend *backend_;
   OrionModelDesc d_;
@@ -505,47 +533,47 @@ int Model<T>::run_step(bool want_argmax) {
   const bool tuned_decode = kBf16 && meta_.decode && decode_attention_supported(kv_, lq_);
   const uint32_t dsplits = tuned_decode ? decode_choose_splits(Tn, lkv_, meta_.max_position, d.block_size, 32) : 1;
 
-  ORION_TRY(launch_embed_rmsnorm<T>(embed_, tokens, layers_[0].in_norm, d.rms_norm_eps, hidden_, normed_, Tn, H, stream_));
+  ORION_TRY(timed(kProfElementwise, [&] { return launch_embed_rmsnorm<T>(embed_, tokens, layers_[0].in_norm, d.rms_norm_eps, hidden_, normed_, Tn, H, stream_); }));
   for (uint32_t l = 0; l < d.num_layers; ++l) {
     const Layer &L = layers_[l];
     GemmPlan p = gemm_plan(kBf16, Tn, nqkv, H, H, H);
-    ORION_TRY(launch_gemm<T>(normed_, H, L.w_qkv, H, partial_, Tn, nqkv, H, p, stream_));
-    ORION_TRY(launch_rope_kvwrite<T>(partial_, p.splits, (size_t)Tn * nqkv, L.b_qkv, positions, slot_block,
-                                     slot_slot, rope_cos_, rope_sin_, qbuf_, arena_, kv_, l, Tn, lq_, stream_));
+    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_qkv, H, partial_, Tn, nqkv, H, p, stream_); }));
+    ORION_TRY(timed(kProfElementwise, [&] { return launch_rope_kvwrite<T>(partial_, p.splits, (size_t)Tn * nqkv, L.b_qkv, positions, slot_block,
+                                     slot_slot, rope_cos_, rope_sin_, qbuf_, arena_, kv_, l, Tn, lq_, stream_); }));
     if (tuned_decode) {
       if constexpr (kBf16) {
         DecodeScratch sc{dscratch_, dscratch_ + (size_t)Tn * lq_ * dsplits * hd, dsplits};
-        ORION_TRY(launch_paged_attention_decode(qbuf_, arena_, kv_, l, ab, lq_, dsplits, sc, attn_, stream_));
+        ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_decode(qbuf_, arena_, kv_, l, ab, lq_, dsplits, sc, attn_, stream_); }));
       }
     } else {
-      ORION_TRY(launch_paged_attention_generic<T>(qbuf_, arena_, kv_, l, ab, lq_, attn_, stream_));
+      ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_generic<T>(qbuf_, arena_, kv_, l, ab, lq_, attn_, stream_); }));
     }
     p = gemm_plan(kBf16, Tn, H, qd, qd, qd);
-    ORION_TRY(launch_gemm<T>(attn_, qd, L.w_o, qd, partial_, Tn, H, qd, p, stream_));
-    ORION_TRY(tp_reduce(&p.splits, (size_t)Tn * H));
-    ORION_TRY(launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, L.post_norm, d.rms_norm_eps,
-                                         normed_, nullptr, Tn, H, stream_));
+    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(attn_, qd, L.w_o, qd, partial_, Tn, H, qd, p, stream_); }));
+    ORION_TRY(timed(kProfCollective, [&] { return tp_reduce(&p.splits, (size_t)Tn * H); }));
+    ORION_TRY(timed(kProfElementwise, [&] { return launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, L.post_norm, d.rms_norm_eps,
+                                         normed_, nullptr, Tn, H, stream_); }));
     p = gemm_plan(kBf16, Tn, 2 * lf_, H, H, H);
-    ORION_TRY(launch_gemm<T>(normed_, H, L.w_gu, H, partial_, Tn, 2 * lf_, H, p, stream_));
-    ORION_TRY(launch_swiglu<T>(partial_, p.splits, (size_t)Tn * 2 * lf_, act_, Tn, lf_, stream_));
+    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_gu, H, partial_, Tn, 2 * lf_, H, p, stream_); }));
+    ORION_TRY(timed(kProfElementwise, [&] { return launch_swiglu<T>(partial_, p.splits, (size_t)Tn * 2 * lf_, act_, Tn, lf_, stream_); }));
     p = gemm_plan(kBf16, Tn, H, lf_, lf_, lf_);
-    ORION_TRY(launch_gemm<T>(act_, lf_, L.w_down, lf_, partial_, Tn, H, lf_, p, stream_));
-    ORION_TRY(tp_reduce(&p.splits, (size_t)Tn * H));
+    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(act_, lf_, L.w_down, lf_, partial_, Tn, H, lf_, p, stream_); }));
+    ORION_TRY(timed(kProfCollective, [&] { return tp_reduce(&p.splits, (size_t)Tn * H); }));
     if (l + 1 < d.num_layers) {
-      ORION_TRY(launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, layers_[l + 1].in_norm,
-                                           d.rms_norm_eps, normed_, nullptr, Tn, H, stream_));
+      ORION_TRY(timed(kProfElementwise, [&] { return launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, layers_[l + 1].in_norm,
+                                           d.rms_norm_eps, normed_, nullptr, Tn, H, stream_); }));
     } else if (!meta_.zero_count) {
       // Final norm over the last row of every sequence (transformer.rs:401-428;
       // the norm is row-wise, so gathering first gives the same rows).
-      ORION_TRY(launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, final_norm_, d.rms_norm_eps,
-                                           tail_, last_rows, S, H, stream_));
+      ORION_TRY(timed(kProfElementwise, [&] { return launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, final_norm_, d.rms_norm_eps,
+                                           tail_, last_rows, S, H, stream_); }));
     }
   }
   if (meta_.zero_count) return ORION_OK;
   GemmPlan hp = gemm_plan(kBf16, S, d.vocab_size, H, H, H);
   hp.splits = 1;  // logits are written in place, row-major [S][V]
-  ORION_TRY(launch_gemm<T>(tail_, H, lm_head_, H, logits_, S, d.vocab_size, H, hp, stream_));
-  if (want_argmax) ORION_TRY(launch_argmax(logits_, S, d.vocab_size, argmax_, stream_));
+  ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(tail_, H, lm_head_, H, logits_, S, d.vocab_size, H, hp, stream_); }));
+  if (want_argmax) ORION_TRY(timed(kProfElementwise, [&] { return launch_argmax(logits_, S, d.vocab_size, argmax_, stream_); }));
   return ORION_OK;
 }
 
@@ -710,6 +738,50 @@ int Model<T>::replay(int iterations, float *elapsed_ms) {
   float ms = 0.f;
   ORION_CUDA_CHECK("replay", cudaEventElapsedTime(&ms, ev0_, ev1_));
   if (elapsed_ms) *elapsed_ms = ms;
+  return ORION_OK;
+}
+
+template <typename T>
+int Model<T>::profile(int iterations, float category_ms[kProfCategories],
+                      uint64_t category_launches[kProfCategories]) {
+  if (meta_.rows == 0 || meta_.zero_count)
+    return set_error(ORION_ERR_INVALID_REQUEST, "profile needs a preceding successful forward");
+  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  for (int c = 0; c < kProfCategories; ++c) {
+    category_ms[c] = 0.f;
+    category_launches[c] = 0;
+  }
+  for (int i = 0; i < iterations; ++i) {
+    prof_recs_.clear();
+    prof_used_ = 0;
+    prof_on_ = true;
+    const int rc = run_step(false);
+    prof_on_ = false;
+    ORION_TRY(rc);
+    ORION_CUDA_CHECK("profile", cudaStreamSynchronize(stream_));
+    for (const ProfRec &r : prof_recs_) {
+      float ms = 0.f;
+      ORION_CUDA_CHECK("profile", cudaEventElapsedTime(&ms, r.a, r.b));
+      category_ms[r.cat] += ms;
+      category_launches[r.cat] += 1;
+    }
+  }
+  return ORION_OK;
+}
+
+template <typename T>
+int Model<T>::fill_kv_random(uint64_t seed, float std) {
+  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  const size_t total = kv_.layer_elems() * d_.num_layers;
+  const size_t chunk = 64u << 20;
+  ORION_TRY(ensure_stage(&stage_f32_, &stage_f32_cap_, std::min(total, chunk) * sizeof(float)));
+  for (size_t off = 0; off < total; off += chunk) {
+    const size_t m = std::min(chunk, total - off);
+    float *tmp = static_cast<float *>(stage_f32_);
+    ORION_TRY(launch_fill_normal<float>(tmp, m, seed + off, stream_));
+    ORION_TRY(launch_scale_convert<T>(tmp, arena_ + off, m, std, stream_));
+  }
+  ORION_CUDA_CHECK("fill_kv_random", cudaStreamSynchronize(stream_));
   return ORION_OK;
 }
 

@@ -46,6 +46,9 @@ struct ParallelLayout {
 int compute_layout(uint32_t heads, uint32_t kv_heads, uint32_t ffn, uint32_t rank, uint32_t world,
                    ParallelLayout *out);
 
+// Kernel categories of a profiled step.
+enum { kProfGemm = 0, kProfAttention = 1, kProfElementwise = 2, kProfCollective = 3, kProfCategories = 4 };
+
 class ModelBase {
  public:
   virtual ~ModelBase() = default;
@@ -56,6 +59,9 @@ class ModelBase {
   virtual int forward(const BatchView &b, float *logits_out, uint64_t logits_capacity,
                       uint32_t *token_ids_out) = 0;
   virtual int replay(int iterations, float *elapsed_ms) = 0;
+  virtual int profile(int iterations, float category_ms[kProfCategories],
+                      uint64_t category_launches[kProfCategories]) = 0;
+  virtual int fill_kv_random(uint64_t seed, float std) = 0;
   virtual int read_kv(float *out, uint64_t capacity) = 0;
   virtual uint64_t last_launch_count() const = 0;
   virtual const OrionModelDesc &desc() const = 0;

@@ -299,6 +299,17 @@ class CudaTransformerModel:
         check(_ffi.lib().orion_cuda_model_replay(self._h, iterations, C.byref(ms)))
         return ms.value
 
+    def profile(self, iterations: int):
+        """Per-category device time of the previous batch: dict name -> (ms, launches), summed
+        over ``iterations`` replays."""
+        ms, n = (C.c_float * 4)(), (C.c_uint64 * 4)()
+        check(_ffi.lib().orion_cuda_model_profile(self._h, iterations, ms, n))
+        names = ("gemm", "attention", "elementwise", "collective")
+        return {k: (float(ms[i]), int(n[i])) for i, k in enumerate(names)}
+
+    def fill_kv_random(self, seed: int, std: float = 1.0) -> None:
+        check(_ffi.lib().orion_cuda_model_fill_kv_random(self._h, seed, std))
+
     def last_launch_count(self) -> int:
         v = C.c_uint64()
         check(_ffi.lib().orion_cuda_model_last_launch_count(self._h, C.byref(v)))
