@@ -14,6 +14,7 @@ pytestmark = pytest.mark.gpu
 
 F32_REL = 1e-3      # f32 build: logits relative error
 BF16_SOFTMAX = 2e-2  # bf16 build: max-abs after softmax
+BF16_TIE_MARGIN = 1e-2  # bf16 build: a greedy token may differ only below this oracle top-2 logit gap
 
 
 @pytest.fixture(scope="module")
@@ -339,14 +340,28 @@ def test_config1_greedy_decode_matches_the_oracle(pkg, backend, oracle, dtype_na
     oracle.set_threads(8)
     drv = GreedyDriver(num_blocks=160, block_size=16, seed=7, num_sequences=8, prompt_range=(32, 128),
                        vocab=C1_META["vocab_size"])
-    worst = 0.0
+    worst, flipped, total_tokens = 0.0, 0, 0
     for step in range(33):  # one prefill step + 32 decode steps
         batch = drv.next_batch()
         exp = ref.forward(oracle.Batch(batch.tokens, batch.positions, batch.slot_token_counts,
                                        batch.context_lens, batch.block_tables))
         ids, got = dev.forward_greedy(batch, want_logits=True)
         exp_ids = [oracle.argmax(r) for r in exp]
-        assert ids.tolist() == exp_ids, f"greedy tokens diverged at step {step}"
+        if dtype == pkg.DType.F32:
+            assert ids.tolist() == exp_ids, f"greedy tokens diverged at step {step}"
+        else:
+            # bf16 storage of activations and KV puts about 6e-3 of noise on logits whose top-2
+            # gap, for a random-init model, is often smaller than that. A token may differ only
+            # where the oracle's own gap is below BF16_TIE_MARGIN; the oracle's token is fed
+            # back either way so that later steps stay comparable.
+            srt = np.sort(exp, axis=1)
+            margin = srt[:, -1] - srt[:, -2]
+            for i, (a, b) in enumerate(zip(ids.tolist(), exp_ids)):
+                total_tokens += 1
+                if a != b:
+                    flipped += 1
+                    assert margin[i] < BF16_TIE_MARGIN, (
+                        f"step {step} seq {i}: token {a} != {b} at an oracle margin of {margin[i]}")
         if dtype == pkg.DType.F32:
             worst = max(worst, rel_err(got, exp))
             assert worst < F32_REL, f"step {step}: logits relative error {worst}"
@@ -355,6 +370,8 @@ def test_config1_greedy_decode_matches_the_oracle(pkg, backend, oracle, dtype_na
             assert worst < BF16_SOFTMAX, f"step {step}: softmax max-abs {worst}"
         drv.accept(exp_ids)
     oracle.set_threads(1)
+    if dtype == pkg.DType.BF16:
+        assert flipped <= 0.02 * total_tokens, f"{flipped} of {total_tokens} greedy tokens differ"
     # the arenas agree slot for slot (block tables and slot mapping are bit-exact by construction)
     kv_dev, kv_ref = dev.read_kv(), ref.kv().array()
     tol = pkg.Tolerance.F32 if dtype == pkg.DType.F32 else pkg.Tolerance.F16
