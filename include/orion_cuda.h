@@ -262,7 +262,46 @@ int orion_cuda_attn_bench_output(OrionAttnBench *bench, float *out);
 /* q: [num_query_heads*head_dim]; k, v: [context_len][num_kv_heads][head_dim] f32. */
 int orion_cuda_attn_bench_sequence(OrionAttnBench *bench, uint32_t seq, float *q, float *k,
                                    float *v);
+/* DEVICE pointers of the benchmark's inputs (bf16 q [batch][heads*dim], the bf16
+ * arena in the library's layout, and the u32 batch arrays), valid until the
+ * handle is destroyed. Any output pointer may be NULL. */
+int orion_cuda_attn_bench_device_views(OrionAttnBench *bench, const void **q, const void **kv_arena,
+                                       const uint32_t **query_positions, const uint32_t **seq_of_row,
+                                       const uint32_t **block_tables_flat,
+                                       const uint32_t **block_table_offsets, uint32_t *max_position);
 void orion_cuda_attn_bench_destroy(OrionAttnBench *bench);
+
+/* ---- decode attention for callers that cannot allocate ----
+ * This entry point has no counterpart in the reference. It is the paged GQA
+ * decode attention above (bf16, head_dim 128, 16-token blocks, one query row
+ * per sequence) for callers that must not allocate device memory when they
+ * call: code between cudaStreamBeginCapture and cudaStreamEndCapture, a serving
+ * loop whose memory all belongs to somebody else's pool, a plugin that is
+ * handed buffers and a stream and nothing more. It never calls cudaMalloc,
+ * cudaFree or any allocating routine.
+ *
+ * All pointers are DEVICE pointers owned by the caller: q and out are bf16
+ * [rows][num_query_heads*128]; kv_arena is ONE layer in the library's layout
+ * ([block][kv head][k|v][slot][dim], 16-byte groups of a row XOR-permuted by
+ * slot & 7); the u32 arrays are as in orion_cuda_paged_attention. `stream` is
+ * a cudaStream_t (NULL = the default stream). `splits` is how many pieces each
+ * context is cut into (0 = chosen like the allocating path does).
+ *
+ * The per-split partial results live in a fixed 16 MiB array inside the
+ * library (held by every GPU that loads it until the process exits). A call
+ * needing more — rows * num_query_heads * splits * 130 floats > 4 Mi floats —
+ * is rejected with ORION_ERR_INVALID_REQUEST; splits == 1 needs none.
+ * The first call on a device looks the array's address up; make that first
+ * call before starting any stream capture. Every call on a device shares the
+ * one array: calls whose kernels can overlap on the GPU (different streams
+ * without ordering between them) race on it and must be serialised by the
+ * caller. The array needs no clearing between calls: each call overwrites
+ * every slot it later reads. */
+int orion_cuda_paged_decode_attention_noalloc(
+    int device, const void *q, const void *kv_arena, uint32_t num_blocks, uint32_t num_kv_heads,
+    uint32_t num_query_heads, const uint32_t *query_positions, const uint32_t *seq_of_row,
+    const uint32_t *block_tables_flat, const uint32_t *block_table_offsets, uint32_t rows,
+    uint32_t max_position, uint32_t splits, void *out, void *stream);
 
 #ifdef __cplusplus
 }

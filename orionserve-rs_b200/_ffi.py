@@ -86,7 +86,12 @@ SIGNATURES = {
     "orion_cuda_attn_bench_run": (_int, [_vp, _int, _int, _f32p, _u64p]),
     "orion_cuda_attn_bench_output": (_int, [_vp, _f32p]),
     "orion_cuda_attn_bench_sequence": (_int, [_vp, _u32, _f32p, _f32p, _f32p]),
+    "orion_cuda_attn_bench_device_views": (_int, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
+                                                  C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
+                                                  C.POINTER(_u32)]),
     "orion_cuda_attn_bench_destroy": (None, [_vp]),
+    "orion_cuda_paged_decode_attention_noalloc": (_int, [_int, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp,
+                                                         _vp, _u32, _u32, _u32, _vp, _vp]),
 }
 
 

@@ -20,8 +20,9 @@ class PagedAttentionBench:
         self.batch = int(self.context_lens.size)
         self.q_heads, self.kv_heads, self.head_dim, self.block_size = (num_query_heads, num_kv_heads,
                                                                       head_dim, block_size)
+        self.num_blocks = num_blocks
         rng = np.random.default_rng(seed)
-        need = int(((self.context_lens + block_size - 1) // block_size).sum())
+        need =int(((self.context_lens + block_size - 1) // block_size).sum())
         if need > num_blocks:
             raise ValueError(f"{need} blocks needed, pool has {num_blocks}")
         # each sequence's table is a consecutive slice of one random permutation of the pool
@@ -42,6 +43,17 @@ class PagedAttentionBench:
         ms, nbytes = C.c_float(), C.c_uint64()
         check(_ffi.lib().orion_cuda_attn_bench_run(self._h, warmup, iterations, C.byref(ms), C.byref(nbytes)))
         return ms.value, nbytes.value
+
+    def device_views(self) -> dict:
+        """Device addresses (ints) of the benchmark's inputs; valid while this object lives."""
+        ptrs = [C.c_void_p() for _ in range(6)]
+        max_pos = C.c_uint32()
+        check(_ffi.lib().orion_cuda_attn_bench_device_views(self._h, *[C.byref(p) for p in ptrs],
+                                                            C.byref(max_pos)))
+        names = ("q", "kv_arena", "query_positions", "seq_of_row", "block_tables_flat", "block_table_offsets")
+        views = {n: p.value for n, p in zip(names, ptrs)}
+        views["max_position"] = max_pos.value
+        return views
 
     def output(self) -> np.ndarray:
         out = np.zeros((self.batch, self.q_heads, self.head_dim), np.float32)

@@ -479,4 +479,78 @@ int decode_poll_error(uint32_t *code) {
   return ORION_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free decode attention
+// ---------------------------------------------------------------------------
+//
+// Some callers may not allocate device memory at the moment they need attention:
+// code running while a CUDA stream is being captured into a graph, code inside a
+// serving loop that has handed all of its memory to a pool it does not own, or a
+// plugin that was only given buffers and a stream. For them the split-context
+// decode kernel gets its per-split partial results from a fixed array that lives
+// in the library image instead of from a buffer sized and allocated per call.
+//
+// The array costs kNoAllocScratchFloats * 4 bytes (16 MiB) on every GPU that loads
+// this library, for the life of the process.
+constexpr size_t kNoAllocScratchFloats = size_t(4) << 20;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of g_noalloc_scratch per device ordinal. The symbol's name is
+// only a host-side handle; a kernel must be given the address looked up with
+// cudaGetSymbolAddress while that device is current.
+float *g_noalloc_ptr[kMaxDevices] = {};
+}  // namespace
+
+int noalloc_decode_attention(int device, const bf16 *q, const bf16 *arena, uint32_t num_blocks,
+                             uint32_t num_kv_heads, uint32_t num_query_heads,
+                             const uint32_t *query_positions, const uint32_t *seq_of_row,
+                             const uint32_t *tables_flat, const uint32_t *table_offsets,
+                             uint32_t rows, uint32_t max_position, uint32_t splits, bf16 *out,
+                             cudaStream_t stream) {
+  if (device < 0 || device >= kMaxDevices)
+    return set_error(ORION_ERR_INVALID_REQUEST, "device ordinal %d outside 0..%d", device, kMaxDevices - 1);
+  KvLayout kv{1, num_blocks, num_kv_heads, (uint32_t)kBlk, (uint32_t)kHd, 1u};
+  if (!decode_attention_supported(kv, num_query_heads))
+    return set_error(ORION_ERR_INVALID_REQUEST,
+                     "allocation-free decode attention covers head_dim 128, block 16, at most 8 query "
+                     "heads per kv head");
+  if (rows == 0) return ORION_OK;
+  if (splits == 0) splits = decode_choose_splits(rows, num_kv_heads, max_position, kBlk, 32);
+  const size_t need = decode_scratch_floats(rows, num_query_heads, kHd, splits);
+  if (splits > 1 && need > kNoAllocScratchFloats)
+    return set_error(ORION_ERR_INVALID_REQUEST,
+                     "allocation-free decode attention: %u rows x %u heads x %u splits needs %zu scratch "
+                     "floats, the built-in array holds %zu; use fewer splits or the allocating entry point",
+                     rows, num_query_heads, splits, need, kNoAllocScratchFloats);
+  ORION_CUDA_CHECK("set device", cudaSetDevice(device));
+  if (!g_noalloc_ptr[device]) {
+    // One-time set-up for this device (no allocation: the array is part of the module).
+    void *p = nullptr;
+    ORION_CUDA_CHECK("scratch symbol address", cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    g_noalloc_ptr[device] = static_cast<float *>(p);
+  }
+  float *base = g_noalloc_ptr[device];
+  // Every (row, head, split) slot is written by the decode kernel before the
+  // combine kernel reads it, so nothing has to be cleared between calls.
+  DecodeScratch sc{base, base + (size_t)rows * num_query_heads * splits * kHd, splits};
+  AttnBatch ab{query_positions, seq_of_row, tables_flat, table_offsets, rows, max_position};
+  return launch_paged_attention_decode(q, arena, kv, 0, ab, num_query_heads, splits, sc, out, stream);
+}
+
 }  // namespace orion
+
+extern "C" int orion_cuda_paged_decode_attention_noalloc(
+    int device, const void *q, const void *kv_arena, uint32_t num_blocks, uint32_t num_kv_heads,
+    uint32_t num_query_heads, const uint32_t *query_positions, const uint32_t *seq_of_row,
+    const uint32_t *block_tables_flat, const uint32_t *block_table_offsets, uint32_t rows,
+    uint32_t max_position, uint32_t splits, void *out, void *stream) {
+  orion::clear_error();
+  if (!q || !kv_arena || !query_positions || !seq_of_row || !block_tables_flat || !block_table_offsets || !out)
+    return orion::set_error(ORION_ERR_INVALID_REQUEST, "null pointer argument");
+  return orion::noalloc_decode_attention(
+      device, static_cast<const orion::bf16 *>(q), static_cast<const orion::bf16 *>(kv_arena), num_blocks,
+      num_kv_heads, num_query_heads, query_positions, seq_of_row, block_tables_flat, block_table_offsets, rows,
+      max_position, splits, static_cast<orion::bf16 *>(out), static_cast<cudaStream_t>(stream));
+}

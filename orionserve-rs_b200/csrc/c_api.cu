@@ -673,6 +673,23 @@ int orion_cuda_attn_bench_sequence(OrionAttnBench *bench, uint32_t seq, float *q
   return ORION_OK;
 }
 
+int orion_cuda_attn_bench_device_views(OrionAttnBench *bench, const void **q, const void **kv_arena,
+                                       const uint32_t **query_positions, const uint32_t **seq_of_row,
+                                       const uint32_t **block_tables_flat, const uint32_t **block_table_offsets,
+                                       uint32_t *max_position) {
+  clear_error();
+  if (!bench) return set_error(ORION_ERR_INVALID_REQUEST, "null bench handle");
+  const uint32_t n = bench->batch;
+  if (q) *q = bench->q;
+  if (kv_arena) *kv_arena = bench->arena;
+  if (query_positions) *query_positions = bench->meta;
+  if (seq_of_row) *seq_of_row = bench->meta + n;
+  if (block_table_offsets) *block_table_offsets = bench->meta + 2 * n;
+  if (block_tables_flat) *block_tables_flat = bench->meta + 2 * n + (n + 1);
+  if (max_position) *max_position = bench->max_position;
+  return ORION_OK;
+}
+
 void orion_cuda_attn_bench_destroy(OrionAttnBench *bench) { delete bench; }
 
 }  // extern "C"
