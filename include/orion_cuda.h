@@ -189,9 +189,18 @@ int orion_cuda_model_desc(const OrionModel *model, OrionModelDesc *out);
  * here is written by DMA directly, a pageable one goes through a bounce copy. */
 void *orion_cuda_host_alloc(uint64_t bytes);
 void orion_cuda_host_free(void *ptr);
-/* Tuning knob: number of CTAs the split-K planner aims for on small batches
- * (0 restores the default of one per SM). */
-int orion_cuda_gemm_set_target_ctas(uint32_t ctas);
+/* Tuning knob: launch the kernels of a step with programmatic dependent launch
+ * (each kernel's prologue and weight prefetch overlap its predecessor's tail).
+ * On by default; 0 gives plain stream-ordered launches. */
+int orion_cuda_set_programmatic_launch(int enabled);
+/* Tuning knob of the decode attention kernel: shared-memory ring depth per warp
+ * (2, 3 or 4; fewer stages = more CTAs per SM) and the number of CTAs the context
+ * split aims for (0 keeps the current value). */
+int orion_cuda_attention_set_tuning(int stages, uint32_t cta_target);
+/* Tuning knob of the projection GEMM: number of CTAs the split-K planner aims
+ * for on decode batches (0 restores the default of two per SM) and the ring
+ * depth for token tiles of at most 64 (3 or 4 stages; 0 keeps it). */
+int orion_cuda_gemm_set_tuning(uint32_t ctas, int small_batch_stages);
 
 /* ---- tensor parallelism (orion-distributed/src/lib.rs) ---- */
 

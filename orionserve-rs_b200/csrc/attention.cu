@@ -36,6 +36,8 @@ paged_attention_generic_kernel(const T *__restrict__ q, const T *__restrict__ ar
   float *scores = smem + hd;    // [kGenChunk]
   __shared__ float red[kGenThreads / 32];
   __shared__ float bcast;
+  pdl_trigger();
+  pdl_wait();
 
   const uint32_t row = blockIdx.x, head = blockIdx.y;
   const uint32_t group = q_heads / kv.num_kv_heads;  // attention.rs:250
@@ -123,10 +125,11 @@ paged_attention_generic_kernel(const T *__restrict__ q, const T *__restrict__ ar
 constexpr int kHd = 128;          // head_dim
 constexpr int kBlk = 16;          // tokens per KV block
 constexpr int kWarps = 4;         // warps per CTA, each with a private ring
-constexpr int kStages = 4;        // ring depth per warp
 constexpr int kChunkBytes = 2 * kBlk * kHd * 2;  // K rows + V rows of one (block, head): 8 KiB
 constexpr int kMaxGroup = 8;      // query heads per kv head (N of the MMA)
-constexpr uint32_t kDecodeSmem = kWarps * kStages * kChunkBytes + 1024;
+// Ring depth per warp is a template parameter: 2 stages = 65 KiB per CTA (3 CTAs per SM),
+// 3 = 97 KiB (2 per SM), 4 = 129 KiB (1 per SM). The merge buffers (16.3 KiB) reuse the ring.
+constexpr uint32_t decode_smem_bytes(int stages) { return kWarps * stages * kChunkBytes + 1024; }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -164,7 +167,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // Device error word: bit 0 = a ring wait ran out of polls.
 __device__ uint32_t g_decode_error = 0;
 
-__global__ void __launch_bounds__(kWarps * 32, 1)
+template <int kStages>
+__global__ void __launch_bounds__(kWarps * 32)
 paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, KvLayout kv,
                     uint32_t layer, AttnBatch batch, uint32_t q_heads, uint32_t splits,
                     DecodeScratch scratch, bf16 *__restrict__ out) {
@@ -183,6 +187,7 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
   const uint32_t b_begin = min(split * per_split, nblocks);
   const uint32_t b_end = min(b_begin + per_split, nblocks);
 
+  pdl_trigger();
   if (threadIdx.x < kWarps * kStages) mbar_init(&bars[threadIdx.x], 1);
   mbar_fence_init();
   __syncthreads();
@@ -209,9 +214,23 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
     mbar_arrive_expect_tx(bar, kChunkBytes);
     bulk_copy_g2s(my_ring + (i % kStages) * kChunkBytes, src, kChunkBytes, bar);
   };
-  for (uint32_t i = 0; i < min(my_count, (uint32_t)kStages); ++i) {
+  // First ring fill. Blocks written in earlier steps are fetched before the
+  // dependency wait; the sequence's newest block (the one the preceding
+  // RoPE/KV-write kernel is filling) and the query only after it.
+  const uint32_t pre = min(my_count, (uint32_t)kStages);
+  uint32_t deferred = UINT32_MAX;
+  for (uint32_t i = 0; i < pre; ++i) {
     const uint32_t pb = entry(i);
+    if (b_begin + warp + i * kWarps == nblocks - 1) {
+      deferred = i;
+      continue;
+    }
     if (lane == 0) issue(i, pb);
+  }
+  pdl_wait();
+  if (deferred != UINT32_MAX) {
+    const uint32_t pb = entry(deferred);
+    if (lane == 0) issue(deferred, pb);
   }
 
   // Q^T as the B operand (k = dim, n = head): per 16-dim chunk two packed regs.
@@ -375,6 +394,8 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
 __global__ void __launch_bounds__(kHd)
 decode_combine_kernel(DecodeScratch scratch, uint32_t splits, uint32_t q_heads,
                       bf16 *__restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   const uint32_t row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const size_t base = ((size_t)row * q_heads + head) * scratch.max_splits;
   float mall = -INFINITY;
@@ -406,14 +427,20 @@ int launch_paged_attention_generic(const T *q, const T *arena, KvLayout kv, uint
     return set_error(ORION_ERR_INTERNAL, "head_dim %u exceeds the attention kernel limit of %d",
                      kv.head_dim, kGenThreads * kGenMaxDimsPerThread);
   const size_t smem = (kv.head_dim + kGenChunk) * sizeof(float);
-  paged_attention_generic_kernel<T><<<dim3(batch.rows, q_heads), kGenThreads, smem, stream>>>(
-      q, arena, kv, layer, batch, q_heads, out);
+  ORION_CUDA_CHECK("paged_attention",
+                   launch_pdl(paged_attention_generic_kernel<T>, dim3(batch.rows, q_heads), dim3(kGenThreads), smem,
+                              stream, q, arena, kv, layer, batch, q_heads, out));
   return after_launch("paged_attention");
 }
 template int launch_paged_attention_generic<float>(const float *, const float *, KvLayout, uint32_t,
                                                    AttnBatch, uint32_t, float *, cudaStream_t);
 template int launch_paged_attention_generic<bf16>(const bf16 *, const bf16 *, KvLayout, uint32_t,
                                                   AttnBatch, uint32_t, bf16 *, cudaStream_t);
+
+namespace {
+int g_decode_stages = 3;                 // ring depth per warp (2, 3 or 4)
+uint32_t g_decode_cta_target = 2 * 148;  // CTAs the context split aims for (two per SM are resident)
+}  // namespace
 
 bool decode_attention_supported(KvLayout kv, uint32_t q_heads) {
   return kv.head_dim == kHd && kv.block_size == kBlk && kv.swizzle == 1 && kv.num_kv_heads > 0 &&
@@ -431,12 +458,37 @@ uint32_t decode_choose_splits(uint32_t rows, uint32_t kv_heads, uint32_t max_pos
   // contexts, but keep at least 16 blocks (4 per warp) in every split.
   const uint32_t ctas = rows * kv_heads;
   if (ctas == 0) return 1;
-  uint32_t want = (4 * 148 + ctas - 1) / ctas;
+  uint32_t want = (g_decode_cta_target + ctas - 1) / ctas;
   const uint32_t nblocks = max_position / block_size + 1;
   const uint32_t cap = nblocks / 16 > 0 ? nblocks / 16 : 1;
   if (want > cap) want = cap;
   if (want > max_splits) want = max_splits;
   return want < 1 ? 1 : want;
+}
+
+namespace {
+template <int STAGES>
+int launch_decode_stages(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer, AttnBatch batch,
+                         uint32_t q_heads, uint32_t splits, DecodeScratch scratch, bf16 *out,
+                         cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    ORION_CUDA_CHECK("paged_decode attr",
+                     cudaFuncSetAttribute(paged_decode_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)decode_smem_bytes(STAGES)));
+    attr_set = true;
+  }
+  ORION_CUDA_CHECK("paged_decode",
+                   launch_pdl(paged_decode_kernel<STAGES>, dim3(kv.num_kv_heads, batch.rows, splits),
+                              dim3(kWarps * 32), (size_t)decode_smem_bytes(STAGES), stream, q, arena, kv, layer,
+                              batch, q_heads, splits, scratch, out));
+  return ORION_OK;
+}
+}  // namespace
+
+void decode_set_tuning(int stages, uint32_t cta_target) {
+  if (stages >= 2 && stages <= 4) g_decode_stages = stages;
+  if (cta_target) g_decode_cta_target = cta_target;
 }
 
 int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer,
@@ -449,20 +501,15 @@ int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv,
   if (splits > 1 && (scratch.partial_out == nullptr || splits > scratch.max_splits))
     return set_error(ORION_ERR_INTERNAL, "decode attention scratch too small for %u splits",
                      splits);
-  static bool attr_set = false;
-  if (!attr_set) {
-    ORION_CUDA_CHECK("paged_decode attr",
-                     cudaFuncSetAttribute(paged_decode_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)kDecodeSmem));
-    attr_set = true;
+  switch (g_decode_stages) {
+    case 2: ORION_TRY(launch_decode_stages<2>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, stream)); break;
+    case 4: ORION_TRY(launch_decode_stages<4>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, stream)); break;
+    default: ORION_TRY(launch_decode_stages<3>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, stream)); break;
   }
-  paged_decode_kernel<<<dim3(kv.num_kv_heads, batch.rows, splits), kWarps * 32, kDecodeSmem,
-                        stream>>>(q, arena, kv, layer, batch, q_heads, splits, scratch, out);
   ORION_TRY(after_launch("paged_decode"));
   if (splits > 1) {
-    decode_combine_kernel<<<dim3(batch.rows, q_heads), kHd, 0, stream>>>(scratch, splits, q_heads,
-                                                                         out);
+    ORION_CUDA_CHECK("decode_combine", launch_pdl(decode_combine_kernel, dim3(batch.rows, q_heads), dim3(kHd), 0,
+                                                  stream, scratch, splits, q_heads, out));
     ORION_TRY(after_launch("decode_combine"));
   }
   return ORION_OK;

@@ -435,7 +435,18 @@ void *orion_cuda_host_alloc(uint64_t bytes) {
 }
 void orion_cuda_host_free(void *p) { if (p) cudaFreeHost(p); }
 
-int orion_cuda_gemm_set_target_ctas(uint32_t ctas) {
+int orion_cuda_set_programmatic_launch(int enabled) {
+  g_pdl_enabled = enabled != 0;
+  return ORION_OK;
+}
+
+int orion_cuda_attention_set_tuning(int stages, uint32_t cta_target) {
+  decode_set_tuning(stages, cta_target);
+  return ORION_OK;
+}
+
+int orion_cuda_gemm_set_tuning(uint32_t ctas, int small_batch_stages) {
+  if (small_batch_stages) gemm_set_small_stages(small_batch_stages);
   gemm_set_target_ctas(ctas);
   return ORION_OK;
 }

@@ -40,6 +40,25 @@ void clear_error();
 extern thread_local uint64_t g_launch_count;
 inline void count_launch() { ++g_launch_count; }
 
+// Launches `kernel` with the programmatic-stream-serialization attribute (see
+// pdl_wait / pdl_trigger below). `enabled` false gives a plain launch.
+extern bool g_pdl_enabled;
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_pdl_enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- storage types ----------------------------------------------------------
 
 using bf16 = __nv_bfloat16;
@@ -144,6 +163,16 @@ __device__ __forceinline__ void tma_load_2d(void *dst_smem, const void *tensor_m
       "l"(tensor_map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
       : "memory");
 }
+
+// Programmatic dependent launch. Every kernel of the step is launched with the
+// programmatic-serialization attribute: it may become resident while its
+// predecessor is still running, and must call pdl_wait() before it touches
+// anything a kernel of the step writes (before the wait only immutable data —
+// weights, norm gains, RoPE tables — may be read). pdl_wait() returns once the
+// predecessor grid has completed and its writes are visible. pdl_trigger() lets
+// the successor start its own prologue. Both are no-ops in a plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -9,6 +9,7 @@
 namespace orion {
 
 thread_local uint64_t g_launch_count = 0;
+bool g_pdl_enabled = true;
 
 namespace {
 
@@ -53,6 +54,8 @@ embed_rmsnorm_kernel(const T *__restrict__ embed, const uint32_t *__restrict__ t
                      T *__restrict__ normed, uint32_t H) {
   using Acc = typename NormAcc<T>::type;
   __shared__ Acc red[32];
+  pdl_trigger();
+  pdl_wait();  // the residual stream and `normed` may still be read by the previous step
   const uint32_t row = blockIdx.x;
   const T *src = embed + (size_t)tokens[row] * H;
   float *h = hidden + (size_t)row * H;
@@ -76,6 +79,8 @@ residual_rmsnorm_kernel(const float *__restrict__ partial, uint32_t splits, size
   using Acc = typename NormAcc<T>::type;
   __shared__ Acc red[32];
   extern __shared__ float row_cache[];  // H floats: the updated residual row
+  pdl_trigger();
+  pdl_wait();
   const uint32_t src_row = row_map ? row_map[blockIdx.x] : blockIdx.x;
   float *h = hidden + (size_t)src_row * H;
   Acc ss = Acc(0);
@@ -97,6 +102,160 @@ residual_rmsnorm_kernel(const float *__restrict__ partial, uint32_t splits, size
     o[c] = from_f32<T>(__fmul_rn(__fmul_rn(row_cache[c], scale), w[c]));
 }
 
+// ---- 128-bit vectorised variants (row widths that are multiples of 4) ------------
+
+__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ float4 add4(float4 a, float4 b) {
+  return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+template <typename T>
+__device__ __forceinline__ void st4(T *dst, float4 v);
+template <>
+__device__ __forceinline__ void st4<float>(float *dst, float4 v) { *reinterpret_cast<float4 *>(dst) = v; }
+template <>
+__device__ __forceinline__ void st4<bf16>(bf16 *dst, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 packed;
+  packed.x = *reinterpret_cast<uint32_t *>(&lo);
+  packed.y = *reinterpret_cast<uint32_t *>(&hi);
+  *reinterpret_cast<uint2 *>(dst) = packed;
+}
+
+// One CTA per output row, up to 1024 threads, CHUNKS float4 groups per thread kept
+// in registers: all loads of a row (residual + every split-K slab) are in flight
+// at once, so a 64-row decode batch costs one memory round trip, not sixteen.
+template <typename T, int CHUNKS>
+__global__ void __launch_bounds__(1024)
+residual_rmsnorm_vec_kernel(const float *__restrict__ partial, uint32_t splits, size_t split_stride,
+                            float *__restrict__ hidden, const float *__restrict__ w, float eps,
+                            T *__restrict__ out, const uint32_t *__restrict__ row_map, uint32_t H) {
+  using Acc = typename NormAcc<T>::type;
+  __shared__ Acc red[32];
+  pdl_trigger();
+  const uint32_t nvec = H / 4;
+  float4 wv[CHUNKS];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {  // gains are immutable: fetched before the dependency wait
+    const uint32_t idx = threadIdx.x + c * blockDim.x;
+    wv[c] = idx < nvec ? ld4(w + 4 * (size_t)idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
+  const uint32_t src_row = row_map ? row_map[blockIdx.x] : blockIdx.x;
+  float *h = hidden + (size_t)src_row * H;
+  float4 v[CHUNKS];
+  Acc ss = Acc(0);
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const uint32_t idx = threadIdx.x + c * blockDim.x;
+    v[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (idx < nvec) {
+      v[c] = ld4(h + 4 * (size_t)idx);
+      if (partial) {
+        const float *p = partial + (size_t)src_row * H + 4 * (size_t)idx;
+        float4 add = ld4(p);
+        for (uint32_t s = 1; s < splits; ++s) add = add4(add, ld4(p + s * split_stride));
+        v[c] = add4(v[c], add);  // hidden += proj, transformer.rs:330-332
+        if (!row_map) *reinterpret_cast<float4 *>(h + 4 * (size_t)idx) = v[c];
+      }
+      ss += (Acc)v[c].x * (Acc)v[c].x + (Acc)v[c].y * (Acc)v[c].y + (Acc)v[c].z * (Acc)v[c].z +
+            (Acc)v[c].w * (Acc)v[c].w;
+    }
+  }
+  const float scale = norm_scale<Acc>(block_sum<Acc>(ss, red), H, eps);
+  T *o = out + (size_t)blockIdx.x * H;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const uint32_t idx = threadIdx.x + c * blockDim.x;
+    if (idx < nvec)
+      st4<T>(o + 4 * (size_t)idx,
+             make_float4(__fmul_rn(__fmul_rn(v[c].x, scale), wv[c].x), __fmul_rn(__fmul_rn(v[c].y, scale), wv[c].y),
+                         __fmul_rn(__fmul_rn(v[c].z, scale), wv[c].z), __fmul_rn(__fmul_rn(v[c].w, scale), wv[c].w)));
+  }
+}
+
+// RoPE + KV-slot write, four rotation pairs per thread: head_dim % 8 == 0.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kvwrite_vec_kernel(const float *__restrict__ partial, uint32_t splits, size_t split_stride,
+                        const float *__restrict__ bias, const uint32_t *__restrict__ positions,
+                        const uint32_t *__restrict__ slot_block, const uint32_t *__restrict__ slot_slot,
+                        const float *__restrict__ rope_cos, const float *__restrict__ rope_sin,
+                        T *__restrict__ q_out, T *__restrict__ arena, KvLayout kv, uint32_t layer,
+                        uint32_t q_heads) {
+  pdl_trigger();
+  pdl_wait();
+  const uint32_t hd = kv.head_dim, half = hd / 2, tph = half / 4;  // threads per head
+  const uint32_t total_heads = q_heads + 2 * kv.num_kv_heads;
+  const uint32_t row = blockIdx.x;
+  const uint32_t head = blockIdx.y * (blockDim.x / tph) + threadIdx.x / tph;
+  if (head >= total_heads) return;
+  const uint32_t i = (threadIdx.x % tph) * 4;
+  const float *p = partial + ((size_t)row * total_heads + head) * hd;
+  float4 x0 = ld4(p + i), x1 = ld4(p + i + half);
+  for (uint32_t s = 1; s < splits; ++s) {
+    x0 = add4(x0, ld4(p + s * split_stride + i));
+    x1 = add4(x1, ld4(p + s * split_stride + i + half));
+  }
+  if (bias) {  // acc + bias, tensor.rs:126
+    x0 = add4(x0, ld4(bias + (size_t)head * hd + i));
+    x1 = add4(x1, ld4(bias + (size_t)head * hd + i + half));
+  }
+  const bool is_q = head < q_heads;
+  const bool is_k = !is_q && head < q_heads + kv.num_kv_heads;
+  if (is_q || is_k) {  // tensor.rs:291-296, products rounded separately like the reference
+    const uint32_t pos = positions[row];
+    const float4 c = ld4(rope_cos + (size_t)pos * half + i), s = ld4(rope_sin + (size_t)pos * half + i);
+    const float4 r0 = make_float4(__fsub_rn(__fmul_rn(x0.x, c.x), __fmul_rn(x1.x, s.x)),
+                                  __fsub_rn(__fmul_rn(x0.y, c.y), __fmul_rn(x1.y, s.y)),
+                                  __fsub_rn(__fmul_rn(x0.z, c.z), __fmul_rn(x1.z, s.z)),
+                                  __fsub_rn(__fmul_rn(x0.w, c.w), __fmul_rn(x1.w, s.w)));
+    const float4 r1 = make_float4(__fadd_rn(__fmul_rn(x0.x, s.x), __fmul_rn(x1.x, c.x)),
+                                  __fadd_rn(__fmul_rn(x0.y, s.y), __fmul_rn(x1.y, c.y)),
+                                  __fadd_rn(__fmul_rn(x0.z, s.z), __fmul_rn(x1.z, c.z)),
+                                  __fadd_rn(__fmul_rn(x0.w, s.w), __fmul_rn(x1.w, c.w)));
+    x0 = r0;
+    x1 = r1;
+  }
+  if (is_q) {
+    T *dst = q_out + ((size_t)row * q_heads + head) * hd;
+    st4<T>(dst + i, x0);
+    st4<T>(dst + i + half, x1);
+  } else {
+    const uint32_t kvh = is_k ? head - q_heads : head - q_heads - kv.num_kv_heads;
+    const uint32_t slot = slot_slot[row];
+    T *dst = arena + kv.row(layer, slot_block[row], kvh, is_k ? 0u : 1u, slot);
+    st4<T>(dst + kv.col(slot, i), x0);  // i % 4 == 0: the four values stay inside one 16-byte group
+    st4<T>(dst + kv.col(slot, i + half), x1);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float silu_f(float g);
+
+// SwiGLU over [rows][2*ffn] partials, four outputs per thread: ffn % 4 == 0.
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_vec_kernel(const float *__restrict__ partial, uint32_t splits, size_t split_stride,
+                  T *__restrict__ act, uint32_t rows, uint32_t ffn) {
+  pdl_trigger();
+  pdl_wait();
+  const uint32_t fv = ffn / 4;
+  const size_t total = (size_t)rows * fv;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = idx / fv, f = (idx % fv) * 4;
+    const float *pg = partial + r * 2 * ffn + f;
+    float4 g = ld4(pg), u = ld4(pg + ffn);
+    for (uint32_t s = 1; s < splits; ++s) {
+      g = add4(g, ld4(pg + s * split_stride));
+      u = add4(u, ld4(pg + s * split_stride + ffn));
+    }
+    st4<T>(act + r * ffn + f,
+           make_float4(__fmul_rn(silu_f<T>(g.x), u.x), __fmul_rn(silu_f<T>(g.y), u.y),
+                       __fmul_rn(silu_f<T>(g.z), u.z), __fmul_rn(silu_f<T>(g.w), u.w)));  // tensor.rs:186
+  }
+}
+
 template <typename T>
 __global__ void rope_kvwrite_kernel(const float *__restrict__ partial, uint32_t splits,
                                     size_t split_stride, const float *__restrict__ bias,
@@ -107,6 +266,8 @@ __global__ void rope_kvwrite_kernel(const float *__restrict__ partial, uint32_t 
                                     const float *__restrict__ rope_sin, T *__restrict__ q_out,
                                     T *__restrict__ arena, KvLayout kv, uint32_t layer,
                                     uint32_t q_heads) {
+  pdl_trigger();
+  pdl_wait();
   const uint32_t row = blockIdx.x, head = blockIdx.y;
   const uint32_t hd = kv.head_dim, half = hd / 2;
   const uint32_t n_total = (q_heads + 2 * kv.num_kv_heads) * hd;
@@ -175,6 +336,8 @@ template <typename T>
 __global__ void swiglu_kernel(const float *__restrict__ partial, uint32_t splits,
                               size_t split_stride, T *__restrict__ act, uint32_t rows,
                               uint32_t ffn) {
+  pdl_trigger();
+  pdl_wait();
   const size_t total = (size_t)rows * ffn;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -192,6 +355,8 @@ __global__ void swiglu_kernel(const float *__restrict__ partial, uint32_t splits
 __global__ void finish_linear_kernel(const float *__restrict__ partial, uint32_t splits,
                                      size_t split_stride, const float *__restrict__ bias,
                                      float *__restrict__ out, uint32_t rows, uint32_t n) {
+  pdl_trigger();
+  pdl_wait();
   const size_t total = (size_t)rows * n;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -205,6 +370,8 @@ __global__ void __launch_bounds__(256)
 argmax_kernel(const float *__restrict__ logits, uint32_t cols, uint32_t *__restrict__ out) {
   __shared__ float s_val[8];
   __shared__ uint32_t s_idx[8];
+  pdl_trigger();
+  pdl_wait();
   const float *row = logits + (size_t)blockIdx.x * cols;
   float best = -INFINITY;
   uint32_t best_i = UINT32_MAX;
@@ -330,10 +497,23 @@ int launch_embed_rmsnorm(const T *embed, const uint32_t *tokens, const float *no
                          float *hidden, T *normed, uint32_t rows, uint32_t hidden_size,
                          cudaStream_t stream) {
   if (rows == 0) return ORION_OK;
-  embed_rmsnorm_kernel<T><<<rows, kNormThreads, 0, stream>>>(embed, tokens, norm_w, eps, hidden,
-                                                             normed, hidden_size);
+  ORION_CUDA_CHECK("embed_rmsnorm", launch_pdl(embed_rmsnorm_kernel<T>, dim3(rows), dim3(kNormThreads), 0,
+                                               stream, embed, tokens, norm_w, eps, hidden, normed,
+                                               hidden_size));
   return after_launch("embed_rmsnorm");
 }
+
+namespace {
+template <typename T, int CHUNKS>
+int launch_residual_vec(const float *partial, uint32_t splits, size_t split_stride, float *hidden,
+                        const float *norm_w, float eps, T *out, const uint32_t *row_map,
+                        uint32_t out_rows, uint32_t H, uint32_t threads, cudaStream_t stream) {
+  ORION_CUDA_CHECK("residual_rmsnorm",
+                   launch_pdl(residual_rmsnorm_vec_kernel<T, CHUNKS>, dim3(out_rows), dim3(threads), 0, stream,
+                              partial, splits, split_stride, hidden, norm_w, eps, out, row_map, H));
+  return after_launch("residual_rmsnorm");
+}
+}  // namespace
 
 template <typename T>
 int launch_residual_rmsnorm(const float *partial, uint32_t splits, size_t split_stride,
@@ -341,6 +521,19 @@ int launch_residual_rmsnorm(const float *partial, uint32_t splits, size_t split_
                             const uint32_t *row_map, uint32_t out_rows, uint32_t hidden_size,
                             cudaStream_t stream) {
   if (out_rows == 0) return ORION_OK;
+  if (hidden_size % 4 == 0 && hidden_size / 4 <= 4096 && split_stride % 4 == 0) {
+    const uint32_t nvec = hidden_size / 4;
+    const uint32_t threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
+    const uint32_t chunks = (nvec + threads - 1) / threads;
+    if (chunks == 1)
+      return launch_residual_vec<T, 1>(partial, splits, split_stride, hidden, norm_w, eps, out, row_map,
+                                       out_rows, hidden_size, threads, stream);
+    if (chunks == 2)
+      return launch_residual_vec<T, 2>(partial, splits, split_stride, hidden, norm_w, eps, out, row_map,
+                                       out_rows, hidden_size, threads, stream);
+    return launch_residual_vec<T, 4>(partial, splits, split_stride, hidden, norm_w, eps, out, row_map,
+                                     out_rows, hidden_size, threads, stream);
+  }
   const size_t smem = (size_t)hidden_size * sizeof(float);
   if (smem > 200 * 1024)
     return set_error(ORION_ERR_INTERNAL, "hidden size %u too large for the fused norm kernel",
@@ -349,8 +542,9 @@ int launch_residual_rmsnorm(const float *partial, uint32_t splits, size_t split_
     ORION_CUDA_CHECK("residual_rmsnorm attr",
                      cudaFuncSetAttribute(residual_rmsnorm_kernel<T>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  residual_rmsnorm_kernel<T><<<out_rows, kNormThreads, smem, stream>>>(
-      partial, splits, split_stride, hidden, norm_w, eps, out, row_map, hidden_size);
+  ORION_CUDA_CHECK("residual_rmsnorm",
+                   launch_pdl(residual_rmsnorm_kernel<T>, dim3(out_rows), dim3(kNormThreads), smem, stream,
+                              partial, splits, split_stride, hidden, norm_w, eps, out, row_map, hidden_size));
   return after_launch("residual_rmsnorm");
 }
 
@@ -369,11 +563,22 @@ int launch_rope_kvwrite(const float *partial, uint32_t splits, size_t split_stri
                         uint32_t q_heads, cudaStream_t stream) {
   if (rows == 0) return ORION_OK;
   const uint32_t half = kv.head_dim / 2;
+  const uint32_t total_heads = q_heads + 2 * kv.num_kv_heads;
+  if (kv.head_dim % 8 == 0 && half / 4 <= 256 && 256 % (half / 4) == 0 && split_stride % 4 == 0) {
+    const uint32_t heads_per_block = 256 / (half / 4);
+    dim3 grid(rows, (total_heads + heads_per_block - 1) / heads_per_block);
+    ORION_CUDA_CHECK("rope_kvwrite",
+                     launch_pdl(rope_kvwrite_vec_kernel<T>, grid, dim3(256), 0, stream, partial, splits,
+                                split_stride, bias, positions, slot_block, slot_slot, rope_cos, rope_sin,
+                                q_out, arena, kv, layer, q_heads));
+    return after_launch("rope_kvwrite");
+  }
   const uint32_t threads = half >= 128 ? 128 : (half < 32 ? 32 : ((half + 31) / 32) * 32);
-  dim3 grid(rows, q_heads + 2 * kv.num_kv_heads);
-  rope_kvwrite_kernel<T><<<grid, threads, 0, stream>>>(partial, splits, split_stride, bias,
-                                                       positions, slot_block, slot_slot, rope_cos,
-                                                       rope_sin, q_out, arena, kv, layer, q_heads);
+  dim3 grid(rows, total_heads);
+  ORION_CUDA_CHECK("rope_kvwrite",
+                   launch_pdl(rope_kvwrite_kernel<T>, grid, dim3(threads), 0, stream, partial, splits,
+                              split_stride, bias, positions, slot_block, slot_slot, rope_cos, rope_sin, q_out,
+                              arena, kv, layer, q_heads));
   return after_launch("rope_kvwrite");
 }
 
@@ -390,9 +595,13 @@ template <typename T>
 int launch_swiglu(const float *partial, uint32_t splits, size_t split_stride, T *act, uint32_t rows,
                   uint32_t ffn, cudaStream_t stream) {
   if (rows == 0 || ffn == 0) return ORION_OK;
-  swiglu_kernel<T><<<grid_for((size_t)rows * ffn, 256), 256, 0, stream>>>(partial, splits,
-                                                                          split_stride, act, rows,
-                                                                          ffn);
+  if (ffn % 4 == 0 && split_stride % 4 == 0) {
+    ORION_CUDA_CHECK("swiglu", launch_pdl(swiglu_vec_kernel<T>, dim3(grid_for((size_t)rows * ffn / 4, 256)),
+                                          dim3(256), 0, stream, partial, splits, split_stride, act, rows, ffn));
+    return after_launch("swiglu");
+  }
+  ORION_CUDA_CHECK("swiglu", launch_pdl(swiglu_kernel<T>, dim3(grid_for((size_t)rows * ffn, 256)), dim3(256), 0,
+                                        stream, partial, splits, split_stride, act, rows, ffn));
   return after_launch("swiglu");
 }
 
@@ -400,15 +609,16 @@ int launch_finish_linear(const float *partial, uint32_t splits, size_t split_str
                          const float *bias, float *out, uint32_t rows, uint32_t n,
                          cudaStream_t stream) {
   if (rows == 0 || n == 0) return ORION_OK;
-  finish_linear_kernel<<<grid_for((size_t)rows * n, 256), 256, 0, stream>>>(
-      partial, splits, split_stride, bias, out, rows, n);
+  ORION_CUDA_CHECK("finish_linear",
+                   launch_pdl(finish_linear_kernel, dim3(grid_for((size_t)rows * n, 256)), dim3(256), 0, stream,
+                              partial, splits, split_stride, bias, out, rows, n));
   return after_launch("finish_linear");
 }
 
 int launch_argmax(const float *logits, uint32_t rows, uint32_t cols, uint32_t *out,
                   cudaStream_t stream) {
   if (rows == 0) return ORION_OK;
-  argmax_kernel<<<rows, 256, 0, stream>>>(logits, cols, out);
+  ORION_CUDA_CHECK("argmax", launch_pdl(argmax_kernel, dim3(rows), dim3(256), 0, stream, logits, cols, out));
   return after_launch("argmax");
 }
 

@@ -29,6 +29,8 @@ gemm_simt_kernel(const T *__restrict__ x, uint32_t ldx, const T *__restrict__ w,
                  float *__restrict__ out, uint32_t M, uint32_t N, uint32_t K) {
   __shared__ float xs[BK][BM + 1];
   __shared__ float ws[BK][BN + 1];
+  pdl_trigger();
+  pdl_wait();
   const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const uint32_t tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // tx -> n, ty -> m
   float acc[TM][TN];
@@ -82,7 +84,8 @@ int launch_gemm_simt(const T *x, uint32_t ldx, const T *w, uint32_t ldw, float *
                      uint32_t n, uint32_t k, cudaStream_t stream) {
   if (rows == 0 || n == 0) return ORION_OK;
   dim3 grid((n + BN - 1) / BN, (rows + BM - 1) / BM);
-  gemm_simt_kernel<T><<<grid, 256, 0, stream>>>(x, ldx, w, ldw, out, rows, n, k);
+  ORION_CUDA_CHECK("gemm_simt", launch_pdl(gemm_simt_kernel<T>, grid, dim3(256), 0, stream, x, ldx, w, ldw, out,
+                                           rows, n, k));
   count_launch();
   ORION_CUDA_CHECK("gemm_simt", cudaGetLastError());
   return ORION_OK;

@@ -38,13 +38,15 @@ constexpr int kThreads = 192;
 
 __device__ uint32_t g_gemm_error = 0;
 
-template <int TOKN>
+// Ring depth is a template parameter. For decode batches (<= 64 tokens) 3 stages = 73 KiB per
+// CTA, so three CTAs fit on an SM: two of the running GEMM and one of its successor, which
+// prefetches its weight tiles while it waits; 4 stages = 97 KiB (two CTAs per SM).
+template <int TOKN, int STAGES>
 struct TcConfig {
   static constexpr int kWBytes = kTileN * kSlabK * 2;
   static constexpr int kXBytes = TOKN * kSlabK * 2;
   static constexpr int kStageBytes = kWBytes + kXBytes;
-  // <= 64 tokens: ~96 KiB so two CTAs share an SM; larger tiles take the SM alone.
-  static constexpr int kStages = TOKN <= 16 ? 5 : (TOKN <= 64 ? 4 : (TOKN == 128 ? 6 : 4));
+  static constexpr int kStages = STAGES;
   static constexpr int kTmemCols = TOKN < 32 ? 32 : TOKN;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -117,11 +119,11 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
          ((uint32_t)(kTileN >> 4) << 24);
 }
 
-template <int TOKN>
+template <int TOKN, int STAGES>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                float *__restrict__ partial, uint32_t M, uint32_t N, uint32_t K, uint32_t splits) {
-  using Cfg = TcConfig<TOKN>;
+  using Cfg = TcConfig<TOKN, STAGES>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                               ~uintptr_t(1023));
@@ -137,6 +139,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t kb_end = (uint32_t)((uint64_t)(split + 1) * nkb / splits);
   const uint32_t my_kb = kb_end - kb_begin;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
       mbar_init(&full[s], 1);
@@ -157,7 +160,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      for (uint32_t i = 0; i < my_kb; ++i) {
+      // Weights are immutable, so the first ring fill streams them while the
+      // kernel that produces the activations is still running; only the
+      // activation tiles wait for it.
+      const uint32_t pre = my_kb < (uint32_t)Cfg::kStages ? my_kb : (uint32_t)Cfg::kStages;
+      for (uint32_t i = 0; i < pre; ++i) {
+        uint8_t *wt = smem + i * Cfg::kStageBytes;
+        mbar_arrive_expect_tx(&full[i], Cfg::kStageBytes);
+        tma_load_2d(wt, &map_w, (int)((kb_begin + i) * kSlabK), (int)n0, &full[i]);
+      }
+      pdl_wait();
+      for (uint32_t i = 0; i < pre; ++i) {
+        uint8_t *xt = smem + i * Cfg::kStageBytes + Cfg::kWBytes;
+        tma_load_2d(xt, &map_x, (int)((kb_begin + i) * kSlabK), (int)t0, &full[i]);
+      }
+      for (uint32_t i = pre; i < my_kb; ++i) {
         const uint32_t s = i % Cfg::kStages, use = i / Cfg::kStages;
         if (!mbar_wait(&empty[s], (use & 1) ^ 1)) { ok = false; break; }
         uint8_t *wt = smem + s * Cfg::kStageBytes;
@@ -195,6 +212,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!mbar_wait(acc_ready, 0)) ok = false;
     }
     tc_fence_after();
+    pdl_wait();  // the partial buffer may still be read by the kernel before the producer of x
     const uint32_t n = n0 + lq * 32 + lane;
     float *dst = partial + (size_t)split * M * N;
 #pragma unroll 1
@@ -287,14 +305,14 @@ int cached_map(const void *base, uint64_t rows, uint64_t k, uint64_t ld, uint32_
   return ORION_OK;
 }
 
-template <int TOKN>
+template <int TOKN, int STAGES>
 int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
               uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream) {
-  using Cfg = TcConfig<TOKN>;
+  using Cfg = TcConfig<TOKN, STAGES>;
   static bool attr_set = false;
   if (!attr_set) {
     ORION_CUDA_CHECK("gemm_tc attr",
-                     cudaFuncSetAttribute(gemm_tc_kernel<TOKN>,
+                     cudaFuncSetAttribute(gemm_tc_kernel<TOKN, STAGES>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           Cfg::kSmemBytes));
     attr_set = true;
@@ -303,12 +321,14 @@ int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *p
   ORION_TRY(cached_map(w, n, k, ldw, kTileN, &mw));
   ORION_TRY(cached_map(x, rows, k, ldx, TOKN, &mx));
   dim3 grid((n + kTileN - 1) / kTileN, (rows + TOKN - 1) / TOKN, splits);
-  gemm_tc_kernel<TOKN><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(*mw, *mx, partial, rows, n, k,
-                                                                    splits);
+  ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, STAGES>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
+                                         *mw, *mx, partial, rows, n, k, splits));
   count_launch();
   ORION_CUDA_CHECK("gemm_tc", cudaGetLastError());
   return ORION_OK;
 }
+
+int g_small_stages = 4;  // ring depth for token tiles <= 64 (4: two CTAs per SM, 3: three)
 
 uint32_t token_tile(uint32_t rows) {
   if (rows <= 16) return 16;
@@ -332,12 +352,19 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
   const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
   if (splits < 1 || splits > nkb)
     return set_error(ORION_ERR_INTERNAL, "gemm split count %u outside 1..%u", splits, nkb);
+  const bool deep = g_small_stages >= 4;
   switch (token_tile(rows)) {
-    case 16: return launch_tc<16>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
-    case 32: return launch_tc<32>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
-    case 64: return launch_tc<64>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
-    case 128: return launch_tc<128>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
-    default: return launch_tc<256>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+    case 16:
+      return deep ? launch_tc<16, 5>(x, ldx, w, ldw, partial, rows, n, k, splits, stream)
+                  : launch_tc<16, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+    case 32:
+      return deep ? launch_tc<32, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, stream)
+                  : launch_tc<32, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+    case 64:
+      return deep ? launch_tc<64, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, stream)
+                  : launch_tc<64, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+    case 128: return launch_tc<128, 6>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+    default: return launch_tc<256, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
   }
 }
 
@@ -355,10 +382,11 @@ int gemm_tc_poll_error(uint32_t *code) {
 // ---- planning and dispatch -------------------------------------------------------
 
 namespace {
-uint32_t g_target_ctas = 148;  // one wave of the 148 SMs
+uint32_t g_target_ctas = 296;  // two CTAs fit on each of the 148 SMs
 }
 
-void gemm_set_target_ctas(uint32_t v) { g_target_ctas = v ? v : 148; }
+void gemm_set_target_ctas(uint32_t v) { g_target_ctas = v ? v : 296; }
+void gemm_set_small_stages(int stages) { g_small_stages = stages >= 4 ? 4 : 3; }
 
 GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx,
                    uint32_t ldw) {

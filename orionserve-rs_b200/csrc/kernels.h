@@ -142,6 +142,8 @@ uint32_t decode_choose_splits(uint32_t rows, uint32_t kv_heads, uint32_t max_pos
 int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer,
                                   AttnBatch batch, uint32_t q_heads, uint32_t splits,
                                   DecodeScratch scratch, bf16 *out, cudaStream_t stream);
+// Tuning: ring depth per warp (2..4) and the CTA count the context split aims for (0 keeps it).
+void decode_set_tuning(int stages, uint32_t cta_target);
 // Device error word of the decode kernel (0 = none); reading clears it.
 int decode_poll_error(uint32_t *code);
 
@@ -161,6 +163,8 @@ int launch_gemm(const T *x, uint32_t ldx, const T *w, uint32_t ldw, float *parti
 size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t k);
 // Number of CTAs split-K aims for on small batches (default 148, one per SM).
 void gemm_set_target_ctas(uint32_t ctas);
+// Ring depth of the decode-batch GEMM (3 or 4 stages).
+void gemm_set_small_stages(int stages);
 
 // SIMT GEMM: exact k-ascending accumulation per output, no FMA for f32.
 template <typename T>

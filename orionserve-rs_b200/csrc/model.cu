@@ -6,6 +6,7 @@
 #include "model.h"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace orion {
@@ -146,6 +147,10 @@ class Model final : public ModelBase {
   }
   template <typename F>
   int timed(int cat, F &&fn) {
+    // Timing diagnostic only: ORION_DEBUG_SKIP is a bit mask of kernel categories to leave out
+    // of the step (results are then meaningless; used to attribute step time under overlap).
+    static const int skip = std::getenv("ORION_DEBUG_SKIP") ? std::atoi(std::getenv("ORION_DEBUG_SKIP")) : 0;
+    if (skip & (1 << cat)) return ORION_OK;
     if (!prof_on_) return fn();
     cudaEvent_t a = prof_event(), b = prof_event();
     cudaEventRecord(a, stream_);
