@@ -1,0 +1,44 @@
+"""Tensor-parallel path: world-size-2 gloo ranks on CPU (sharded oracle + collectives), and
+NCCL ranks on 2 GPUs when the box has them."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+from conftest import ROOT
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run_ranks(world: int, *worker_args: str, timeout: int = 600):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "tests", "tp_worker.py"), *worker_args]
+    env = dict(os.environ, OMP_NUM_THREADS="1", NCCL_NVLS_ENABLE="0")
+    return subprocess.run(cmd, cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                          timeout=timeout)
+
+
+def test_two_gloo_ranks_reproduce_the_unsharded_forward():
+    r = _run_ranks(2, "--mode", "cpu")
+    assert r.returncode == 0, r.stdout[-3000:]
+
+
+def test_four_gloo_ranks_reproduce_the_unsharded_forward():
+    r = _run_ranks(4, "--mode", "cpu")
+    assert r.returncode == 0, r.stdout[-3000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["F32", "BF16"])
+def test_two_gpu_ranks_match_the_oracle(pkg, dtype):
+    if pkg.device_count() < 2:
+        pytest.skip("needs two GPUs on the box")
+    r = _run_ranks(2, "--mode", "gpu", "--dtype", dtype)
+    assert r.returncode == 0, r.stdout[-3000:]
