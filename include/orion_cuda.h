@@ -189,6 +189,10 @@ int orion_cuda_model_desc(const OrionModel *model, OrionModelDesc *out);
  * here is written by DMA directly, a pageable one goes through a bounce copy. */
 void *orion_cuda_host_alloc(uint64_t bytes);
 void orion_cuda_host_free(void *ptr);
+/* Tuning knob: bytes of the NEXT projection's weights that each heavy kernel of a
+ * decode step asks L2 to prefetch once its own loads are issued (default 0 = off,
+ * measured neutral at batch 64). */
+int orion_cuda_set_l2_prefetch_bytes(uint64_t bytes);
 /* Tuning knob: launch the kernels of a step with programmatic dependent launch
  * (each kernel's prologue and weight prefetch overlap its predecessor's tail).
  * On by default; 0 gives plain stream-ordered launches. */
@@ -224,6 +228,12 @@ int orion_cuda_linear(OrionBackend *backend, int dtype, const float *x, uint64_t
                       uint64_t in_features, const float *weight, uint64_t out_features,
                       uint64_t weight_in_features, const float *bias, uint64_t bias_len,
                       float *out);
+/* Device-resident timing of the bf16 tensor::linear kernel on N(0,1) operands:
+ * mean milliseconds per launch over `iterations` back-to-back launches, and the
+ * split-K factor the planner chose. */
+int orion_cuda_linear_bench(OrionBackend *backend, uint64_t rows, uint64_t in_features,
+                            uint64_t out_features, int warmup, int iterations, float *mean_ms,
+                            uint32_t *splits_used);
 /* tensor::rms_norm (tensor.rs:143-163), in place. */
 int orion_cuda_rms_norm(OrionBackend *backend, int dtype, float *x, uint64_t rows, uint64_t cols,
                         const float *weight, uint64_t weight_len, float eps);

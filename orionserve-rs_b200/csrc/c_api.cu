@@ -435,6 +435,11 @@ void *orion_cuda_host_alloc(uint64_t bytes) {
 }
 void orion_cuda_host_free(void *p) { if (p) cudaFreeHost(p); }
 
+int orion_cuda_set_l2_prefetch_bytes(uint64_t bytes) {
+  model_set_prefetch_budget((size_t)bytes);
+  return ORION_OK;
+}
+
 int orion_cuda_set_programmatic_launch(int enabled) {
   g_pdl_enabled = enabled != 0;
   return ORION_OK;
@@ -539,6 +544,45 @@ int orion_cuda_paged_attention(OrionBackend *backend, int dtype, const float *kv
     return op_attention<bf16>(kv, num_blocks, block_size, num_kv_heads, head_dim, query, rows, num_query_heads,
                               query_positions, seq_of_row, block_tables_flat, block_table_offsets, num_sequences, out);
   return bad_dtype(dtype);
+}
+
+int orion_cuda_linear_bench(OrionBackend *backend, uint64_t rows, uint64_t in_features, uint64_t out_features,
+                            int warmup, int iterations, float *mean_ms, uint32_t *splits_used) {
+  clear_error();
+  ORION_TRY(check_backend(backend));
+  Dev<bf16> x, w;
+  Dev<float> part;
+  ORION_TRY(x.alloc(rows * in_features));
+  ORION_TRY(w.alloc(out_features * in_features));
+  ORION_TRY(launch_fill_normal<bf16>(x.p, rows * in_features, 11, 0));
+  ORION_TRY(launch_fill_normal<bf16>(w.p, out_features * in_features, 12, 0));
+  GemmPlan p = gemm_plan(true, (uint32_t)rows, (uint32_t)out_features, (uint32_t)in_features,
+                         (uint32_t)in_features, (uint32_t)in_features);
+  if (!p.tensor_core) return set_error(ORION_ERR_INVALID_REQUEST, "shape is not covered by the tensor-core GEMM");
+  ORION_TRY(part.alloc((size_t)p.splits * rows * out_features));
+  cudaEvent_t e0, e1;
+  ORION_CUDA_CHECK("create event", cudaEventCreate(&e0));
+  ORION_CUDA_CHECK("create event", cudaEventCreate(&e1));
+  int rc = ORION_OK;
+  for (int i = 0; i < warmup + iterations && rc == ORION_OK; ++i) {
+    if (i == warmup) cudaEventRecord(e0, 0);
+    rc = launch_gemm<bf16>(x.p, (uint32_t)in_features, w.p, (uint32_t)in_features, part.p, (uint32_t)rows,
+                           (uint32_t)out_features, (uint32_t)in_features, p, 0);
+  }
+  cudaEventRecord(e1, 0);
+  cudaError_t e = cudaEventSynchronize(e1);
+  float ms = 0.f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  ORION_TRY(rc);
+  ORION_CUDA_CHECK("linear bench", e);
+  uint32_t code = 0;
+  ORION_TRY(gemm_tc_poll_error(&code));
+  if (code) return set_error(ORION_ERR_BACKEND, "backend cuda failed at gemm: a bounded pipeline wait ran out (code %u)", code);
+  if (mean_ms) *mean_ms = iterations > 0 ? ms / iterations : 0.f;
+  if (splits_used) *splits_used = p.splits;
+  return ORION_OK;
 }
 
 int orion_cuda_argmax(OrionBackend *backend, const float *logits, uint64_t rows, uint64_t cols, uint32_t *out) {

@@ -7,13 +7,14 @@
 // byte exactly once. W [n][k] and x [r][k] are both K-major as stored, so no
 // transposition is needed.
 //
-// Per CTA (192 threads):
-//   warp 0   one lane issues TMA tensor loads (128B-swizzled 64-wide k slabs of
-//            the W tile and the x tile) into a multi-stage ring, completion
-//            counted on "full" mbarriers;
+// Per CTA (256 threads):
+//   warp 0   one lane streams the W tile (TMA tensor loads, 128B-swizzled 64-wide k
+//            slabs) into the deep weight ring; it never waits for the preceding kernel;
+//   warp 2   one lane waits for the preceding kernel (programmatic dependent launch),
+//            then keeps the short activation ring full (x tiles come from L2);
 //   warp 1   allocates tensor memory, one lane issues tcgen05.mma (128 x TOKN x 16,
-//            four per k slab) and commits to the "empty" barrier of the stage;
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (lane = weight row, column =
+//            four per k slab) and commits to the "empty" barriers of both stages;
+//   warps 4-7 epilogue: tcgen05.ld the accumulator (lane = weight row, column =
 //            token) and store f32 partials, 128 contiguous bytes per warp store.
 // Split-K: blockIdx.z owns a contiguous range of k slabs and writes its own slab
 // of the partial buffer; the consumer kernel sums the slabs.
@@ -34,21 +35,25 @@ namespace {
 constexpr int kTileN = 128;   // weight rows per CTA (M of the MMA)
 constexpr int kSlabK = 64;    // k elements per stage: 128 bytes = one swizzle atom
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 192;
+constexpr int kThreads = 256;
 
 __device__ uint32_t g_gemm_error = 0;
 
-// Ring depth is a template parameter. For decode batches (<= 64 tokens) 3 stages = 73 KiB per
-// CTA, so three CTAs fit on an SM: two of the running GEMM and one of its successor, which
-// prefetches its weight tiles while it waits; 4 stages = 97 KiB (two CTAs per SM).
-template <int TOKN, int STAGES>
+// Two rings per CTA. Weight tiles come from HBM (long latency, the stream that must never
+// stall): WST stages of 16 KiB. Activation tiles come from L2 (every CTA re-reads them):
+// XST stages of TOKN x 128 B are enough. Measured on decode shapes, weight bandwidth follows
+// the weight bytes in flight per SM (160 KiB -> 6.0 TB/s, 128 KiB -> 5.3 TB/s), so shared
+// memory goes to the W ring first.
+template <int TOKN, int WST, int XST>
 struct TcConfig {
   static constexpr int kWBytes = kTileN * kSlabK * 2;
   static constexpr int kXBytes = TOKN * kSlabK * 2;
-  static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kStages = STAGES;
+  static constexpr int kWStages = WST;
+  static constexpr int kXStages = XST;
+  static constexpr int kXRingOffset = WST * kWBytes;
+  static constexpr int kBarrierOffset = kXRingOffset + XST * kXBytes;
   static constexpr int kTmemCols = TOKN < 32 ? 32 : TOKN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kBarrierOffset + 1024 /*align*/ + 512 /*barriers*/;
 };
 
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t ncols) {
@@ -119,17 +124,21 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
          ((uint32_t)(kTileN >> 4) << 24);
 }
 
-template <int TOKN, int STAGES>
+template <int TOKN, int WST, int XST>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               float *__restrict__ partial, uint32_t M, uint32_t N, uint32_t K, uint32_t splits) {
-  using Cfg = TcConfig<TOKN, STAGES>;
+               float *__restrict__ partial, uint32_t M, uint32_t N, uint32_t K, uint32_t splits,
+               PrefetchHint next) {
+  using Cfg = TcConfig<TOKN, WST, XST>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                               ~uintptr_t(1023));
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem + Cfg::kStages * Cfg::kStageBytes);
-  uint64_t *empty = full + Cfg::kStages;
-  uint64_t *acc_ready = empty + Cfg::kStages;
+  uint8_t *w_ring = smem, *x_ring = smem + Cfg::kXRingOffset;
+  uint64_t *full_w = reinterpret_cast<uint64_t *>(smem + Cfg::kBarrierOffset);
+  uint64_t *empty_w = full_w + WST;
+  uint64_t *full_x = empty_w + WST;
+  uint64_t *empty_x = full_x + XST;
+  uint64_t *acc_ready = empty_x + XST;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -141,9 +150,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   pdl_trigger();
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::kStages; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+    for (int s = 0; s < WST; ++s) {
+      mbar_init(&full_w[s], 1);
+      mbar_init(&empty_w[s], 1);
+    }
+    for (int s = 0; s < XST; ++s) {
+      mbar_init(&full_x[s], 1);
+      mbar_init(&empty_x[s], 1);
     }
     mbar_init(acc_ready, 1);
     mbar_fence_init();
@@ -159,41 +172,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   bool ok = true;
 
   if (warp == 0) {
+    // Weight producer. Weights are immutable, so this stream starts while the kernel that
+    // produces the activations is still running and never waits for it.
     if (lane == 0) {
-      // Weights are immutable, so the first ring fill streams them while the
-      // kernel that produces the activations is still running; only the
-      // activation tiles wait for it.
-      const uint32_t pre = my_kb < (uint32_t)Cfg::kStages ? my_kb : (uint32_t)Cfg::kStages;
-      for (uint32_t i = 0; i < pre; ++i) {
-        uint8_t *wt = smem + i * Cfg::kStageBytes;
-        mbar_arrive_expect_tx(&full[i], Cfg::kStageBytes);
-        tma_load_2d(wt, &map_w, (int)((kb_begin + i) * kSlabK), (int)n0, &full[i]);
+      for (uint32_t i = 0; i < my_kb; ++i) {
+        const uint32_t s = i % WST, use = i / WST;
+        if (!mbar_wait(&empty_w[s], (use & 1) ^ 1)) { ok = false; break; }
+        mbar_arrive_expect_tx(&full_w[s], Cfg::kWBytes);
+        tma_load_2d(w_ring + s * Cfg::kWBytes, &map_w, (int)((kb_begin + i) * kSlabK), (int)n0, &full_w[s]);
       }
+      prefetch_slice(next);  // own loads are all issued: start pulling the next GEMM's weights into L2
+    }
+  } else if (warp == 2) {
+    // Activation producer: waits for the preceding kernel, then keeps the short x ring full.
+    if (lane == 0) {
       pdl_wait();
-      for (uint32_t i = 0; i < pre; ++i) {
-        uint8_t *xt = smem + i * Cfg::kStageBytes + Cfg::kWBytes;
-        tma_load_2d(xt, &map_x, (int)((kb_begin + i) * kSlabK), (int)t0, &full[i]);
-      }
-      for (uint32_t i = pre; i < my_kb; ++i) {
-        const uint32_t s = i % Cfg::kStages, use = i / Cfg::kStages;
-        if (!mbar_wait(&empty[s], (use & 1) ^ 1)) { ok = false; break; }
-        uint8_t *wt = smem + s * Cfg::kStageBytes;
-        uint8_t *xt = wt + Cfg::kWBytes;
-        mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
-        const int kc = (int)((kb_begin + i) * kSlabK);
-        tma_load_2d(wt, &map_w, kc, (int)n0, &full[s]);
-        tma_load_2d(xt, &map_x, kc, (int)t0, &full[s]);
+      for (uint32_t i = 0; i < my_kb; ++i) {
+        const uint32_t s = i % XST, use = i / XST;
+        if (!mbar_wait(&empty_x[s], (use & 1) ^ 1)) { ok = false; break; }
+        mbar_arrive_expect_tx(&full_x[s], Cfg::kXBytes);
+        tma_load_2d(x_ring + s * Cfg::kXBytes, &map_x, (int)((kb_begin + i) * kSlabK), (int)t0, &full_x[s]);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc<TOKN>();
       for (uint32_t i = 0; i < my_kb; ++i) {
-        const uint32_t s = i % Cfg::kStages, use = i / Cfg::kStages;
-        if (!mbar_wait(&full[s], use & 1)) { ok = false; break; }
+        const uint32_t sw = i % WST, sx = i % XST;
+        if (!mbar_wait(&full_w[sw], (i / WST) & 1) || !mbar_wait(&full_x[sx], (i / XST) & 1)) {
+          ok = false;
+          break;
+        }
         tc_fence_after();
-        const uint32_t wt = smem_u32(smem + s * Cfg::kStageBytes);
-        const uint32_t xt = wt + Cfg::kWBytes;
+        const uint32_t wt = smem_u32(w_ring + sw * Cfg::kWBytes);
+        const uint32_t xt = smem_u32(x_ring + sx * Cfg::kXBytes);
 #pragma unroll
         for (int k = 0; k < kSlabK / kUmmaK; ++k) {
           // advancing 16 k elements inside the swizzle atom = +32 bytes on the start address
@@ -201,11 +213,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const uint64_t b = smem_desc_sw128(xt + k * kUmmaK * 2);
           umma_bf16(tmem_base, a, b, idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+        umma_commit(&empty_w[sw]);  // both stages are free once these MMAs have read them
+        umma_commit(&empty_x[sx]);
       }
-      umma_commit(acc_ready);    // arrives when every MMA above has completed
+      umma_commit(acc_ready);  // arrives when every MMA above has completed
     }
-  } else {
+  } else if (warp >= 4) {
     // Epilogue warps: warp w may touch tensor-memory lanes 32*(w%4) .. +31.
     const uint32_t lq = warp & 3;
     if (my_kb > 0) {
@@ -305,14 +318,15 @@ int cached_map(const void *base, uint64_t rows, uint64_t k, uint64_t ld, uint32_
   return ORION_OK;
 }
 
-template <int TOKN, int STAGES>
+template <int TOKN, int WST, int XST>
 int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
-              uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream) {
-  using Cfg = TcConfig<TOKN, STAGES>;
+              uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, PrefetchHint next, cudaStream_t stream) {
+  using Cfg = TcConfig<TOKN, WST, XST>;
+  static_assert(Cfg::kSmemBytes <= 232448, "ring exceeds the shared memory of an SM");
   static bool attr_set = false;
   if (!attr_set) {
     ORION_CUDA_CHECK("gemm_tc attr",
-                     cudaFuncSetAttribute(gemm_tc_kernel<TOKN, STAGES>,
+                     cudaFuncSetAttribute(gemm_tc_kernel<TOKN, WST, XST>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           Cfg::kSmemBytes));
     attr_set = true;
@@ -321,14 +335,14 @@ int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *p
   ORION_TRY(cached_map(w, n, k, ldw, kTileN, &mw));
   ORION_TRY(cached_map(x, rows, k, ldx, TOKN, &mx));
   dim3 grid((n + kTileN - 1) / kTileN, (rows + TOKN - 1) / TOKN, splits);
-  ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, STAGES>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
-                                         *mw, *mx, partial, rows, n, k, splits));
+  ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, WST, XST>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
+                                         *mw, *mx, partial, rows, n, k, splits, next));
   count_launch();
   ORION_CUDA_CHECK("gemm_tc", cudaGetLastError());
   return ORION_OK;
 }
 
-int g_small_stages = 4;  // ring depth for token tiles <= 64 (4: two CTAs per SM, 3: three)
+int g_small_stages = 5;  // 5: deep weight ring + short activation ring for decode batches; 4: equal rings
 
 uint32_t token_tile(uint32_t rows) {
   if (rows <= 16) return 16;
@@ -348,23 +362,24 @@ bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint
 }
 
 int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
-                   uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream) {
+                   uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream,
+                   PrefetchHint next) {
   const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
   if (splits < 1 || splits > nkb)
     return set_error(ORION_ERR_INTERNAL, "gemm split count %u outside 1..%u", splits, nkb);
-  const bool deep = g_small_stages >= 4;
+  const bool deep = g_small_stages >= 5;
   switch (token_tile(rows)) {
     case 16:
-      return deep ? launch_tc<16, 5>(x, ldx, w, ldw, partial, rows, n, k, splits, stream)
-                  : launch_tc<16, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+      return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream)
+                  : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream);
     case 32:
-      return deep ? launch_tc<32, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, stream)
-                  : launch_tc<32, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+      return deep ? launch_tc<32, 6, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream)
+                  : launch_tc<32, 5, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream);
     case 64:
-      return deep ? launch_tc<64, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, stream)
-                  : launch_tc<64, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
-    case 128: return launch_tc<128, 6>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
-    default: return launch_tc<256, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, stream);
+      return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream)
+                  : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream);
+    case 128: return launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream);
+    default: return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream);
   }
 }
 
@@ -386,7 +401,7 @@ uint32_t g_target_ctas = 296;  // two CTAs fit on each of the 148 SMs
 }
 
 void gemm_set_target_ctas(uint32_t v) { g_target_ctas = v ? v : 296; }
-void gemm_set_small_stages(int stages) { g_small_stages = stages >= 4 ? 4 : 3; }
+void gemm_set_small_stages(int stages) { g_small_stages = stages >= 5 ? 5 : 4; }
 
 GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx,
                    uint32_t ldw) {
@@ -422,17 +437,18 @@ size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t
 
 template <>
 int launch_gemm<float>(const float *x, uint32_t ldx, const float *w, uint32_t ldw, float *partial,
-                       uint32_t rows, uint32_t n, uint32_t k, GemmPlan, cudaStream_t stream) {
+                       uint32_t rows, uint32_t n, uint32_t k, GemmPlan, cudaStream_t stream, PrefetchHint) {
   return launch_gemm_simt<float>(x, ldx, w, ldw, partial, rows, n, k, stream);
 }
 
 template <>
 int launch_gemm<bf16>(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
-                      uint32_t rows, uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream) {
+                      uint32_t rows, uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream,
+                      PrefetchHint next) {
   if (plan.tensor_core) {
     if (!gemm_tc_supported(rows, n, k, ldx, ldw, x, w))
       return set_error(ORION_ERR_INTERNAL, "tensor-core GEMM planned for an unaligned operand");
-    return launch_gemm_tc(x, ldx, w, ldw, partial, rows, n, k, plan.splits, stream);
+    return launch_gemm_tc(x, ldx, w, ldw, partial, rows, n, k, plan.splits, stream, next);
   }
   return launch_gemm_simt<bf16>(x, ldx, w, ldw, partial, rows, n, k, stream);
 }

@@ -141,7 +141,8 @@ uint32_t decode_choose_splits(uint32_t rows, uint32_t kv_heads, uint32_t max_pos
                               uint32_t block_size, uint32_t max_splits);
 int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer,
                                   AttnBatch batch, uint32_t q_heads, uint32_t splits,
-                                  DecodeScratch scratch, bf16 *out, cudaStream_t stream);
+                                  DecodeScratch scratch, bf16 *out, cudaStream_t stream,
+                                  PrefetchHint next = {});
 // Tuning: ring depth per warp (2..4) and the CTA count the context split aims for (0 keeps it).
 void decode_set_tuning(int stages, uint32_t cta_target);
 // Device error word of the decode kernel (0 = none); reading clears it.
@@ -159,7 +160,7 @@ struct GemmPlan {
 GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint32_t ldw);
 template <typename T>
 int launch_gemm(const T *x, uint32_t ldx, const T *w, uint32_t ldw, float *partial, uint32_t rows,
-                uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream);
+                uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream, PrefetchHint next = {});
 size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t k);
 // Number of CTAs split-K aims for on small batches (default 148, one per SM).
 void gemm_set_target_ctas(uint32_t ctas);
@@ -174,7 +175,8 @@ int launch_gemm_simt(const T *x, uint32_t ldx, const T *w, uint32_t ldw, float *
 bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint32_t ldw,
                        const void *x, const void *w);
 int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
-                   uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream);
+                   uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream,
+                   PrefetchHint next = {});
 // Device error word set by kernels whose bounded waits ran out (0 = none).
 int gemm_tc_poll_error(uint32_t *code);
 
