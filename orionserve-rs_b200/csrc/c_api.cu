@@ -195,6 +195,30 @@ int op_attention(const float *kv, uint64_t num_blocks, uint64_t block_size, uint
       done = true;
     }
   }
+  if constexpr (sizeof(T) == 2) {
+    if (!done && prefill_attention_supported(lay, (uint32_t)qh)) {
+      // tiles of consecutive rows of one sequence, like the model builds them
+      const uint32_t tile_rows = prefill_tile_positions((uint32_t)qh, (uint32_t)kvh);
+      std::vector<PrefillTile> tiles;
+      for (uint64_t r = 0; r < rows;) {
+        PrefillTile t{(uint32_t)r, 0, seq_of_row[r], 0};
+        while (r < rows && seq_of_row[r] == t.seq && t.num_rows < tile_rows) {
+          t.max_position = std::max(t.max_position, qpos[r]);
+          ++t.num_rows;
+          ++r;
+        }
+        tiles.push_back(t);
+      }
+      Dev<PrefillTile> dt;
+      ORION_TRY(dt.upload(tiles.data(), tiles.size()));
+      ORION_TRY(launch_paged_attention_prefill(qt.p, arena.p, lay, 0, ab, dt.p, (uint32_t)tiles.size(), (uint32_t)qh, ot.p, 0));
+      ORION_CUDA_CHECK("paged_attention", cudaDeviceSynchronize());
+      uint32_t code = 0;
+      ORION_TRY(prefill_poll_error(&code));
+      if (code) return set_error(ORION_ERR_BACKEND, "backend cuda failed at prefill attention: a bounded pipeline wait ran out (code %u)", code);
+      done = true;
+    }
+  }
   if (!done) ORION_TRY(launch_paged_attention_generic<T>(qt.p, arena.p, lay, 0, ab, (uint32_t)qh, ot.p, 0));
   ORION_TRY(launch_convert_to_f32<T>(ot.p, back.p, qn, 0));
   ORION_CUDA_CHECK("paged_attention", cudaMemcpy(out, back.p, qn * sizeof(float), cudaMemcpyDeviceToHost));

@@ -126,6 +126,22 @@ template <typename T>
 int launch_paged_attention_generic(const T *q, const T *arena, KvLayout kv, uint32_t layer,
                                    AttnBatch batch, uint32_t q_heads, T *out, cudaStream_t stream);
 
+// Tuned prefill / mixed-batch path (bf16, head_dim 128, block 16): the batch is cut into
+// tiles of consecutive rows of one sequence (prefill_tile_positions rows at most); one CTA per
+// (kv head, tile) streams the sequence's K/V once for all rows of the tile.
+struct PrefillTile {
+  uint32_t row_start;     // first batch row of the tile
+  uint32_t num_rows;      // rows (query positions) in the tile
+  uint32_t seq;           // sequence the rows belong to
+  uint32_t max_position;  // largest query position in the tile
+};
+bool prefill_attention_supported(KvLayout kv, uint32_t q_heads);
+uint32_t prefill_tile_positions(uint32_t q_heads, uint32_t kv_heads);
+int launch_paged_attention_prefill(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer,
+                                   AttnBatch batch, const PrefillTile *tiles, uint32_t num_tiles,
+                                   uint32_t q_heads, bf16 *out, cudaStream_t stream);
+int prefill_poll_error(uint32_t *code);
+
 // Tuned decode path (bf16, head_dim 128, block 16, one query row per sequence):
 // one CTA per (sequence, kv head, context split); the query heads of a GQA group
 // share every K/V tile. `scratch` holds the per-split partial outputs.

@@ -194,7 +194,8 @@ class Model final : public ModelBase {
     uint32_t rows = 0, seqs = 0, max_position = 0;
     bool decode = false, zero_count = false;
     size_t tokens = 0, positions = 0, slot_block = 0, slot_slot = 0, seq_of_row = 0, last_rows = 0,
-           offsets = 0, tables = 0, total = 0;
+           offsets = 0, tables = 0, tiles = 0, total = 0;
+    uint32_t num_tiles = 0;  // prefill attention tiles (0 = the batch does not use that kernel)
   } meta_;
 
   void *stage_raw_ = nullptr, *stage_f32_ = nullptr;
@@ -567,6 +568,11 @@ int Model<T>::run_step(bool want_argmax) {
         ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_decode(qbuf_, arena_, kv_, l, ab, lq_, dsplits, sc, attn_, stream_,
                                                                                      hint(L.w_o, (size_t)H * qd)); }));
       }
+    } else if (meta_.num_tiles > 0) {
+      if constexpr (kBf16) {
+        const PrefillTile *tiles = reinterpret_cast<const PrefillTile *>(m + meta_.tiles);
+        ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_prefill(qbuf_, arena_, kv_, l, ab, tiles, meta_.num_tiles, lq_, attn_, stream_); }));
+      }
     } else {
       ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_generic<T>(qbuf_, arena_, kv_, l, ab, lq_, attn_, stream_); }));
     }
@@ -650,7 +656,12 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
   mt.last_rows = 5 * Tn;
   mt.offsets = 5 * Tn + S;
   mt.tables = 5 * Tn + 2 * S + 1;
-  mt.total = mt.tables + table_entries;
+  mt.tiles = mt.tables + table_entries;
+  constexpr bool kBf16Build = DTypeOf<T>::is_bf16;
+  const bool tuned_prefill = kBf16Build && prefill_attention_supported(kv_, lq_);
+  const uint32_t tile_rows = tuned_prefill ? prefill_tile_positions(lq_, lkv_) : 0;
+  const size_t max_tiles = tile_rows ? S + Tn / tile_rows + 1 : 0;
+  mt.total = mt.tiles + 4 * max_tiles;
   if (table_entries > UINT32_MAX) return set_error(ORION_ERR_INVALID_REQUEST, "block tables too large");
   if (mt.total > meta_cap_) {
     const size_t cap = mt.total * 2 + 1024;
@@ -715,6 +726,26 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
   }
   if (table_entries) std::memcpy(h + mt.tables, b.block_tables_flat, table_entries * sizeof(uint32_t));
   mt.decode = all_single;
+  if (tuned_prefill && !all_single) {
+    // Tiles of consecutive rows of one sequence for the prefill attention kernel.
+    uint32_t *t = h + mt.tiles;
+    uint64_t row = 0;
+    for (uint64_t s = 0; s < S; ++s) {
+      const uint64_t end = row + b.slot_token_counts[s];
+      while (row < end) {
+        const uint32_t n = (uint32_t)std::min<uint64_t>(tile_rows, end - row);
+        uint32_t max_pos = 0;
+        for (uint32_t i = 0; i < n; ++i) max_pos = std::max(max_pos, b.positions[row + i]);
+        t[0] = (uint32_t)row;
+        t[1] = n;
+        t[2] = (uint32_t)s;
+        t[3] = max_pos;
+        t += 4;
+        ++mt.num_tiles;
+        row += n;
+      }
+    }
+  }
   meta_ = mt;
 
   g_launch_count = 0;
@@ -741,6 +772,8 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
   if (DTypeOf<T>::is_bf16) {
     ORION_TRY(gemm_tc_poll_error(&code));
     if (code) return set_error(ORION_ERR_BACKEND, "backend cuda failed at gemm: a bounded pipeline wait ran out (code %u)", code);
+    ORION_TRY(prefill_poll_error(&code));
+    if (code) return set_error(ORION_ERR_BACKEND, "backend cuda failed at prefill attention: a bounded pipeline wait ran out (code %u)", code);
     ORION_TRY(decode_poll_error(&code));
     if (code) return set_error(ORION_ERR_BACKEND, "backend cuda failed at attention: a bounded pipeline wait ran out (code %u)", code);
   }

@@ -381,6 +381,58 @@ def test_config1_greedy_decode_matches_the_oracle(pkg, backend, oracle, dtype_na
     assert rep.passed(), rep.render()
 
 
+@pytest.mark.parametrize("heads,kv_heads", [(8, 2), (14, 2)])
+def test_chunked_prefill_and_mixed_batches_on_the_tuned_path(pkg, backend, oracle, heads, kv_heads):
+    """head_dim 128 / block 16 / bf16: chunked prefill rows, decode rows and both in one batch
+    (the tensor-core prefill attention and decode attention kernels), against the oracle."""
+    meta_d = dict(hidden_size=256, num_layers=2, num_attention_heads=heads, num_kv_heads=kv_heads, head_dim=128,
+                  vocab_size=384, ffn_dim=512, max_position_embeddings=1024, rope_theta=10000.0,
+                  rms_norm_eps=1e-5, has_qkv_bias=False, tied_lm_head=False, num_blocks=96, block_size=16)
+    t = {k: (oracle.round_to_bf16(v) if v.ndim == 2 else v)
+         for k, v in random_tensors(np.random.default_rng(heads), meta_d, std=0.05).items()}
+    ref = oracle.Model(**meta_d).load(t)
+    meta = pkg.ModelMetadata(architecture="llama", name="p",
+                             **{k: v for k, v in meta_d.items() if k not in ("num_blocks", "block_size")})
+    dev = pkg.CudaTransformerModel.new(meta, t, 96, 16, backend, compute_dtype=pkg.DType.BF16,
+                                       max_batch_tokens=512, max_batch_sequences=8)
+    rng = np.random.default_rng(99)
+    prompts = [rng.integers(0, 384, n).tolist() for n in (301, 37, 150, 16)]
+    perm = rng.permutation(96).tolist()
+    tables = [[perm.pop() for _ in range((len(p) + 8 + 15) // 16)] for p in prompts]
+    done = [0] * 4          # prompt tokens already prefilled
+    generated = [[] for _ in range(4)]
+    oracle.set_threads(8)
+    worst = 0.0
+    for step in range(6):
+        budget, tokens, positions, counts, ctx, ids, tabs = 160, [], [], [], [], [], []
+        for s in range(4):  # decode rows first, then prefill chunks, like the reference's scheduler
+            if done[s] == len(prompts[s]) and generated[s]:
+                pos = len(prompts[s]) + len(generated[s]) - 1
+                tokens.append(generated[s][-1]); positions.append(pos); counts.append(1); ctx.append(pos + 1)
+                ids.append(s + 1); tabs.append(tables[s]); budget -= 1
+        for s in range(4):
+            if done[s] < len(prompts[s]) and budget > 0:
+                n = min(budget, len(prompts[s]) - done[s], 100 + 13 * s)
+                tokens += prompts[s][done[s]:done[s] + n]; positions += list(range(done[s], done[s] + n))
+                counts.append(n); ctx.append(done[s] + n); ids.append(s + 1); tabs.append(tables[s]); budget -= n
+                done[s] += n
+        batch = pkg.ForwardBatch(tokens, positions, ids, counts, ctx, tabs, has_prefill=True)
+        exp = ref.forward(oracle.Batch(tokens, positions, counts, ctx, tabs))
+        got = dev.forward(batch).logits
+        worst = max(worst, float(np.max(np.abs(softmax_rows(got) - softmax_rows(exp)))))
+        assert worst < BF16_SOFTMAX, f"step {step}: softmax max-abs {worst}"
+        assert rel_err(got, exp) < 3e-2, f"step {step}: logits relative error {rel_err(got, exp)}"
+        for row, sid in enumerate(ids):
+            s = sid - 1
+            if done[s] == len(prompts[s]) and len(generated[s]) < 8:
+                generated[s].append(int(oracle.argmax(exp[row])))
+    oracle.set_threads(1)
+    kv_dev, kv_ref = dev.read_kv(), ref.kv().array()
+    assert np.array_equal(kv_dev != 0, kv_ref != 0), "exactly the same slots were written"
+    rep = pkg.validate("kv_arena", kv_ref, kv_dev, pkg.Tolerance(0.1, 0.1))
+    assert rep.passed(), rep.render()
+
+
 def test_qwen2_shape_with_qkv_bias(pkg, backend, oracle):
     meta_d = dict(SMALL_META, hidden_size=128, head_dim=64, num_attention_heads=4, num_kv_heads=2,
                   ffn_dim=256, vocab_size=300, has_qkv_bias=True, num_blocks=16, block_size=16,
