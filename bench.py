@@ -211,6 +211,23 @@ def make_decode_batch(pkg, rng, num_blocks):
                             [CONTEXT] * BATCH, tables, has_prefill=False)
 
 
+def attention_sweep(pkg, backend, peak):
+    """Paged GQA decode-attention microbenchmark (bf16, 32 query / 8 KV heads, head_dim 128, block 16):
+    batch in {1, 8, 64, 256}, context lengths uniform in [512, 8192], each table a consecutive slice of
+    one random permutation of a 200 000-block pool, N(0, 1) values. GB/s = algorithmic bytes / launch."""
+    out = []
+    rng = np.random.default_rng(2024)
+    for batch in (1, 8, 64, 256):
+        ctx = rng.integers(512, 8193, batch)
+        bench = pkg.PagedAttentionBench(backend, ctx, num_blocks=200_000, seed=batch)
+        ms, nbytes = bench.run(3, 20)
+        gbs = nbytes / (ms / 1000.0) / 1e9
+        out.append({"batch": batch, "context_tokens": int(ctx.sum()), "ms": ms, "algorithmic_bytes": nbytes,
+                    "gbs": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_8tbs_nominal": gbs / 8000.0})
+        del bench
+    return out
+
+
 def run_ours(args):
     import __graft_entry__ as ge
 
@@ -326,6 +343,8 @@ def run_ours(args):
         "step_breakdown_note": "event pair around every launch in a separate pass: serialises the launches, so "
                                "the parts add up to more than ms_per_step",
     }
+    if world == 1 and not args.no_attention_sweep:
+        line["attention_microbench"] = attention_sweep(pkg, backend, peak)
     if world == 1 and not args.no_cpu_baseline:
         from oracle import binding as oracle
 
@@ -351,6 +370,8 @@ def main():
     ap.add_argument("--layers", type=int, default=32,
                     help="layers of the Llama-3-8B shape to build; fewer than 32 gives a small case with the "
                          "same per-launch kernel shapes, for profiler captures (not a benchmark number)")
+    ap.add_argument("--no-attention-sweep", action="store_true",
+                    help="skip the paged-attention microbenchmark sweep that is appended at N=1")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (tuning A/B)")
     ap.add_argument("--gemm-ctas", type=int, default=0, help="split-K CTA target (tuning A/B)")
     ap.add_argument("--l2-prefetch-mb", type=int, default=-1, help="L2 weight prefetch per hand-over (tuning A/B)")

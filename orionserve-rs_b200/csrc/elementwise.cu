@@ -640,6 +640,27 @@ int launch_f16_to_f32(const uint16_t *src, float *dst, size_t n, cudaStream_t st
   return after_launch("f16_to_f32");
 }
 
+namespace {
+template <typename T>
+__global__ void gather_rows_kernel(const T *__restrict__ src, const uint32_t *__restrict__ row_map,
+                                   T *__restrict__ dst, uint32_t cols) {
+  pdl_trigger();
+  pdl_wait();
+  const T *s = src + (size_t)row_map[blockIdx.x] * cols;
+  T *d = dst + (size_t)blockIdx.x * cols;
+  for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) d[c] = s[c];
+}
+}  // namespace
+
+template <typename T>
+int launch_gather_rows(const T *src, const uint32_t *row_map, T *dst, uint32_t rows, uint32_t cols,
+                       cudaStream_t stream) {
+  if (rows == 0) return ORION_OK;
+  ORION_CUDA_CHECK("gather_rows", launch_pdl(gather_rows_kernel<T>, dim3(rows), dim3(256), 0, stream, src, row_map,
+                                             dst, cols));
+  return after_launch("gather_rows");
+}
+
 template <typename T>
 int launch_scale_convert(const float *src, T *dst, size_t n, float scale, cudaStream_t stream) {
   if (n == 0) return ORION_OK;
@@ -693,6 +714,7 @@ int launch_fill_normal(T *dst, size_t n, uint64_t seed, cudaStream_t stream) {
   template int launch_arena_to_reference_order<T>(const T *, KvLayout, float *, cudaStream_t);    \
   template int launch_arena_from_reference_order<T>(const float *, KvLayout, T *, cudaStream_t);  \
   template int launch_scale_convert<T>(const float *, T *, size_t, float, cudaStream_t);           \
+  template int launch_gather_rows<T>(const T *, const uint32_t *, T *, uint32_t, uint32_t, cudaStream_t); \
   template int launch_fill_normal<T>(T *, size_t, uint64_t, cudaStream_t);
 
 ORION_INSTANTIATE(float)

@@ -94,6 +94,10 @@ int launch_convert_from_f32(const float *src, T *dst, size_t n, cudaStream_t str
 template <typename T>
 int launch_convert_to_f32(const T *src, float *dst, size_t n, cudaStream_t stream);
 int launch_f16_to_f32(const uint16_t *src, float *dst, size_t n, cudaStream_t stream);
+// dst[i][:] = src[row_map[i]][:]
+template <typename T>
+int launch_gather_rows(const T *src, const uint32_t *row_map, T *dst, uint32_t rows, uint32_t cols,
+                       cudaStream_t stream);
 // dst[i] = T(src[i] * scale)
 template <typename T>
 int launch_scale_convert(const float *src, T *dst, size_t n, float scale, cudaStream_t stream);
@@ -163,6 +167,29 @@ int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv,
 void decode_set_tuning(int stages, uint32_t cta_target);
 // Device error word of the decode kernel (0 = none); reading clears it.
 int decode_poll_error(uint32_t *code);
+
+// ---- tensor-parallel hand-over ---------------------------------------------------
+
+constexpr int kMaxTpWorld = 8;
+// Largest batch the fused hand-over takes; larger (prefill-sized) batches are bandwidth-bound
+// and go through the library all-reduce.
+constexpr uint32_t kTpFusedMaxRows = 256;
+// Peer-mapped inboxes of every rank of the tensor-parallel group (index = rank; the entry of
+// this rank is its own local pointer). An inbox is [parity 2][sender world][slot_floats] units
+// of 8 bytes: one f32 of a partial sum and the epoch of the hand-over that wrote it.
+struct TpPeers {
+  uint32_t *inbox[kMaxTpWorld];
+  int rank, world;
+  uint32_t slot_floats;
+};
+// All-reduce of the partial sums over ranks and split-K slabs + residual add + RMSNorm for
+// `rows` batch rows; every rank ends up with the full residual stream in `hidden` and all
+// normalised rows in `out`. `epoch` cycles 1, 2, ..., 0xFFFFFFFE, 1, ...: one step per call.
+template <typename T>
+int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, const float *partial, uint32_t splits,
+                                         size_t split_stride, float *hidden, const float *norm_w, float eps, T *out,
+                                         uint32_t rows, uint32_t hidden_size, cudaStream_t stream);
+int tp_poll_error(uint32_t *code);
 
 // ---- GEMM ----------------------------------------------------------------------
 

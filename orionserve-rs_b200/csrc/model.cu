@@ -79,6 +79,7 @@ class Model final : public ModelBase {
   ~Model() override {
     cudaSetDevice(backend_->ordinal);
     if (stream_) cudaStreamSynchronize(stream_);
+    for (void *p : ipc_opened_) cudaIpcCloseMemHandle(p);
     for (void *p : allocs_) cudaFree(p);
     if (h_meta_) cudaFreeHost(h_meta_);
     if (stage_raw_) cudaFree(stage_raw_);
@@ -136,6 +137,16 @@ class Model final : public ModelBase {
                    uint64_t r1, uint64_t c0, uint64_t c1);
   int run_step(bool want_argmax);
   int tp_reduce(uint32_t *splits, size_t slab);
+  int setup_peer_handover();
+  // Row-parallel projection -> residual + norm. Single GPU: the fused residual/norm kernel.
+  // Tensor parallel: the fused peer-memory all-reduce + residual + norm kernel, or NCCL followed
+  // by the single-GPU kernel. `out_rows`/`row_map` select gathered output rows (final norm).
+  int handover(uint32_t splits, const float *norm_w, T *out, const uint32_t *row_map, uint32_t out_rows);
+  TpPeers peers_{};
+  uint32_t *tp_inbox_ = nullptr;  // where the peers push their partial sums (peer-mapped)
+  uint32_t tp_epoch_ = 1;
+  bool tp_fused_ = false;
+  std::vector<void *> ipc_opened_;
   // Per-launch event pairs of a profiled step, resolved after the stream drains.
   struct ProfRec { int cat; cudaEvent_t a, b; };
   std::vector<ProfRec> prof_recs_;
@@ -302,8 +313,50 @@ int Model<T>::init() {
   if (d.tp_world > 1) {
     nccl_.reset(new NcclCollective());
     ORION_TRY(nccl_->init(d.nccl_unique_id, (int)d.tp_rank, (int)d.tp_world));
+    const char *mode = std::getenv("ORION_TP_ALLREDUCE");  // "nccl" keeps the library all-reduce
+    if (!(mode && !strcmp(mode, "nccl")) && d.tp_world <= (uint32_t)kMaxTpWorld && H % 4 == 0 && H / 4 <= 4096)
+      ORION_TRY(setup_peer_handover());
   }
   ORION_CUDA_CHECK("model init", cudaStreamSynchronize(stream_));
+  return ORION_OK;
+}
+
+// Maps every rank's inbox into this process (CUDA IPC; the 64-byte handles travel through
+// one NCCL all-gather) so that the fused all-reduce + residual + norm kernel can push its
+// partial sums straight into the peers' memory.
+template <typename T>
+int Model<T>::setup_peer_handover() {
+  const int world = (int)d_.tp_world, rank = (int)d_.tp_rank;
+  const size_t slot_floats = (size_t)std::min(d_.max_batch_tokens, kTpFusedMaxRows) * d_.hidden_size;
+  const size_t inbox_words = 2 * (size_t)world * slot_floats * 2;
+  ORION_TRY(alloc(&tp_inbox_, inbox_words));
+  ORION_CUDA_CHECK("clear inbox", cudaMemset(tp_inbox_, 0, inbox_words * sizeof(uint32_t)));  // epoch 0 is never sent
+  constexpr int kFloatsPerHandle = sizeof(cudaIpcMemHandle_t) / sizeof(float);
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are 64 bytes");
+  cudaIpcMemHandle_t mine;
+  ORION_CUDA_CHECK("ipc export", cudaIpcGetMemHandle(&mine, tp_inbox_));
+  float *d_send = nullptr, *d_recv = nullptr;
+  ORION_TRY(alloc(&d_send, kFloatsPerHandle));
+  ORION_TRY(alloc(&d_recv, (size_t)kFloatsPerHandle * world));
+  ORION_CUDA_CHECK("ipc exchange", cudaMemcpy(d_send, &mine, sizeof mine, cudaMemcpyHostToDevice));
+  ORION_TRY(nccl_->all_gather(d_send, d_recv, kFloatsPerHandle, stream_));
+  ORION_CUDA_CHECK("ipc exchange", cudaStreamSynchronize(stream_));
+  std::vector<cudaIpcMemHandle_t> all((size_t)world);
+  ORION_CUDA_CHECK("ipc exchange", cudaMemcpy(all.data(), d_recv, all.size() * sizeof(cudaIpcMemHandle_t),
+                                               cudaMemcpyDeviceToHost));
+  peers_.rank = rank;
+  peers_.world = world;
+  peers_.slot_floats = (uint32_t)slot_floats;
+  for (int r = 0; r < world; ++r) {
+    void *p = tp_inbox_;
+    if (r != rank) {
+      ORION_CUDA_CHECK("ipc import", cudaIpcOpenMemHandle(&p, all[(size_t)r], cudaIpcMemLazyEnablePeerAccess));
+      ipc_opened_.push_back(p);
+    }
+    peers_.inbox[r] = static_cast<uint32_t *>(p);
+  }
+  ORION_TRY(nccl_->barrier(stream_));  // nobody starts a step before every mapping exists
+  tp_fused_ = true;
   return ORION_OK;
 }
 
@@ -531,6 +584,24 @@ int Model<T>::tp_reduce(uint32_t *splits, size_t slab) {
 }
 
 template <typename T>
+int Model<T>::handover(uint32_t splits, const float *norm_w, T *out, const uint32_t *row_map, uint32_t out_rows) {
+  const uint32_t Tn = meta_.rows, H = d_.hidden_size;
+  const size_t slab = (size_t)Tn * H;
+  if (nccl_ && tp_fused_ && Tn <= kTpFusedMaxRows) {
+    // every rank ends up with the whole residual stream and all Tn normalised rows
+    ORION_TRY(launch_tp_allreduce_residual_rmsnorm<T>(peers_, tp_epoch_, partial_, splits, slab, hidden_, norm_w,
+                                                      d_.rms_norm_eps, normed_, Tn, H, stream_));
+    tp_epoch_ = tp_epoch_ == 0xFFFFFFFEu ? 1u : tp_epoch_ + 1;
+    if (row_map) return launch_gather_rows<T>(normed_, row_map, out, out_rows, H, stream_);
+    if (out != normed_) return set_error(ORION_ERR_INTERNAL, "fused hand-over writes the activation buffer only");
+    return ORION_OK;
+  }
+  ORION_TRY(tp_reduce(&splits, slab));
+  return launch_residual_rmsnorm<T>(partial_, splits, slab, hidden_, norm_w, d_.rms_norm_eps, out, row_map, out_rows, H,
+                                    stream_);
+}
+
+template <typename T>
 int Model<T>::run_step(bool want_argmax) {
   const OrionModelDesc &d = d_;
   constexpr bool kBf16 = DTypeOf<T>::is_bf16;
@@ -579,9 +650,8 @@ int Model<T>::run_step(bool want_argmax) {
     p = gemm_plan(kBf16, Tn, H, qd, qd, qd);
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(attn_, qd, L.w_o, qd, partial_, Tn, H, qd, p, stream_,
                                                               hint(L.w_gu, (size_t)2 * lf_ * H)); }));
-    ORION_TRY(timed(kProfCollective, [&] { return tp_reduce(&p.splits, (size_t)Tn * H); }));
-    ORION_TRY(timed(kProfElementwise, [&] { return launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, L.post_norm, d.rms_norm_eps,
-                                         normed_, nullptr, Tn, H, stream_); }));
+    const int handover_cat = nccl_ ? kProfCollective : kProfElementwise;
+    ORION_TRY(timed(handover_cat, [&] { return handover(p.splits, L.post_norm, normed_, nullptr, Tn); }));
     p = gemm_plan(kBf16, Tn, 2 * lf_, H, H, H);
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_gu, H, partial_, Tn, 2 * lf_, H, p, stream_,
                                                               hint(L.w_down, (size_t)H * lf_)); }));
@@ -590,15 +660,15 @@ int Model<T>::run_step(bool want_argmax) {
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(act_, lf_, L.w_down, lf_, partial_, Tn, H, lf_, p, stream_,
                                                               l + 1 < d.num_layers ? hint(layers_[l + 1].w_qkv, (size_t)nqkv * H)
                                                                                    : hint(lm_head_, (size_t)d.vocab_size * H)); }));
-    ORION_TRY(timed(kProfCollective, [&] { return tp_reduce(&p.splits, (size_t)Tn * H); }));
     if (l + 1 < d.num_layers) {
-      ORION_TRY(timed(kProfElementwise, [&] { return launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, layers_[l + 1].in_norm,
-                                           d.rms_norm_eps, normed_, nullptr, Tn, H, stream_); }));
+      ORION_TRY(timed(handover_cat, [&] { return handover(p.splits, layers_[l + 1].in_norm, normed_, nullptr, Tn); }));
     } else if (!meta_.zero_count) {
       // Final norm over the last row of every sequence (transformer.rs:401-428;
       // the norm is row-wise, so gathering first gives the same rows).
-      ORION_TRY(timed(kProfElementwise, [&] { return launch_residual_rmsnorm<T>(partial_, p.splits, (size_t)Tn * H, hidden_, final_norm_, d.rms_norm_eps,
-                                           tail_, last_rows, S, H, stream_); }));
+      ORION_TRY(timed(handover_cat, [&] { return handover(p.splits, final_norm_, tail_, last_rows, S); }));
+    } else if (nccl_) {
+      // keep the ranks in lock step even though this step ends in an error
+      ORION_TRY(timed(handover_cat, [&] { return handover(p.splits, final_norm_, normed_, nullptr, Tn); }));
     }
   }
   if (meta_.zero_count) return ORION_OK;
@@ -769,6 +839,10 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
     ORION_CUDA_CHECK("forward", cudaStreamSynchronize(stream_));
   }
   uint32_t code = 0;
+  if (tp_fused_) {
+    ORION_TRY(tp_poll_error(&code));
+    if (code) return set_error(ORION_ERR_BACKEND, "backend cuda failed at all_reduce: a peer did not arrive within the wait limit (code %u)", code);
+  }
   if (DTypeOf<T>::is_bf16) {
     ORION_TRY(gemm_tc_poll_error(&code));
     if (code) return set_error(ORION_ERR_BACKEND, "backend cuda failed at gemm: a bounded pipeline wait ran out (code %u)", code);

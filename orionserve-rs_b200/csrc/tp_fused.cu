@@ -1,0 +1,219 @@
+// Fused tensor-parallel hand-over after a row-parallel projection (O or down):
+//   all-reduce of the per-rank partial sums  +  residual add  +  RMSNorm
+// in ONE kernel over peer-mapped memory (orion-distributed/src/lib.rs:317-319 places one
+// all-reduce here; transformer.rs:330-336 the residual add and the norm).
+//
+// One-shot, flag-in-data: every thread folds this rank's split-K slabs for four elements,
+// pushes the four sums into every peer's inbox with plain peer stores over NVLink, then
+// collects the peers' sums for the same four elements from its own inbox, adds them in rank
+// order (identical on every rank, so all ranks hold bit-identical residual streams), updates
+// the f32 residual and normalises the row. Each 8-byte unit in an inbox carries one f32 and
+// the 32-bit epoch of the hand-over, so a unit validates itself: there is no barrier, no
+// fence and no separate flag, and the only latency on the path is one NVLink store.
+//
+// Inboxes are double-buffered by the parity of the epoch. A rank can enter hand-over k+2
+// only after it received every peer's data of hand-over k+1, which a peer sends only after
+// it finished reading hand-over k, so a slot is never overwritten while it is being read.
+//
+// Every wait is bounded: after about two seconds a thread records an error word and goes
+// on with what it has; the host turns the word into a backend error after the step.
+// One process per GPU; the kernel never waits on another launch on the same GPU.
+#include "kernels.h"
+
+#include <algorithm>
+#include <cstdlib>
+#include <type_traits>
+
+namespace orion {
+namespace {
+
+__device__ uint32_t g_tp_error = 0;
+// Debug trace (ORION_TP_TRACE=1): %globaltimer at the phase boundaries of CTA 0 of the last launch.
+__device__ unsigned long long g_tp_trace[4];
+__device__ uint32_t g_tp_trace_on = 0;
+__device__ __forceinline__ void trace(int k) {
+  if (g_tp_trace_on && blockIdx.x == 0 && threadIdx.x == 0) g_tp_trace[k] = global_timer_ns();
+}
+
+__device__ __forceinline__ void st_unit2(uint32_t *dst, float a, float b, uint32_t epoch) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(__float_as_uint(a)), "r"(epoch),
+               "r"(__float_as_uint(b)), "r"(epoch)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_unit2(const uint32_t *src) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+  return v;
+}
+// Polls two 16-byte slots (four self-validating units) until all carry `epoch`.
+__device__ __forceinline__ float4 receive4(const uint32_t *src, uint32_t epoch) {
+  uint4 lo = ld_unit2(src), hi = ld_unit2(src + 4);
+  if (lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch) {
+    const uint64_t start = global_timer_ns();
+    uint32_t spins = 0;
+    do {
+      lo = ld_unit2(src);
+      hi = ld_unit2(src + 4);
+      if ((++spins & 1023u) == 0 && global_timer_ns() - start > 2000000000ull) {
+        atomicOr(&g_tp_error, 1u);
+        break;
+      }
+    } while (lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch);
+  }
+  return make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x), __uint_as_float(hi.z));
+}
+
+template <typename T>
+__device__ __forceinline__ void st_row4(T *dst, float4 v);
+template <>
+__device__ __forceinline__ void st_row4<float>(float *dst, float4 v) { *reinterpret_cast<float4 *>(dst) = v; }
+template <>
+__device__ __forceinline__ void st_row4<bf16>(bf16 *dst, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 packed;
+  packed.x = *reinterpret_cast<uint32_t *>(&lo);
+  packed.y = *reinterpret_cast<uint32_t *>(&hi);
+  *reinterpret_cast<uint2 *>(dst) = packed;
+}
+
+// Sum of `n` f32 slabs at `p` (stride `stride`), four floats per thread, loads issued in
+// independent batches of 8.
+__device__ __forceinline__ float4 sum_slabs_local(const float *p, uint32_t n, size_t stride) {
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (uint32_t j0 = 0; j0 < n; j0 += 8) {
+    float4 x[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      x[j] = (j0 + j < n) ? *reinterpret_cast<const float4 *>(p + (size_t)(j0 + j) * stride)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      acc.x += x[j].x; acc.y += x[j].y; acc.z += x[j].z; acc.w += x[j].w;
+    }
+  }
+  return acc;
+}
+
+// One CTA per batch row.
+template <typename T, typename Acc>
+__global__ void __launch_bounds__(1024)
+tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ partial,
+                                     uint32_t splits, size_t split_stride, float *__restrict__ hidden,
+                                     const float *__restrict__ w, float eps, T *__restrict__ out, uint32_t H) {
+  __shared__ Acc red[32];
+  pdl_trigger();
+  pdl_wait();  // this rank's projection has finished
+  trace(0);
+  const uint32_t nvec = H / 4, row = blockIdx.x;
+  const size_t slot = (size_t)peers.slot_floats * 2;  // u32 words per (parity, sender) slot
+  const size_t parity_base = (size_t)(epoch & 1u) * peers.world * slot;
+  float4 v[4];  // H / 4 <= 4 * blockDim.x is guaranteed by the launcher
+
+  // ---- send: fold the local split-K slabs and push the sums to every peer ----
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t idx = threadIdx.x + c * blockDim.x;
+    if (idx < nvec) {
+      const size_t off = (size_t)row * H + 4 * (size_t)idx;
+      v[c] = sum_slabs_local(partial + off, splits, split_stride);
+      const size_t at = parity_base + (size_t)peers.rank * slot + off * 2;
+      for (int r = 0; r < peers.world; ++r)
+        if (r != peers.rank) {
+          st_unit2(peers.inbox[r] + at, v[c].x, v[c].y, epoch);
+          st_unit2(peers.inbox[r] + at + 4, v[c].z, v[c].w, epoch);
+        }
+    }
+  }
+  trace(1);
+  // ---- receive: add the ranks' sums in rank order, update the residual ----
+  Acc ss = Acc(0);
+  float *h = hidden + (size_t)row * H;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t idx = threadIdx.x + c * blockDim.x;
+    if (idx < nvec) {
+      const size_t off = (size_t)row * H + 4 * (size_t)idx;
+      float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < peers.world; ++r) {
+        const float4 x = r == peers.rank ? v[c]
+                                         : receive4(peers.inbox[peers.rank] + parity_base + (size_t)r * slot + off * 2, epoch);
+        add.x += x.x; add.y += x.y; add.z += x.z; add.w += x.w;
+      }
+      const float4 old = *reinterpret_cast<const float4 *>(h + 4 * (size_t)idx);
+      v[c] = make_float4(old.x + add.x, old.y + add.y, old.z + add.z, old.w + add.w);
+      *reinterpret_cast<float4 *>(h + 4 * (size_t)idx) = v[c];
+      ss += (Acc)v[c].x * (Acc)v[c].x + (Acc)v[c].y * (Acc)v[c].y + (Acc)v[c].z * (Acc)v[c].z +
+            (Acc)v[c].w * (Acc)v[c].w;
+    }
+  }
+  trace(2);
+  // ---- RMSNorm of the row (tensor.rs:143-163) ----
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  Acc total = Acc(0);
+  for (uint32_t i = 0; i < (blockDim.x + 31) / 32; ++i) total += red[i];
+  const float scale = sizeof(Acc) == 8 ? (float)(1.0 / sqrt((double)total / (double)H + (double)eps))
+                                       : rsqrtf((float)total / (float)H + eps);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t idx = threadIdx.x + c * blockDim.x;
+    if (idx < nvec) {
+      const float4 g = *reinterpret_cast<const float4 *>(w + 4 * (size_t)idx);
+      st_row4<T>(out + (size_t)row * H + 4 * (size_t)idx,
+                 make_float4(__fmul_rn(__fmul_rn(v[c].x, scale), g.x), __fmul_rn(__fmul_rn(v[c].y, scale), g.y),
+                             __fmul_rn(__fmul_rn(v[c].z, scale), g.z), __fmul_rn(__fmul_rn(v[c].w, scale), g.w)));
+    }
+  }
+  trace(3);
+}
+
+}  // namespace
+
+template <typename T>
+int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, const float *partial, uint32_t splits,
+                                         size_t split_stride, float *hidden, const float *norm_w, float eps, T *out,
+                                         uint32_t rows, uint32_t hidden_size, cudaStream_t stream) {
+  if (hidden_size % 4 != 0 || hidden_size / 4 > 4096 || split_stride % 4 != 0 ||
+      (size_t)rows * hidden_size > peers.slot_floats || epoch == 0 || epoch == 0xFFFFFFFFu)
+    return set_error(ORION_ERR_INTERNAL, "fused tensor-parallel hand-over: unsupported shape or epoch");
+  if (rows == 0) return ORION_OK;
+  const uint32_t nvec = hidden_size / 4;
+  uint32_t threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
+  if (threads < 32) threads = 32;
+  using Acc = typename std::conditional<sizeof(T) == 4, double, float>::type;
+  ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
+                   launch_pdl(tp_allreduce_residual_rmsnorm_kernel<T, Acc>, dim3(rows), dim3(threads), 0, stream, peers,
+                              epoch, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size));
+  count_launch();
+  ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm", cudaGetLastError());
+  return ORION_OK;
+}
+template int launch_tp_allreduce_residual_rmsnorm<float>(const TpPeers &, uint32_t, const float *, uint32_t, size_t,
+                                                         float *, const float *, float, float *, uint32_t, uint32_t,
+                                                         cudaStream_t);
+template int launch_tp_allreduce_residual_rmsnorm<bf16>(const TpPeers &, uint32_t, const float *, uint32_t, size_t,
+                                                        float *, const float *, float, bf16 *, uint32_t, uint32_t,
+                                                        cudaStream_t);
+
+int tp_poll_error(uint32_t *code) {
+  static const bool tracing = std::getenv("ORION_TP_TRACE") != nullptr;
+  if (tracing) {
+    uint32_t on = 1;
+    unsigned long long t[4];
+    cudaMemcpyFromSymbol(t, g_tp_trace, sizeof t);
+    cudaMemcpyToSymbol(g_tp_trace_on, &on, sizeof on);
+    fprintf(stderr, "tp trace of CTA 0 (us): fold+send %.2f receive %.2f norm %.2f total %.2f\n", (t[1] - t[0]) / 1e3,
+            (t[2] - t[1]) / 1e3, (t[3] - t[2]) / 1e3, (t[3] - t[0]) / 1e3);
+  }
+  uint32_t v = 0;
+  ORION_CUDA_CHECK("tp error word", cudaMemcpyFromSymbol(&v, g_tp_error, sizeof v));
+  if (v) {
+    uint32_t zero = 0;
+    ORION_CUDA_CHECK("tp error word", cudaMemcpyToSymbol(g_tp_error, &zero, sizeof zero));
+  }
+  *code = v;
+  return ORION_OK;
+}
+
+}  // namespace orion
