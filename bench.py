@@ -30,6 +30,11 @@ LLAMA3_8B = dict(hidden_size=4096, num_layers=32, num_attention_heads=32, num_kv
 BATCH, CONTEXT, BLOCK = 64, 1024, 16
 WORKLOAD = "llama3_8b_decode_batch64_ctx1024_bf16"
 METRIC = "decode tokens/s at batch 64 (Llama-3-8B shape)"
+# DRAM bytes (read + write) of the projection GEMM launches of one 32-layer step, from the ncu
+# capture summarised in profiles/gemm_tc_kernel_decode_batch64_llama3_8b_shape.md: the four
+# projections of one layer moved 450.13 MB (algorithmic 436.21 MB); 32 layers of that plus the LM
+# head at its algorithmic 1050.67 MB of weights + 32.83 MB of logits (the head was not captured).
+GEMM_TRAFFIC_BYTES_PER_STEP = int(32 * 450.13e6 + 1050.67e6 + 32.83e6)
 
 
 def measured_peaks():
@@ -301,6 +306,12 @@ def run_ours(args):
     # (3) per-kernel device time for the roofline, event pair around every launch
     prof = model.profile(args.steps)
     barrier()
+    # (4) one kernel family at a time, launched back to back as inside the step (dependent-launch
+    # overlap included) with the other families left out: the per-launch duration of the roofline
+    gemm_chain_ms = max_over_ranks(model.replay_categories(args.steps, "gemm"))
+    attn_chain_ms = max_over_ranks(model.replay_categories(args.steps, "attention"))
+    barrier()
+    model.forward(batch, out=logits)  # leave the buffers holding a real step again
     if rank != 0:
         return 0
 
@@ -312,8 +323,10 @@ def run_ours(args):
     attn_ms, attn_n = prof["attention"]
     wbytes = weight_bytes_per_step(m, world)
     kbytes = kv_bytes_per_step(m, [CONTEXT] * BATCH, world)
-    gemm_gbs = wbytes * args.steps / (gemm_ms / 1000.0) / 1e9 if gemm_ms > 0 else None
-    attn_gbs = kbytes * args.steps / (attn_ms / 1000.0) / 1e9 if attn_ms > 0 else None
+    gemm_gbs = wbytes * args.steps / (gemm_chain_ms / 1000.0) / 1e9
+    attn_gbs = kbytes * args.steps / (attn_chain_ms / 1000.0) / 1e9
+    gemm_gbs_serial = wbytes * args.steps / (gemm_ms / 1000.0) / 1e9 if gemm_ms > 0 else None
+    attn_gbs_serial = kbytes * args.steps / (attn_ms / 1000.0) / 1e9 if attn_ms > 0 else None
     meta_bytes = 4 * (5 * BATCH + 2 * BATCH + 1 + sum(len(t) for t in batch.block_tables))
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -328,12 +341,20 @@ def run_ours(args):
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel (projection weights streamed once per step)",
                      "achieved": gemm_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                     "frac": (gemm_gbs / peak) if gemm_gbs else None, "traffic": None,
+                     "frac": gemm_gbs / peak, "traffic": GEMM_TRAFFIC_BYTES_PER_STEP if world == 1 and args.layers == 32 else None,
                      "algorithmic_bytes_per_step": wbytes, "launches_per_step": gemm_n // max(args.steps, 1),
-                     "ms_per_step": gemm_ms / args.steps},
+                     "ms_per_step": gemm_chain_ms / args.steps,
+                     "timing": "CUDA events around the step's projection launches run back to back on the launch "
+                               "stream (dependent-launch overlap as in the step, other kernels left out)",
+                     "serialised": {"achieved": gemm_gbs_serial, "frac": (gemm_gbs_serial / peak) if gemm_gbs_serial else None,
+                                    "ms_per_step": gemm_ms / args.steps,
+                                    "timing": "event pair around every single launch (no overlap between launches)"}},
         "roofline_attention": {"bound": "hbm", "kernel": "paged_decode_kernel", "achieved": attn_gbs, "peak": peak,
-                               "unit": "GB/s", "frac": (attn_gbs / peak) if attn_gbs else None,
-                               "algorithmic_bytes_per_step": kbytes, "ms_per_step": attn_ms / args.steps},
+                               "unit": "GB/s", "frac": attn_gbs / peak,
+                               "algorithmic_bytes_per_step": kbytes, "ms_per_step": attn_chain_ms / args.steps,
+                               "serialised": {"achieved": attn_gbs_serial,
+                                              "frac": (attn_gbs_serial / peak) if attn_gbs_serial else None,
+                                              "ms_per_step": attn_ms / args.steps}},
         # whole step: every weight byte and every KV byte once per step over the device step time
         "roofline_step": {"bound": "hbm", "achieved": (wbytes + kbytes) / (ms_per_step / 1000.0) / 1e9,
                           "peak": peak, "unit": "GB/s",

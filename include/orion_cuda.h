@@ -168,6 +168,16 @@ int orion_cuda_model_forward_greedy(OrionModel *model, const uint32_t *tokens,
  * device copy (inputs and block tables stay resident). Used to time the
  * device-resident step; results land in the model's device logits buffer. */
 int orion_cuda_model_replay(OrionModel *model, int iterations, float *elapsed_ms);
+/* Timing only (no reference counterpart): replays just the kernels of the
+ * categories named by `category_mask` (bit 0 projection GEMMs, bit 1 paged
+ * attention, bit 2 elementwise, bit 3 tensor-parallel reductions) back to back
+ * on the launching stream, as they run inside a step (programmatic dependent
+ * launch included) but without the kernels of the other categories between
+ * them. The buffers keep the step's shapes; their contents become meaningless
+ * until the next forward. Gives the per-kernel duration the roofline of one
+ * kernel family is computed from. */
+int orion_cuda_model_replay_categories(OrionModel *model, int iterations, uint32_t category_mask,
+                                       float *elapsed_ms);
 /* Replays the previous batch with an event pair around every kernel launch and
  * sums device time and launch counts per category: [0] projection GEMMs,
  * [1] paged attention, [2] fused elementwise kernels, [3] tensor-parallel

@@ -396,7 +396,15 @@ int orion_cuda_model_forward(OrionModel *model, const uint32_t *tokens, uint64_t
 int orion_cuda_model_replay(OrionModel *model, int iterations, float *elapsed_ms) {
   clear_error();
   if (!model) return set_error(ORION_ERR_INVALID_REQUEST, "null model handle");
-  return model->impl->replay(iterations, elapsed_ms);
+  return model->impl->replay(iterations, 0, elapsed_ms);
+}
+
+int orion_cuda_model_replay_categories(OrionModel *model, int iterations, uint32_t category_mask, float *elapsed_ms) {
+  clear_error();
+  if (!model) return set_error(ORION_ERR_INVALID_REQUEST, "null model handle");
+  if (category_mask == 0 || category_mask >= (1u << kProfCategories))
+    return set_error(ORION_ERR_INVALID_REQUEST, "category mask must name at least one of the four kernel categories");
+  return model->impl->replay(iterations, category_mask, elapsed_ms);
 }
 
 int orion_cuda_model_profile(OrionModel *model, int iterations, float category_ms[4],

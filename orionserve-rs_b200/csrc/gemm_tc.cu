@@ -25,6 +25,7 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -38,6 +39,13 @@ constexpr int kUmmaK = 16;
 constexpr int kThreads = 256;
 
 __device__ uint32_t g_gemm_error = 0;
+// Debug trace (ORION_GEMM_TRACE=1): %globaltimer stamps of CTA (0,0,0) of the last launches.
+constexpr int kTraceLaunches = 160, kTraceStamps = 8;
+__device__ unsigned long long g_gemm_trace[kTraceLaunches][kTraceStamps];
+__device__ uint32_t g_gemm_trace_on = 0, g_gemm_trace_next = 0;
+__device__ __forceinline__ void gtrace(uint32_t slot, int k) {
+  if (slot != 0xFFFFFFFFu) g_gemm_trace[slot][k] = global_timer_ns();
+}
 
 // Two rings per CTA. Weight tiles come from HBM (long latency, the stream that must never
 // stall): WST stages of 16 KiB. Activation tiles come from L2 (every CTA re-reads them):
@@ -149,7 +157,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t my_kb = kb_end - kb_begin;
 
   pdl_trigger();
+  __shared__ uint32_t trace_slot_s;
   if (threadIdx.x == 0) {
+    uint32_t slot = 0xFFFFFFFFu;
+    if (g_gemm_trace_on && blockIdx.x + blockIdx.y + blockIdx.z == 0) {
+      slot = atomicAdd(&g_gemm_trace_next, 1u) % kTraceLaunches;
+      g_gemm_trace[slot][7] = ((unsigned long long)gridDim.x << 32) | (gridDim.z << 16) | my_kb;
+    }
+    trace_slot_s = slot;
+    gtrace(slot, 0);
     for (int s = 0; s < WST; ++s) {
       mbar_init(&full_w[s], 1);
       mbar_init(&empty_w[s], 1);
@@ -169,12 +185,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tslot = trace_slot_s;
   bool ok = true;
 
   if (warp == 0) {
     // Weight producer. Weights are immutable, so this stream starts while the kernel that
     // produces the activations is still running and never waits for it.
     if (lane == 0) {
+      gtrace(tslot, 1);
       for (uint32_t i = 0; i < my_kb; ++i) {
         const uint32_t s = i % WST, use = i / WST;
         if (!mbar_wait(&empty_w[s], (use & 1) ^ 1)) { ok = false; break; }
@@ -187,6 +205,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // Activation producer: waits for the preceding kernel, then keeps the short x ring full.
     if (lane == 0) {
       pdl_wait();
+      gtrace(tslot, 3);
       for (uint32_t i = 0; i < my_kb; ++i) {
         const uint32_t s = i % XST, use = i / XST;
         if (!mbar_wait(&empty_x[s], (use & 1) ^ 1)) { ok = false; break; }
@@ -199,10 +218,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       constexpr uint32_t idesc = instr_desc<TOKN>();
       for (uint32_t i = 0; i < my_kb; ++i) {
         const uint32_t sw = i % WST, sx = i % XST;
-        if (!mbar_wait(&full_w[sw], (i / WST) & 1) || !mbar_wait(&full_x[sx], (i / XST) & 1)) {
-          ok = false;
-          break;
-        }
+        if (!mbar_wait(&full_w[sw], (i / WST) & 1)) { ok = false; break; }
+        if (i == 0) gtrace(tslot, 2);
+        if (!mbar_wait(&full_x[sx], (i / XST) & 1)) { ok = false; break; }
         tc_fence_after();
         const uint32_t wt = smem_u32(w_ring + sw * Cfg::kWBytes);
         const uint32_t xt = smem_u32(x_ring + sx * Cfg::kXBytes);
@@ -217,6 +235,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         umma_commit(&empty_x[sx]);
       }
       umma_commit(acc_ready);  // arrives when every MMA above has completed
+      gtrace(tslot, 4);
     }
   } else if (warp >= 4) {
     // Epilogue warps: warp w may touch tensor-memory lanes 32*(w%4) .. +31.
@@ -225,6 +244,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!mbar_wait(acc_ready, 0)) ok = false;
     }
     tc_fence_after();
+    if (threadIdx.x == 128) gtrace(tslot, 5);
     pdl_wait();  // the partial buffer may still be read by the kernel before the producer of x
     const uint32_t n = n0 + lq * 32 + lane;
     float *dst = partial + (size_t)split * M * N;
@@ -248,6 +268,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
   }
+  if (threadIdx.x == 128) gtrace(tslot, 6);
   if (!ok) atomicOr(&g_gemm_error, 1u);
   tc_fence_before();
   __syncthreads();
@@ -384,6 +405,26 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
 }
 
 int gemm_tc_poll_error(uint32_t *code) {
+  static const bool tracing = std::getenv("ORION_GEMM_TRACE") != nullptr;
+  if (tracing) {
+    static unsigned long long t[kTraceLaunches][kTraceStamps];
+    uint32_t next = 0, on = 1;
+    cudaMemcpyFromSymbol(t, g_gemm_trace, sizeof t);
+    cudaMemcpyFromSymbol(&next, g_gemm_trace_next, sizeof next);
+    cudaMemcpyToSymbol(g_gemm_trace_on, &on, sizeof on);
+    if (next >= (uint32_t)kTraceLaunches) {
+      unsigned long long prev_end = 0;
+      fprintf(stderr, "gemm trace of CTA 0 (us): grid.x splits slabs | gap-from-prev-end setup first-W pdl-wait last-mma acc-ready epilogue total\n");
+      for (int i = 0; i < kTraceLaunches; ++i) {
+        const unsigned long long *r = t[(next + i) % kTraceLaunches];
+        fprintf(stderr, "  %4u %2u %3u | %7.2f %6.2f %6.2f %6.2f %6.2f %6.2f %6.2f %6.2f\n", (unsigned)(r[7] >> 32),
+                (unsigned)((r[7] >> 16) & 0xFFFF), (unsigned)(r[7] & 0xFFFF), prev_end ? ((double)r[0] - (double)prev_end) / 1e3 : 0.0,
+                (r[1] - r[0]) / 1e3, (r[2] - r[0]) / 1e3, (r[3] - r[0]) / 1e3, (r[4] - r[0]) / 1e3, (r[5] - r[0]) / 1e3,
+                (r[6] - r[0]) / 1e3, (r[6] - r[0]) / 1e3);
+        prev_end = r[6];
+      }
+    }
+  }
   uint32_t v = 0;
   ORION_CUDA_CHECK("gemm error word", cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof v));
   if (v) {

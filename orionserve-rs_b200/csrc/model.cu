@@ -97,7 +97,7 @@ class Model final : public ModelBase {
   int finalize() override;
   int forward(const BatchView &b, float *logits_out, uint64_t logits_capacity,
               uint32_t *token_ids_out) override;
-  int replay(int iterations, float *elapsed_ms) override;
+  int replay(int iterations, uint32_t category_mask, float *elapsed_ms) override;
   int profile(int iterations, float category_ms[kProfCategories],
               uint64_t category_launches[kProfCategories]) override;
   int fill_kv_random(uint64_t seed, float std) override;
@@ -153,6 +153,7 @@ class Model final : public ModelBase {
   std::vector<cudaEvent_t> prof_pool_;
   size_t prof_used_ = 0;
   bool prof_on_ = false;
+  uint32_t only_mask_ = 0;  // non-zero: launch only these kernel categories (timing replays)
   cudaEvent_t prof_event() {
     if (prof_used_ == prof_pool_.size()) {
       cudaEvent_t e = nullptr;
@@ -163,10 +164,9 @@ class Model final : public ModelBase {
   }
   template <typename F>
   int timed(int cat, F &&fn) {
-    // Timing diagnostic only: ORION_DEBUG_SKIP is a bit mask of kernel categories to leave out
-    // of the step (results are then meaningless; used to attribute step time under overlap).
-    static const int skip = std::getenv("ORION_DEBUG_SKIP") ? std::atoi(std::getenv("ORION_DEBUG_SKIP")) : 0;
-    if (skip & (1 << cat)) return ORION_OK;
+    // Timing only: a replay restricted to some kernel categories launches just those, back to
+    // back, on whatever the buffers hold (the results are meaningless, the shapes are the step's).
+    if (only_mask_ && !(only_mask_ & (1u << cat))) return ORION_OK;
     if (!prof_on_) return fn();
     cudaEvent_t a = prof_event(), b = prof_event();
     cudaEventRecord(a, stream_);
@@ -855,17 +855,23 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
 }
 
 template <typename T>
-int Model<T>::replay(int iterations, float *elapsed_ms) {
+int Model<T>::replay(int iterations, uint32_t category_mask, float *elapsed_ms) {
   if (meta_.rows == 0 || meta_.zero_count)
     return set_error(ORION_ERR_INVALID_REQUEST, "replay needs a preceding successful forward");
   ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
   ORION_CUDA_CHECK("replay", cudaStreamSynchronize(stream_));
   ORION_CUDA_CHECK("replay", cudaEventRecord(ev0_, stream_));
+  only_mask_ = category_mask & ((1u << kProfCategories) - 1);
   for (int i = 0; i < iterations; ++i) {
     g_launch_count = 0;
-    ORION_TRY(run_step(false));
+    const int rc = run_step(false);
+    if (rc != ORION_OK) {
+      only_mask_ = 0;
+      return rc;
+    }
     last_launches_ = g_launch_count;
   }
+  only_mask_ = 0;
   ORION_CUDA_CHECK("replay", cudaEventRecord(ev1_, stream_));
   ORION_CUDA_CHECK("replay", cudaEventSynchronize(ev1_));
   float ms = 0.f;

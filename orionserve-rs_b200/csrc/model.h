@@ -58,7 +58,7 @@ class ModelBase {
   virtual int finalize() = 0;
   virtual int forward(const BatchView &b, float *logits_out, uint64_t logits_capacity,
                       uint32_t *token_ids_out) = 0;
-  virtual int replay(int iterations, float *elapsed_ms) = 0;
+  virtual int replay(int iterations, uint32_t category_mask, float *elapsed_ms) = 0;
   virtual int profile(int iterations, float category_ms[kProfCategories],
                       uint64_t category_launches[kProfCategories]) = 0;
   virtual int fill_kv_random(uint64_t seed, float std) = 0;

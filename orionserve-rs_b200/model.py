@@ -299,6 +299,18 @@ class CudaTransformerModel:
         check(_ffi.lib().orion_cuda_model_replay(self._h, iterations, C.byref(ms)))
         return ms.value
 
+    CATEGORIES = ("gemm", "attention", "elementwise", "collective")
+
+    def replay_categories(self, iterations: int, *names: str) -> float:
+        """Timing only: replays just the kernels of the named categories back to back, as they
+        run inside a step; returns elapsed ms. Buffer contents are meaningless afterwards."""
+        mask = 0
+        for n in names:
+            mask |= 1 << self.CATEGORIES.index(n)
+        ms = C.c_float()
+        check(_ffi.lib().orion_cuda_model_replay_categories(self._h, iterations, mask, C.byref(ms)))
+        return ms.value
+
     def profile(self, iterations: int):
         """Per-category device time of the previous batch: dict name -> (ms, launches), summed
         over ``iterations`` replays."""

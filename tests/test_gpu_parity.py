@@ -288,6 +288,19 @@ def test_tiny_model_matches_the_oracle_and_keeps_its_invariants(pkg, backend, or
     assert np.max(np.abs(a - b)) < 1e-5
 
 
+def test_timing_replays_leave_the_next_forward_unchanged(pkg, backend):
+    m = _tiny(pkg, backend, 2, pkg.DType.F32)
+    batch = _one(pkg, [1, 2, 3], [0, 1, 2], [0])
+    first = m.forward(batch).logits.copy()
+    assert m.replay(2) > 0.0
+    for name in ("gemm", "attention", "elementwise"):
+        assert m.replay_categories(2, name) > 0.0
+    assert m.replay_categories(1, "gemm", "attention") > 0.0
+    with pytest.raises(pkg.InvalidRequest, match="category mask"):
+        m.replay_categories(1)
+    assert np.array_equal(m.forward(batch).logits, first)
+
+
 def test_forward_errors_precede_any_kv_write(pkg, backend):
     m = _tiny(pkg, backend, 1, pkg.DType.F32)
     with pytest.raises(pkg.InternalError, match="outside the vocabulary"):
