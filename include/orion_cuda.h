@@ -34,7 +34,10 @@ typedef enum OrionStatus {
   ORION_ERR_BACKEND = 2,         /* EngineError::Backend{backend:"cuda",stage,reason} (error.rs:119-124) */
   ORION_ERR_INVALID_REQUEST = 3, /* EngineError::InvalidRequest (orion-distributed/src/lib.rs:76-88) */
   ORION_ERR_UNAVAILABLE = 4,     /* CudaUnavailable::{NoDriver,NoDevices,NoSuchDevice} (orion-cuda/src/lib.rs:40-49) */
-  ORION_ERR_MODEL = 5            /* ModelError::{Malformed,MissingTensor,UnsupportedDtype} (transformer.rs:62-120) */
+  ORION_ERR_MODEL = 5,           /* ModelError::{Malformed,MissingTensor,UnsupportedDtype} (transformer.rs:62-120) */
+  ORION_ERR_CONTEXT_LENGTH = 6,  /* EngineError::ContextLengthExceeded (error.rs:84-92) */
+  ORION_ERR_QUEUE_FULL = 7,      /* EngineError::QueueFull, retryable (error.rs:95-96) */
+  ORION_ERR_CACHE_EXHAUSTED = 8  /* EngineError::CacheExhausted, retryable (error.rs:100-101) */
 } OrionStatus;
 
 /* DType (crates/orion-core/src/traits.rs:21-29). */

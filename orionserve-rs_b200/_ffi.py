@@ -13,7 +13,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liborion_cuda.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "orion_cuda.h")
 
-ORION_OK, ERR_INTERNAL, ERR_BACKEND, ERR_INVALID_REQUEST, ERR_UNAVAILABLE, ERR_MODEL = range(6)
+DRIVER_HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "orion_driver.h")
+
+(ORION_OK, ERR_INTERNAL, ERR_BACKEND, ERR_INVALID_REQUEST, ERR_UNAVAILABLE, ERR_MODEL, ERR_CONTEXT_LENGTH,
+ ERR_QUEUE_FULL, ERR_CACHE_EXHAUSTED) = range(9)
 NCCL_ID_BYTES = 128
 
 
@@ -100,6 +103,98 @@ SIGNATURES = {
 }
 
 
+class OrionAllocationOutcome(C.Structure):
+    _fields_ = [("allocated", C.c_uint64), ("reused", C.c_uint64), ("cached_tokens", C.c_uint64)]
+
+
+class OrionCacheStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("total_blocks", "used_blocks", "free_blocks", "block_size", "num_sequences",
+                                          "prefix_cache_entries", "prefix_cache_hits", "prefix_cache_misses")]
+
+
+class OrionSchedulerConfig(C.Structure):
+    _fields_ = [("max_num_seqs", C.c_uint64), ("max_num_batched_tokens", C.c_uint64), ("max_model_len", C.c_uint64),
+                ("enable_chunked_prefill", C.c_uint32), ("max_waiting_requests", C.c_uint64),
+                ("request_timeout_secs", C.c_uint64), ("prioritize_decode", C.c_uint32)]
+
+
+class OrionSamplingParams(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("repetition_penalty", C.c_float),
+                ("top_k", C.c_uint64), ("max_tokens", C.c_uint64), ("min_tokens", C.c_uint64),
+                ("stop_token_ids", C.POINTER(C.c_uint32)), ("num_stop_token_ids", C.c_uint64)]
+
+
+class OrionScheduledSequence(C.Structure):
+    _fields_ = [("id", C.c_uint64), ("num_tokens", C.c_uint64), ("start_position", C.c_uint64),
+                ("is_prefill", C.c_uint32)]
+
+
+class OrionSchedulerStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("total_steps", "total_admitted", "total_finished", "total_preempted",
+                                          "total_rejected", "total_batched_tokens", "total_prefill_tokens",
+                                          "total_decode_tokens")]
+
+
+class OrionEngineEvent(C.Structure):
+    _fields_ = [("id", C.c_uint64), ("kind", C.c_uint32), ("token", C.c_uint32), ("index", C.c_uint64),
+                ("reason", C.c_uint32), ("prompt_tokens", C.c_uint64), ("completion_tokens", C.c_uint64)]
+
+
+_u64 = C.c_uint64
+_u32p, _u64p = C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)
+FORWARD_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, _u32p, _u64, _u32p, _u64p, _u64p, _u64p, _u32p, _u64p, _u64, C.c_int,
+                         _u32p)
+
+# include/orion_driver.h
+DRIVER_SIGNATURES = {
+    "orion_hash_block": (_u64, [C.c_int, _u64, _u32p, _u64]),
+    "orion_sequence_id_peek": (_u64, []),
+    "orion_kv_manager_create": (C.c_void_p, [_u64, _u64, C.c_int]),
+    "orion_kv_manager_destroy": (None, [C.c_void_p]),
+    "orion_kv_manager_allocate": (C.c_int, [C.c_void_p, _u64, _u32p, _u64, C.POINTER(OrionAllocationOutcome)]),
+    "orion_kv_manager_commit_prefill": (None, [C.c_void_p, _u64, _u32p, _u64]),
+    "orion_kv_manager_append_token": (C.c_int, [C.c_void_p, _u64]),
+    "orion_kv_manager_free": (None, [C.c_void_p, _u64]),
+    "orion_kv_manager_preempt": (_u64, [C.c_void_p, _u64]),
+    "orion_kv_manager_stats": (C.c_int, [C.c_void_p, C.POINTER(OrionCacheStats)]),
+    "orion_kv_manager_can_allocate": (C.c_int, [C.c_void_p, _u64]),
+    "orion_kv_manager_blocks_needed_for": (_u64, [C.c_void_p, _u64]),
+    "orion_kv_manager_evict_cached": (_u64, [C.c_void_p, _u64]),
+    "orion_kv_manager_clear_prefix_cache": (None, [C.c_void_p]),
+    "orion_kv_manager_num_evictable": (_u64, [C.c_void_p]),
+    "orion_kv_manager_block_table": (C.c_int, [C.c_void_p, _u64, _u32p, _u64, _u64p, _u64p]),
+    "orion_kv_manager_block_info": (C.c_int, [C.c_void_p, C.c_uint32, _u32p, _u64p, C.POINTER(C.c_int), _u64p]),
+    "orion_kv_manager_fail_next": (None, [C.c_void_p, C.c_int]),
+    "orion_scheduler_create": (C.c_void_p, [C.POINTER(OrionSchedulerConfig), _u64, _u64, C.c_int]),
+    "orion_scheduler_destroy": (None, [C.c_void_p]),
+    "orion_scheduler_cache": (C.c_void_p, [C.c_void_p]),
+    "orion_scheduler_add_request": (C.c_int, [C.c_void_p, _u32p, _u64, C.POINTER(OrionSamplingParams), _u64p]),
+    "orion_scheduler_cancel": (C.c_int, [C.c_void_p, _u64]),
+    "orion_scheduler_schedule": (C.c_int, [C.c_void_p, C.POINTER(OrionScheduledSequence), _u64, _u64p, _u64p, _u64,
+                                           _u64p]),
+    "orion_scheduler_on_token": (C.c_int, [C.c_void_p, _u64, C.c_uint32, _u32p, _u64]),
+    "orion_scheduler_reap_finished": (_u64, [C.c_void_p, _u64p, _u64]),
+    "orion_scheduler_commit_prefill": (None, [C.c_void_p, _u64]),
+    "orion_scheduler_num_waiting": (_u64, [C.c_void_p]),
+    "orion_scheduler_num_running": (_u64, [C.c_void_p]),
+    "orion_scheduler_stats": (C.c_int, [C.c_void_p, C.POINTER(OrionSchedulerStats)]),
+    "orion_scheduler_running_sequence": (C.c_int, [C.c_void_p, _u64, C.POINTER(C.c_int), _u64p, _u64p]),
+    "orion_engine_create": (C.c_void_p, [C.c_void_p, FORWARD_FN, C.c_void_p, C.POINTER(OrionSchedulerConfig), _u64,
+                                         _u64, C.c_int, _u32p, _u64]),
+    "orion_engine_destroy": (None, [C.c_void_p]),
+    "orion_engine_scheduler": (C.c_void_p, [C.c_void_p]),
+    "orion_engine_submit": (C.c_int, [C.c_void_p, _u32p, _u64, C.POINTER(OrionSamplingParams), _u64p]),
+    "orion_engine_cancel": (None, [C.c_void_p, _u64]),
+    "orion_engine_has_work": (C.c_int, [C.c_void_p]),
+    "orion_engine_step": (C.c_int, [C.c_void_p, _u64p]),
+    "orion_engine_take_events": (_u64, [C.c_void_p, C.POINTER(OrionEngineEvent), _u64]),
+    "orion_engine_num_active": (_u64, [C.c_void_p]),
+    "orion_engine_last_batch": (C.c_int, [C.c_void_p, C.POINTER(_u32p), _u64p, C.POINTER(_u32p), C.POINTER(_u64p),
+                                          C.POINTER(_u64p), C.POINTER(_u64p), C.POINTER(_u32p), C.POINTER(_u64p),
+                                          _u64p, C.POINTER(C.c_int)]),
+}
+
+
 def lib() -> C.CDLL:
     """Loads the shared library, declaring every entry point; raises if it is absent."""
     global _lib
@@ -110,7 +205,7 @@ def lib() -> C.CDLL:
             f"{LIB_PATH} is not built; run `python -c 'import __graft_entry__ as g; g.build()'`. "
             "There is no CPU fallback for the forward path.")
     L = C.CDLL(LIB_PATH)
-    for name, (res, args) in SIGNATURES.items():
+    for name, (res, args) in list(SIGNATURES.items()) + list(DRIVER_SIGNATURES.items()):
         fn = getattr(L, name)  # AttributeError here means the library lacks a declared symbol
         fn.restype = res
         fn.argtypes = args

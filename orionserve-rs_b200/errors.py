@@ -29,12 +29,27 @@ class ModelError(EngineError):
     """``ModelError::{Malformed, MissingTensor, UnsupportedDtype}``."""
 
 
+class ContextLengthExceeded(EngineError):
+    """``EngineError::ContextLengthExceeded``: prompt plus requested output do not fit the context."""
+
+
+class QueueFull(EngineError):
+    """``EngineError::QueueFull``: the waiting queue is at its limit (retryable)."""
+
+
+class CacheExhausted(EngineError):
+    """``EngineError::CacheExhausted``: not enough free KV blocks (retryable)."""
+
+
 _BY_STATUS = {
     _ffi.ERR_INTERNAL: InternalError,
     _ffi.ERR_BACKEND: BackendError,
     _ffi.ERR_INVALID_REQUEST: InvalidRequest,
     _ffi.ERR_UNAVAILABLE: CudaUnavailable,
     _ffi.ERR_MODEL: ModelError,
+    _ffi.ERR_CONTEXT_LENGTH: ContextLengthExceeded,
+    _ffi.ERR_QUEUE_FULL: QueueFull,
+    _ffi.ERR_CACHE_EXHAUSTED: CacheExhausted,
 }
 
 

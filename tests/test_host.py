@@ -21,6 +21,16 @@ def test_library_exports_every_symbol_the_header_declares(pkg):
     pkg._ffi.lib()
 
 
+def test_library_exports_every_driver_symbol_the_header_declares(pkg):
+    header = open(os.path.join(ROOT, "include", "orion_driver.h")).read()
+    declared = set(re.findall(r"\b(orion_(?:hash_block|sequence_id|kv_manager|scheduler|engine)[a-z0-9_]*)\s*\(", header))
+    assert len(declared) >= 40
+    lib = ctypes.CDLL(pkg._ffi.LIB_PATH)
+    missing = [n for n in sorted(declared) if not hasattr(lib, n)]
+    assert not missing, f"declared but not exported: {missing}"
+    assert declared == set(pkg._ffi.DRIVER_SIGNATURES), "the ctypes table and the header must list the same symbols"
+
+
 def test_without_a_device_construction_fails_loudly(pkg):
     if pkg.is_available():
         pytest.skip("a CUDA device is present")
