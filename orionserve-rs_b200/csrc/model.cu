@@ -75,9 +75,10 @@ enum : uint32_t {
 template <typename T>
 class Model final : public ModelBase {
  public:
-  Model(OrionBackend *backend, const OrionModelDesc &d) : backend_(backend), d_(d) {}
+  // Only the ordinal is kept: the model may outlive the backend handle it was created from.
+  Model(OrionBackend *backend, const OrionModelDesc &d) : ordinal_(backend->ordinal), d_(d) {}
   ~Model() override {
-    cudaSetDevice(backend_->ordinal);
+    cudaSetDevice(ordinal_);
     if (stream_) cudaStreamSynchronize(stream_);
     for (void *p : ipc_opened_) cudaIpcCloseMemHandle(p);
     for (void *p : allocs_) cudaFree(p);
@@ -176,7 +177,7 @@ class Model final : public ModelBase {
     return rc;
   }
 
-  OrionBackend *backend_;
+  int ordinal_;
   OrionModelDesc d_;
   cudaStream_t stream_ = nullptr;
   cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
@@ -207,6 +208,10 @@ class Model final : public ModelBase {
     size_t tokens = 0, positions = 0, slot_block = 0, slot_slot = 0, seq_of_row = 0, last_rows = 0,
            offsets = 0, tables = 0, tiles = 0, total = 0;
     uint32_t num_tiles = 0;  // prefill attention tiles (0 = the batch does not use that kernel)
+    // Mixed batches: a run of one-token sequences at the head or the tail of the batch (the
+    // scheduler puts all decodes before or after all prefills, scheduler.rs:244-250) goes to
+    // the decode attention kernel, the other rows to the prefill kernel.
+    uint32_t dec_row0 = 0, dec_rows = 0;
   } meta_;
 
   void *stage_raw_ = nullptr, *stage_f32_ = nullptr;
@@ -238,7 +243,7 @@ int Model<T>::init() {
   lkv_ = (uint32_t)lay_.kv_heads.len;
   lf_ = (uint32_t)lay_.ffn.len;
 
-  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  ORION_CUDA_CHECK("set device", cudaSetDevice(ordinal_));
   ORION_CUDA_CHECK("create stream", cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
   ORION_CUDA_CHECK("create event", cudaEventCreate(&ev0_));
   ORION_CUDA_CHECK("create event", cudaEventCreate(&ev1_));
@@ -411,7 +416,7 @@ template <typename T>
 int Model<T>::load_tensor(const char *name, int dtype, const uint64_t *shape, int ndim,
                           const void *data) {
   const OrionModelDesc &d = d_;
-  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  ORION_CUDA_CHECK("set device", cudaSetDevice(ordinal_));
   if (dtype_size(dtype) == 0 || dtype == ORION_DTYPE_I8 || dtype == ORION_DTYPE_I4)
     return set_error(ORION_ERR_MODEL, "unsupported dtype %d (tensor `%s`)", dtype, name);  // loader.rs:89-93
   if (!data || ndim < 1 || ndim > 2) return set_error(ORION_ERR_MODEL, "tensor `%s` has rank %d", name, ndim);
@@ -518,7 +523,7 @@ int Model<T>::init_random(uint64_t seed, float std) {
   // N(0, std) matrices, RMSNorm weights 1.0, zero biases. Values are drawn on
   // the device; they depend on (seed, tensor index) only.
   const OrionModelDesc &d = d_;
-  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  ORION_CUDA_CHECK("set device", cudaSetDevice(ordinal_));
   const size_t H = d.hidden_size, hd = d.head_dim, V = d.vocab_size;
   uint64_t tensor = 0;
   auto fill = [&](T *p, size_t n) -> int {
@@ -639,10 +644,20 @@ int Model<T>::run_step(bool want_argmax) {
         ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_decode(qbuf_, arena_, kv_, l, ab, lq_, dsplits, sc, attn_, stream_,
                                                                                      hint(L.w_o, (size_t)H * qd)); }));
       }
-    } else if (meta_.num_tiles > 0) {
+    } else if (meta_.num_tiles > 0 || meta_.dec_rows > 0) {
       if constexpr (kBf16) {
-        const PrefillTile *tiles = reinterpret_cast<const PrefillTile *>(m + meta_.tiles);
-        ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_prefill(qbuf_, arena_, kv_, l, ab, tiles, meta_.num_tiles, lq_, attn_, stream_); }));
+        if (meta_.dec_rows > 0) {  // the decode rows of a mixed batch: one contiguous run of rows
+          const uint32_t r0 = meta_.dec_row0, n = meta_.dec_rows;
+          AttnBatch sub{positions + r0, m + meta_.seq_of_row + r0, ab.tables_flat, ab.table_offsets, n, meta_.max_position};
+          const uint32_t sp = decode_choose_splits(n, lkv_, meta_.max_position, d.block_size, 32);
+          DecodeScratch sc{dscratch_, dscratch_ + (size_t)n * lq_ * sp * hd, sp};
+          ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_decode(qbuf_ + (size_t)r0 * qd, arena_, kv_, l, sub, lq_, sp, sc,
+                                                                                       attn_ + (size_t)r0 * qd, stream_); }));
+        }
+        if (meta_.num_tiles > 0) {
+          const PrefillTile *tiles = reinterpret_cast<const PrefillTile *>(m + meta_.tiles);
+          ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_prefill(qbuf_, arena_, kv_, l, ab, tiles, meta_.num_tiles, lq_, attn_, stream_); }));
+        }
       }
     } else {
       ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_generic<T>(qbuf_, arena_, kv_, l, ab, lq_, attn_, stream_); }));
@@ -713,7 +728,7 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
     return set_error(ORION_ERR_INVALID_REQUEST, "logits buffer holds %llu floats, %llu needed",
                      (unsigned long long)logits_capacity, (unsigned long long)(S * (uint64_t)d.vocab_size));
 
-  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  ORION_CUDA_CHECK("set device", cudaSetDevice(ordinal_));
   const uint64_t table_entries = b.block_table_offsets[S];
   Meta mt;
   mt.rows = (uint32_t)Tn;
@@ -797,11 +812,24 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
   if (table_entries) std::memcpy(h + mt.tables, b.block_tables_flat, table_entries * sizeof(uint32_t));
   mt.decode = all_single;
   if (tuned_prefill && !all_single) {
+    if (decode_attention_supported(kv_, lq_)) {
+      uint64_t head = 0, tail = 0;
+      while (head < S && b.slot_token_counts[head] == 1) ++head;
+      while (tail < S && b.slot_token_counts[S - 1 - tail] == 1) ++tail;
+      if (std::max(head, tail) >= 8) {  // worth a launch of its own
+        mt.dec_rows = (uint32_t)std::max(head, tail);
+        mt.dec_row0 = head >= tail ? 0u : (uint32_t)(Tn - tail);
+      }
+    }
     // Tiles of consecutive rows of one sequence for the prefill attention kernel.
     uint32_t *t = h + mt.tiles;
     uint64_t row = 0;
     for (uint64_t s = 0; s < S; ++s) {
       const uint64_t end = row + b.slot_token_counts[s];
+      if (row >= mt.dec_row0 && row < (uint64_t)mt.dec_row0 + mt.dec_rows) {  // a decode row: no tile
+        row = end;
+        continue;
+      }
       while (row < end) {
         const uint32_t n = (uint32_t)std::min<uint64_t>(tile_rows, end - row);
         uint32_t max_pos = 0;
@@ -858,7 +886,7 @@ template <typename T>
 int Model<T>::replay(int iterations, uint32_t category_mask, float *elapsed_ms) {
   if (meta_.rows == 0 || meta_.zero_count)
     return set_error(ORION_ERR_INVALID_REQUEST, "replay needs a preceding successful forward");
-  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  ORION_CUDA_CHECK("set device", cudaSetDevice(ordinal_));
   ORION_CUDA_CHECK("replay", cudaStreamSynchronize(stream_));
   ORION_CUDA_CHECK("replay", cudaEventRecord(ev0_, stream_));
   only_mask_ = category_mask & ((1u << kProfCategories) - 1);
@@ -885,7 +913,7 @@ int Model<T>::profile(int iterations, float category_ms[kProfCategories],
                       uint64_t category_launches[kProfCategories]) {
   if (meta_.rows == 0 || meta_.zero_count)
     return set_error(ORION_ERR_INVALID_REQUEST, "profile needs a preceding successful forward");
-  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  ORION_CUDA_CHECK("set device", cudaSetDevice(ordinal_));
   for (int c = 0; c < kProfCategories; ++c) {
     category_ms[c] = 0.f;
     category_launches[c] = 0;
@@ -910,7 +938,7 @@ int Model<T>::profile(int iterations, float category_ms[kProfCategories],
 
 template <typename T>
 int Model<T>::fill_kv_random(uint64_t seed, float std) {
-  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  ORION_CUDA_CHECK("set device", cudaSetDevice(ordinal_));
   const size_t total = kv_.layer_elems() * d_.num_layers;
   const size_t chunk = 64u << 20;
   ORION_TRY(ensure_stage(&stage_f32_, &stage_f32_cap_, std::min(total, chunk) * sizeof(float)));
@@ -930,7 +958,7 @@ int Model<T>::read_kv(float *out, uint64_t capacity) {
   if (capacity < total)
     return set_error(ORION_ERR_INVALID_REQUEST, "KV read-back buffer holds %llu floats, %zu needed",
                      (unsigned long long)capacity, total);
-  ORION_CUDA_CHECK("set device", cudaSetDevice(backend_->ordinal));
+  ORION_CUDA_CHECK("set device", cudaSetDevice(ordinal_));
   float *tmp = nullptr;
   ORION_CUDA_CHECK("allocate", cudaMalloc(&tmp, (total ? total : 1) * sizeof(float)));
   int rc = launch_arena_to_reference_order<T>(arena_, kv_, tmp, stream_);

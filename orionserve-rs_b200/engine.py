@@ -141,7 +141,10 @@ def next_sequence_id() -> int:
 class KvCacheManager:
     """``KvCacheManager`` (crates/orion-kv-cache/src/manager.rs:73-425)."""
 
-    def __init__(self, num_blocks: int, block_size: int, prefix_caching_enabled: bool, *, _borrowed=None):
+    def __init__(self, num_blocks: int, block_size: int, prefix_caching_enabled: bool, *, _borrowed=None, _keep=None):
+        # A borrowed view keeps its owner alive (`_keep`); owners never point back at their views,
+        # so there is no reference cycle and handles are destroyed in dependency order.
+        self._keep = _keep
         self._owned = _borrowed is None
         self._h = _borrowed or _ffi.lib().orion_kv_manager_create(num_blocks, block_size, int(prefix_caching_enabled))
         if not self._h:
@@ -241,7 +244,6 @@ class Scheduler:
             self._h = _borrowed
         if not self._h:
             raise EngineError(_ffi.last_error())
-        self._cache = KvCacheManager(0, 1, False, _borrowed=_ffi.lib().orion_scheduler_cache(self._h))
 
     def __del__(self):
         if getattr(self, "_owned", False) and getattr(self, "_h", None):
@@ -249,7 +251,7 @@ class Scheduler:
             self._h = None
 
     def cache(self) -> KvCacheManager:
-        return self._cache
+        return KvCacheManager(0, 1, False, _borrowed=_ffi.lib().orion_scheduler_cache(self._h), _keep=self)
 
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
         keep, ptr = _u32(prompt)
@@ -343,7 +345,7 @@ class Engine:
                                                  int(prefix_caching_enabled), eos, len(keep))
         if not self._h:
             raise EngineError(_ffi.last_error())
-        self._sched = Scheduler(config, 0, 1, _borrowed=_ffi.lib().orion_engine_scheduler(self._h), _keep=self)
+        self._config = config
 
     def __del__(self):
         if getattr(self, "_h", None):
@@ -366,7 +368,7 @@ class Engine:
             return _ffi.ERR_INTERNAL
 
     def scheduler(self) -> Scheduler:
-        return self._sched
+        return Scheduler(self._config, 0, 1, _borrowed=_ffi.lib().orion_engine_scheduler(self._h), _keep=self)
 
     def submit(self, prompt: Sequence[int], params: SamplingParams) -> int:
         keep, ptr = _u32(prompt)

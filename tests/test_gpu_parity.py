@@ -446,6 +446,56 @@ def test_chunked_prefill_and_mixed_batches_on_the_tuned_path(pkg, backend, oracl
     assert rep.passed(), rep.render()
 
 
+@pytest.mark.parametrize("decodes_first", [True, False])
+def test_mixed_batch_with_a_run_of_decode_rows(pkg, backend, oracle, decodes_first):
+    """A mixed batch whose one-token sequences form a run of 8 or more at the head (decode-first
+    scheduling) or the tail (prefill-first) of the batch: those rows take the decode attention
+    kernel, the prefill chunks the prefill kernel, in the same step."""
+    meta_d = dict(hidden_size=256, num_layers=2, num_attention_heads=8, num_kv_heads=2, head_dim=128,
+                  vocab_size=384, ffn_dim=512, max_position_embeddings=1024, rope_theta=10000.0,
+                  rms_norm_eps=1e-5, has_qkv_bias=False, tied_lm_head=False, num_blocks=160, block_size=16)
+    t = {k: (oracle.round_to_bf16(v) if v.ndim == 2 else v)
+         for k, v in random_tensors(np.random.default_rng(5), meta_d, std=0.05).items()}
+    ref = oracle.Model(**meta_d).load(t)
+    meta = pkg.ModelMetadata(architecture="llama", name="p",
+                             **{k: v for k, v in meta_d.items() if k not in ("num_blocks", "block_size")})
+    dev = pkg.CudaTransformerModel.new(meta, t, 160, 16, backend, compute_dtype=pkg.DType.BF16,
+                                       max_batch_tokens=1024, max_batch_sequences=16)
+    rng = np.random.default_rng(17)
+    lens = [33, 70, 16, 95, 48, 129, 5, 64, 81, 17, 110]  # eleven decoders
+    prompts = [rng.integers(0, 384, n).tolist() for n in lens]
+    perm = rng.permutation(160).tolist()
+    tables = [[perm.pop() for _ in range(len(p) // 16 + 1)] for p in prompts]
+    oracle.set_threads(8)
+
+    def run(tokens, positions, counts, ctx, tabs):
+        ids = list(range(1, len(counts) + 1))
+        exp = ref.forward(oracle.Batch(tokens, positions, counts, ctx, tabs))
+        got = dev.forward(pkg.ForwardBatch(tokens, positions, ids, counts, ctx, tabs, has_prefill=True)).logits
+        assert float(np.max(np.abs(softmax_rows(got) - softmax_rows(exp)))) < BF16_SOFTMAX
+        assert rel_err(got, exp) < 3e-2
+        return exp
+
+    # step 1: prefill all eleven prompts (a pure prefill batch)
+    toks = sum(prompts, [])
+    pos = sum((list(range(len(p))) for p in prompts), [])
+    exp = run(toks, pos, [len(p) for p in prompts], [len(p) for p in prompts], tables)
+    nxt = [int(oracle.argmax(r)) for r in exp]
+    # step 2: eleven decode rows plus two fresh prefill chunks, decodes at the head or the tail
+    new_prompts = [rng.integers(0, 384, n).tolist() for n in (90, 41)]
+    new_tables = [[perm.pop() for _ in range(len(p) // 16 + 1)] for p in new_prompts]
+    dec = dict(tokens=nxt, positions=[len(p) for p in prompts], counts=[1] * 11, ctx=[len(p) + 1 for p in prompts],
+               tabs=tables)
+    pre = dict(tokens=sum(new_prompts, []), positions=sum((list(range(len(p))) for p in new_prompts), []),
+               counts=[len(p) for p in new_prompts], ctx=[len(p) for p in new_prompts], tabs=new_tables)
+    first, second = (dec, pre) if decodes_first else (pre, dec)
+    run(*[first[k] + second[k] for k in ("tokens", "positions", "counts", "ctx", "tabs")])
+    oracle.set_threads(1)
+    kv_dev, kv_ref = dev.read_kv(), ref.kv().array()
+    assert np.array_equal(kv_dev != 0, kv_ref != 0), "exactly the same slots were written"
+    assert pkg.validate("kv_arena", kv_ref, kv_dev, pkg.Tolerance(0.1, 0.1)).passed()
+
+
 def test_qwen2_shape_with_qkv_bias(pkg, backend, oracle):
     meta_d = dict(SMALL_META, hidden_size=128, head_dim=64, num_attention_heads=4, num_kv_heads=2,
                   ffn_dim=256, vocab_size=300, has_qkv_bias=True, num_blocks=16, block_size=16,
