@@ -318,8 +318,13 @@ int Model<T>::init() {
   if (d.tp_world > 1) {
     nccl_.reset(new NcclCollective());
     ORION_TRY(nccl_->init(d.nccl_unique_id, (int)d.tp_rank, (int)d.tp_world));
-    const char *mode = std::getenv("ORION_TP_ALLREDUCE");  // "nccl" keeps the library all-reduce
-    if (!(mode && !strcmp(mode, "nccl")) && d.tp_world <= (uint32_t)kMaxTpWorld && H % 4 == 0 && H / 4 <= 4096)
+    // The one-shot peer-memory hand-over sends every partial sum to every peer: the fastest way at
+    // 2 ranks (4.01 vs 4.53 ms per headline step), bandwidth-bound beyond (4 ranks: 4.29 vs 3.98 ms
+    // through NCCL; 8 ranks: 6.10 vs 4.09 ms), so it is the default at 2 ranks only.
+    // ORION_TP_ALLREDUCE=fused / nccl forces either.
+    const char *mode = std::getenv("ORION_TP_ALLREDUCE");
+    const bool want_fused = mode ? !strcmp(mode, "fused") : d.tp_world == 2;
+    if (want_fused && d.tp_world <= (uint32_t)kMaxTpWorld && H % 4 == 0 && H / 4 <= 4096)
       ORION_TRY(setup_peer_handover());
   }
   ORION_CUDA_CHECK("model init", cudaStreamSynchronize(stream_));

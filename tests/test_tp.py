@@ -16,11 +16,13 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _run_ranks(world: int, *worker_args: str, timeout: int = 600):
+def _run_ranks(world: int, *worker_args: str, timeout: int = 600, handover: str = ""):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(ROOT, "tests", "tp_worker.py"), *worker_args]
     env = dict(os.environ, OMP_NUM_THREADS="1", NCCL_NVLS_ENABLE="0")
+    if handover:  # "fused" = peer-memory all-reduce + residual + norm kernel, "nccl" = library all-reduce
+        env["ORION_TP_ALLREDUCE"] = handover
     return subprocess.run(cmd, cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                           timeout=timeout)
 
@@ -36,9 +38,22 @@ def test_four_gloo_ranks_reproduce_the_unsharded_forward():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("handover", ["fused", "nccl"])
 @pytest.mark.parametrize("dtype", ["F32", "BF16"])
-def test_two_gpu_ranks_match_the_oracle(pkg, dtype):
+def test_two_gpu_ranks_match_the_oracle(pkg, dtype, handover):
     if pkg.device_count() < 2:
         pytest.skip("needs two GPUs on the box")
-    r = _run_ranks(2, "--mode", "gpu", "--dtype", dtype)
+    r = _run_ranks(2, "--mode", "gpu", "--dtype", dtype, handover=handover)
+    assert r.returncode == 0, r.stdout[-3000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("handover", ["fused", "nccl"])
+@pytest.mark.parametrize("dtype", ["F32", "BF16"])
+def test_four_gpu_ranks_match_the_oracle(pkg, dtype, handover):
+    """One KV head per rank: the widest split the test model allows, and three peers per inbox in
+    the fused hand-over."""
+    if pkg.device_count() < 4:
+        pytest.skip("needs four GPUs on the box")
+    r = _run_ranks(4, "--mode", "gpu", "--dtype", dtype, handover=handover)
     assert r.returncode == 0, r.stdout[-3000:]
