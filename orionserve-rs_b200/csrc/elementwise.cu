@@ -236,7 +236,7 @@ __device__ __forceinline__ float silu_f(float g);
 template <typename T>
 __global__ void __launch_bounds__(256)
 swiglu_vec_kernel(const float *__restrict__ partial, uint32_t splits, size_t split_stride,
-                  T *__restrict__ act, uint32_t rows, uint32_t ffn) {
+                  T *__restrict__ act, uint32_t rows, uint32_t ffn, bool interleaved) {
   pdl_trigger();
   pdl_wait();
   const uint32_t fv = ffn / 4;
@@ -244,11 +244,24 @@ swiglu_vec_kernel(const float *__restrict__ partial, uint32_t splits, size_t spl
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t r = idx / fv, f = (idx % fv) * 4;
-    const float *pg = partial + r * 2 * ffn + f;
-    float4 g = ld4(pg), u = ld4(pg + ffn);
-    for (uint32_t s = 1; s < splits; ++s) {
-      g = add4(g, ld4(pg + s * split_stride));
-      u = add4(u, ld4(pg + s * split_stride + ffn));
+    float4 g, u;
+    if (interleaved) {  // columns 2f = gate f, 2f + 1 = up f
+      const float *pg = partial + r * 2 * ffn + 2 * f;
+      float4 a = ld4(pg), b = ld4(pg + 4);
+      for (uint32_t s = 1; s < splits; ++s) {
+        a = add4(a, ld4(pg + s * split_stride));
+        b = add4(b, ld4(pg + s * split_stride + 4));
+      }
+      g = make_float4(a.x, a.z, b.x, b.z);
+      u = make_float4(a.y, a.w, b.y, b.w);
+    } else {
+      const float *pg = partial + r * 2 * ffn + f;
+      g = ld4(pg);
+      u = ld4(pg + ffn);
+      for (uint32_t s = 1; s < splits; ++s) {
+        g = add4(g, ld4(pg + s * split_stride));
+        u = add4(u, ld4(pg + s * split_stride + ffn));
+      }
     }
     st4<T>(act + r * ffn + f,
            make_float4(__fmul_rn(silu_f<T>(g.x), u.x), __fmul_rn(silu_f<T>(g.y), u.y),
@@ -335,18 +348,19 @@ __device__ __forceinline__ float silu_f<bf16>(float g) { return g / (1.0f + __ex
 template <typename T>
 __global__ void swiglu_kernel(const float *__restrict__ partial, uint32_t splits,
                               size_t split_stride, T *__restrict__ act, uint32_t rows,
-                              uint32_t ffn) {
+                              uint32_t ffn, bool interleaved) {
   pdl_trigger();
   pdl_wait();
   const size_t total = (size_t)rows * ffn;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t r = idx / ffn, f = idx % ffn;
-    const float *pg = partial + r * 2 * ffn + f;
-    float g = pg[0], u = pg[ffn];
+    const float *pg = partial + r * 2 * ffn + (interleaved ? 2 * f : f);
+    const size_t up = interleaved ? 1 : ffn;
+    float g = pg[0], u = pg[up];
     for (uint32_t s = 1; s < splits; ++s) {
       g += pg[s * split_stride];
-      u += pg[s * split_stride + ffn];
+      u += pg[s * split_stride + up];
     }
     act[idx] = from_f32<T>(__fmul_rn(silu_f<T>(g), u));  // tensor.rs:186
   }
@@ -593,16 +607,33 @@ int launch_rope_rows(T *x, const uint32_t *positions, const float *rope_cos, con
 
 template <typename T>
 int launch_swiglu(const float *partial, uint32_t splits, size_t split_stride, T *act, uint32_t rows,
-                  uint32_t ffn, cudaStream_t stream) {
+                  uint32_t ffn, cudaStream_t stream, bool interleaved) {
   if (rows == 0 || ffn == 0) return ORION_OK;
   if (ffn % 4 == 0 && split_stride % 4 == 0) {
     ORION_CUDA_CHECK("swiglu", launch_pdl(swiglu_vec_kernel<T>, dim3(grid_for((size_t)rows * ffn / 4, 256)),
-                                          dim3(256), 0, stream, partial, splits, split_stride, act, rows, ffn));
+                                          dim3(256), 0, stream, partial, splits, split_stride, act, rows, ffn, interleaved));
     return after_launch("swiglu");
   }
   ORION_CUDA_CHECK("swiglu", launch_pdl(swiglu_kernel<T>, dim3(grid_for((size_t)rows * ffn, 256)), dim3(256), 0,
-                                        stream, partial, splits, split_stride, act, rows, ffn));
+                                        stream, partial, splits, split_stride, act, rows, ffn, interleaved));
   return after_launch("swiglu");
+}
+
+// dst[r * dst_stride + c] = src[r * cols + c]: spreads the rows of a contiguous matrix over a
+// strided destination (the gate and up projections are stored row-interleaved).
+template <typename T>
+__global__ void copy_rows_strided_kernel(const T *__restrict__ src, T *__restrict__ dst, size_t rows, size_t cols,
+                                         size_t dst_stride) {
+  const size_t total = rows * cols;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+    dst[(idx / cols) * dst_stride + idx % cols] = src[idx];
+}
+
+template <typename T>
+int launch_copy_rows_strided(const T *src, T *dst, size_t rows, size_t cols, size_t dst_stride, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return ORION_OK;
+  copy_rows_strided_kernel<T><<<grid_for(rows * cols, 256), 256, 0, stream>>>(src, dst, rows, cols, dst_stride);
+  return after_launch("copy_rows_strided");
 }
 
 int launch_finish_linear(const float *partial, uint32_t splits, size_t split_stride,
@@ -707,8 +738,9 @@ int launch_fill_normal(T *dst, size_t n, uint64_t seed, cudaStream_t stream) {
                                       uint32_t, uint32_t, cudaStream_t);                          \
   template int launch_rope_rows<T>(T *, const uint32_t *, const float *, const float *, uint32_t, \
                                    uint32_t, uint32_t, cudaStream_t);                             \
+  template int launch_copy_rows_strided<T>(const T *, T *, size_t, size_t, size_t, cudaStream_t);   \
   template int launch_swiglu<T>(const float *, uint32_t, size_t, T *, uint32_t, uint32_t,         \
-                                cudaStream_t);                                                    \
+                                cudaStream_t, bool);                                              \
   template int launch_convert_from_f32<T>(const float *, T *, size_t, cudaStream_t);              \
   template int launch_convert_to_f32<T>(const T *, float *, size_t, cudaStream_t);                \
   template int launch_arena_to_reference_order<T>(const T *, KvLayout, float *, cudaStream_t);    \

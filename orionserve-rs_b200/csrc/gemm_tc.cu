@@ -135,8 +135,8 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
 template <int TOKN, int WST, int XST>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               float *__restrict__ partial, uint32_t M, uint32_t N, uint32_t K, uint32_t splits,
-               PrefetchHint next) {
+               float *__restrict__ partial, bf16 *__restrict__ act, uint32_t M, uint32_t N, uint32_t K,
+               uint32_t splits, PrefetchHint next) {
   using Cfg = TcConfig<TOKN, WST, XST>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
@@ -259,7 +259,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 16; ++j) r[j] = 0u;
       }
-      if (n < N) {
+      if (act != nullptr) {
+        // Fused SwiGLU (tensor.rs:167-189): weight rows are interleaved, lane 2i holds gate_f and
+        // lane 2i + 1 holds up_f of the same f for these 16 tokens. Each lane of a pair trades
+        // half of its values with the other and finishes one token of every token pair.
+        const uint32_t odd = lane & 1u;
+        const uint32_t f = n >> 1, F = N >> 1;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const uint32_t send = odd ? r[2 * jj] : r[2 * jj + 1];
+          const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
+          const float g = __uint_as_float(odd ? recv : r[2 * jj]);
+          const float u = __uint_as_float(odd ? r[2 * jj + 1] : recv);
+          const uint32_t tok = t0 + c + 2 * jj + odd;
+          if (tok < M && n < N) act[(size_t)tok * F + f] = __float2bfloat16_rn(__fmul_rn(g / (1.0f + __expf(-g)), u));
+        }
+      } else if (n < N) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const uint32_t tok = t0 + c + j;
@@ -340,7 +355,7 @@ int cached_map(const void *base, uint64_t rows, uint64_t k, uint64_t ld, uint32_
 }
 
 template <int TOKN, int WST, int XST>
-int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
+int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial, bf16 *act,
               uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, PrefetchHint next, cudaStream_t stream) {
   using Cfg = TcConfig<TOKN, WST, XST>;
   static_assert(Cfg::kSmemBytes <= 232448, "ring exceeds the shared memory of an SM");
@@ -357,7 +372,7 @@ int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *p
   ORION_TRY(cached_map(x, rows, k, ldx, TOKN, &mx));
   dim3 grid((n + kTileN - 1) / kTileN, (rows + TOKN - 1) / TOKN, splits);
   ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, WST, XST>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
-                                         *mw, *mx, partial, rows, n, k, splits, next));
+                                         *mw, *mx, partial, act, rows, n, k, splits, next));
   count_launch();
   ORION_CUDA_CHECK("gemm_tc", cudaGetLastError());
   return ORION_OK;
@@ -384,23 +399,25 @@ bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint
 
 int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
                    uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream,
-                   PrefetchHint next) {
+                   PrefetchHint next, bf16 *act) {
   const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
+  if (act != nullptr && (splits != 1 || n % 2 != 0))
+    return set_error(ORION_ERR_INTERNAL, "the fused SwiGLU epilogue needs one k split and an even row count");
   if (splits < 1 || splits > nkb)
     return set_error(ORION_ERR_INTERNAL, "gemm split count %u outside 1..%u", splits, nkb);
   const bool deep = g_small_stages >= 5;
   switch (token_tile(rows)) {
     case 16:
-      return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream)
-                  : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream);
+      return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream)
+                  : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream);
     case 32:
-      return deep ? launch_tc<32, 6, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream)
-                  : launch_tc<32, 5, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream);
+      return deep ? launch_tc<32, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream)
+                  : launch_tc<32, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream);
     case 64:
-      return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream)
-                  : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream);
-    case 128: return launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream);
-    default: return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, rows, n, k, splits, next, stream);
+      return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream)
+                  : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream);
+    case 128: return launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream);
+    default: return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream);
   }
 }
 
@@ -474,6 +491,13 @@ size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t
     if (need > best) best = need;
   }
   return best;
+}
+
+int launch_gemm_swiglu(const bf16 *x, uint32_t ldx, const bf16 *w_interleaved, uint32_t ldw, bf16 *act, uint32_t rows,
+                       uint32_t ffn, uint32_t k, cudaStream_t stream, PrefetchHint next) {
+  if (!gemm_tc_supported(rows, 2 * ffn, k, ldx, ldw, x, w_interleaved))
+    return set_error(ORION_ERR_INTERNAL, "tensor-core GEMM planned for an unaligned operand");
+  return launch_gemm_tc(x, ldx, w_interleaved, ldw, nullptr, rows, 2 * ffn, k, 1, stream, next, act);
 }
 
 template <>

@@ -72,11 +72,14 @@ template <typename T>
 int launch_rope_rows(T *x, const uint32_t *positions, const float *rope_cos, const float *rope_sin,
                      uint32_t rows, uint32_t heads, uint32_t head_dim, cudaStream_t stream);
 
-// act[r][f] = silu(g) * u with g = sum_s partial[s][r][f], u = sum_s partial[s][r][ffn + f].
-// (tensor.rs:167-189)
+// act[r][f] = silu(g) * u with g = sum_s partial[s][r][f], u = sum_s partial[s][r][ffn + f];
+// `interleaved`: gate f and up f sit in columns 2f and 2f + 1 instead. (tensor.rs:167-189)
 template <typename T>
 int launch_swiglu(const float *partial, uint32_t splits, size_t split_stride, T *act, uint32_t rows,
-                  uint32_t ffn, cudaStream_t stream);
+                  uint32_t ffn, cudaStream_t stream, bool interleaved = false);
+// dst[r * dst_stride + c] = src[r * cols + c]
+template <typename T>
+int launch_copy_rows_strided(const T *src, T *dst, size_t rows, size_t cols, size_t dst_stride, cudaStream_t stream);
 
 // out[r][n] = sum_s partial[s][r][n] + bias[n]  (finishes tensor::linear, tensor.rs:126).
 int launch_finish_linear(const float *partial, uint32_t splits, size_t split_stride,
@@ -219,7 +222,12 @@ bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint
                        const void *x, const void *w);
 int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
                    uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream,
-                   PrefetchHint next = {});
+                   PrefetchHint next = {}, bf16 *act = nullptr);
+// Gate/up projection with SwiGLU in the epilogue: `w_interleaved` is [2 * ffn][k] with gate row f
+// at 2f and up row f at 2f + 1; writes act[r][f] = silu(x.gate_f) * (x.up_f) and no partials.
+// One k split only (gemm_plan(...).splits == 1 and .tensor_core).
+int launch_gemm_swiglu(const bf16 *x, uint32_t ldx, const bf16 *w_interleaved, uint32_t ldw, bf16 *act, uint32_t rows,
+                       uint32_t ffn, uint32_t k, cudaStream_t stream, PrefetchHint next = {});
 // Device error word set by kernels whose bounded waits ran out (0 = none).
 int gemm_tc_poll_error(uint32_t *code);
 

@@ -46,6 +46,8 @@ int compute_layout(uint32_t heads, uint32_t kv_heads, uint32_t ffn, uint32_t ran
 // Off by default: measured at batch 64 on the Llama-3-8B shape, 16..96 MiB of prefetch per
 // hand-over changed the step time by less than the run-to-run noise (5.11-5.20 vs 5.14 ms).
 size_t g_prefetch_budget = 0;
+// Tuning A/B: ORION_FUSE_SWIGLU=0 keeps the separate SwiGLU kernel after the gate/up projection.
+bool g_fuse_swiglu = std::getenv("ORION_FUSE_SWIGLU") ? std::atoi(std::getenv("ORION_FUSE_SWIGLU")) != 0 : true;
 void model_set_prefetch_budget(size_t bytes) { g_prefetch_budget = bytes; }
 
 namespace {
@@ -107,6 +109,9 @@ class Model final : public ModelBase {
   const OrionModelDesc &desc() const override { return d_; }
 
  private:
+  // bf16 build: gate and up rows alternate in w_gu so that the GEMM epilogue can apply SwiGLU.
+  static constexpr bool kInterleaveGateUp = sizeof(T) == 2;
+  T *gu_stage_ = nullptr;  // upload staging for one gate or up matrix
   struct Layer {
     T *w_qkv = nullptr, *w_o = nullptr, *w_gu = nullptr, *w_down = nullptr;
     float *b_qkv = nullptr, *in_norm = nullptr, *post_norm = nullptr;
@@ -491,15 +496,17 @@ int Model<T>::load_tensor(const char *name, int dtype, const uint64_t *shape, in
       L.got |= kGotO;
       return upload_slice(L.w_o, nullptr, data, dtype, C, 0, H, q0, q1);
     }
-    if (!strcmp(rest, "mlp.gate_proj.weight")) {
+    const bool is_gate = !strcmp(rest, "mlp.gate_proj.weight");
+    if (is_gate || !strcmp(rest, "mlp.up_proj.weight")) {
       ORION_TRY(expect(F, H));
-      L.got |= kGotGate;
-      return upload_slice(L.w_gu, nullptr, data, dtype, C, f0, f1, 0, H);
-    }
-    if (!strcmp(rest, "mlp.up_proj.weight")) {
-      ORION_TRY(expect(F, H));
-      L.got |= kGotUp;
-      return upload_slice(L.w_gu + (size_t)lf_ * H, nullptr, data, dtype, C, f0, f1, 0, H);
+      L.got |= is_gate ? kGotGate : kGotUp;
+      if (!kInterleaveGateUp) return upload_slice(L.w_gu + (is_gate ? 0 : (size_t)lf_ * H), nullptr, data, dtype, C, f0, f1, 0, H);
+      // gate row f -> row 2f, up row f -> row 2f + 1 (the GEMM epilogue pairs neighbouring rows)
+      if (!gu_stage_) ORION_TRY(alloc(&gu_stage_, (size_t)lf_ * H));
+      ORION_TRY(upload_slice(gu_stage_, nullptr, data, dtype, C, f0, f1, 0, H));
+      ORION_TRY(launch_copy_rows_strided<T>(gu_stage_, L.w_gu + (is_gate ? 0 : H), lf_, H, 2 * (size_t)H, stream_));
+      ORION_CUDA_CHECK("upload tensor", cudaStreamSynchronize(stream_));
+      return ORION_OK;
     }
     if (!strcmp(rest, "mlp.down_proj.weight")) {
       ORION_TRY(expect(H, F));
@@ -673,9 +680,20 @@ int Model<T>::run_step(bool want_argmax) {
     const int handover_cat = nccl_ ? kProfCollective : kProfElementwise;
     ORION_TRY(timed(handover_cat, [&] { return handover(p.splits, L.post_norm, normed_, nullptr, Tn); }));
     p = gemm_plan(kBf16, Tn, 2 * lf_, H, H, H);
-    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_gu, H, partial_, Tn, 2 * lf_, H, p, stream_,
-                                                              hint(L.w_down, (size_t)H * lf_)); }));
-    ORION_TRY(timed(kProfElementwise, [&] { return launch_swiglu<T>(partial_, p.splits, (size_t)Tn * 2 * lf_, act_, Tn, lf_, stream_); }));
+    bool fused_swiglu = false;
+    if constexpr (kBf16) {
+      if (p.tensor_core && p.splits == 1 && g_fuse_swiglu) {  // SwiGLU in the GEMM epilogue: no partials, no extra launch
+        fused_swiglu = true;
+        ORION_TRY(timed(kProfGemm, [&] { return launch_gemm_swiglu(normed_, H, L.w_gu, H, act_, Tn, lf_, H, stream_,
+                                                                    hint(L.w_down, (size_t)H * lf_)); }));
+      }
+    }
+    if (!fused_swiglu) {
+      ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_gu, H, partial_, Tn, 2 * lf_, H, p, stream_,
+                                                                hint(L.w_down, (size_t)H * lf_)); }));
+      ORION_TRY(timed(kProfElementwise, [&] { return launch_swiglu<T>(partial_, p.splits, (size_t)Tn * 2 * lf_, act_, Tn, lf_, stream_,
+                                                                       kInterleaveGateUp); }));
+    }
     p = gemm_plan(kBf16, Tn, H, lf_, lf_, lf_);
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(act_, lf_, L.w_down, lf_, partial_, Tn, H, lf_, p, stream_,
                                                               l + 1 < d.num_layers ? hint(layers_[l + 1].w_qkv, (size_t)nqkv * H)
