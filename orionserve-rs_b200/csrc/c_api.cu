@@ -79,7 +79,7 @@ int op_linear(const float *x, uint64_t rows, uint64_t k, const float *w, uint64_
   ORION_TRY(part.alloc((size_t)p.splits * rows * n));
   ORION_TRY(res.alloc(rows * n));
   ORION_TRY(launch_gemm<T>(xt.p, (uint32_t)k, wt.p, (uint32_t)k, part.p, (uint32_t)rows, (uint32_t)n, (uint32_t)k, p, 0));
-  ORION_TRY(launch_finish_linear(part.p, p.splits, rows * n, bias ? bf_.p : nullptr, res.p, (uint32_t)rows, (uint32_t)n, 0));
+  ORION_TRY(launch_finish_linear(part.p, p.out_slabs, rows * n, bias ? bf_.p : nullptr, res.p, (uint32_t)rows, (uint32_t)n, 0));
   ORION_CUDA_CHECK("linear", cudaMemcpy(out, res.p, rows * n * sizeof(float), cudaMemcpyDeviceToHost));
   uint32_t code = 0;
   if (kBf16) {

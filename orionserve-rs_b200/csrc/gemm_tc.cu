@@ -106,6 +106,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
 }
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in cluster member `rank`.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -136,7 +153,7 @@ template <int TOKN, int WST, int XST>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                float *__restrict__ partial, bf16 *__restrict__ act, uint32_t M, uint32_t N, uint32_t K,
-               uint32_t splits, PrefetchHint next) {
+               uint32_t splits, uint32_t cluster_reduce, PrefetchHint next) {
   using Cfg = TcConfig<TOKN, WST, XST>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
@@ -248,6 +265,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     pdl_wait();  // the partial buffer may still be read by the kernel before the producer of x
     const uint32_t n = n0 + lq * 32 + lane;
     float *dst = partial + (size_t)split * M * N;
+    // Split-K inside a cluster: the tile goes to shared memory as stage[token][128 weight rows]
+    // (the rings are idle: every load has landed and every MMA has read its operands).
+    float *stage = reinterpret_cast<float *>(smem);
 #pragma unroll 1
     for (int c = 0; c < TOKN; c += 16) {
       if (t0 + c >= M) break;  // warp-uniform
@@ -259,7 +279,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 16; ++j) r[j] = 0u;
       }
-      if (act != nullptr) {
+      if (cluster_reduce) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) stage[(c + j) * kTileN + lq * 32 + lane] = __uint_as_float(r[j]);
+      } else if (act != nullptr) {
         // Fused SwiGLU (tensor.rs:167-189): weight rows are interleaved, lane 2i holds gate_f and
         // lane 2i + 1 holds up_f of the same f for these 16 tokens. Each lane of a pair trades
         // half of its values with the other and finishes one token of every token pair.
@@ -282,6 +305,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
       }
     }
+  }
+  if (cluster_reduce) {
+    // The `splits` CTAs of one tile form a cluster (1, 1, splits). Every CTA sums a share of the
+    // tile's tokens over all members' staged tiles (distributed shared memory, member order, so
+    // the result is the same as summing slabs in order) and writes slab 0 only.
+    __syncthreads();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (warp >= 4) {
+      const uint32_t row = (warp & 3) * 32 + lane, n = n0 + row;
+      const uint32_t valid = (M - t0) < (uint32_t)TOKN ? (M - t0) : (uint32_t)TOKN;
+      const uint32_t tb = split * valid / splits, te = (split + 1) * valid / splits;
+      const uint32_t base = smem_u32(smem) + row * 4;
+#pragma unroll 2
+      for (uint32_t tok = tb; tok < te; ++tok) {
+        float x[8];
+#pragma unroll
+        for (uint32_t s = 0; s < 8; ++s) x[s] = s < splits ? ld_dsmem_f32(mapa_u32(base + tok * (kTileN * 4), s)) : 0.f;
+        float acc = 0.f;
+#pragma unroll
+        for (uint32_t s = 0; s < 8; ++s)
+          if (s < splits) acc += x[s];
+        if (n < N) partial[(size_t)(t0 + tok) * N + n] = acc;
+      }
+    }
+    cluster_arrive_release();  // nobody leaves while a peer may still read its staged tile
+    cluster_wait_acquire();
   }
   if (threadIdx.x == 128) gtrace(tslot, 6);
   if (!ok) atomicOr(&g_gemm_error, 1u);
@@ -356,7 +406,8 @@ int cached_map(const void *base, uint64_t rows, uint64_t k, uint64_t ld, uint32_
 
 template <int TOKN, int WST, int XST>
 int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial, bf16 *act,
-              uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, PrefetchHint next, cudaStream_t stream) {
+              uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, bool cluster_reduce, PrefetchHint next,
+              cudaStream_t stream) {
   using Cfg = TcConfig<TOKN, WST, XST>;
   static_assert(Cfg::kSmemBytes <= 232448, "ring exceeds the shared memory of an SM");
   static bool attr_set = false;
@@ -371,8 +422,13 @@ int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *p
   ORION_TRY(cached_map(w, n, k, ldw, kTileN, &mw));
   ORION_TRY(cached_map(x, rows, k, ldx, TOKN, &mx));
   dim3 grid((n + kTileN - 1) / kTileN, (rows + TOKN - 1) / TOKN, splits);
-  ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, WST, XST>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
-                                         *mw, *mx, partial, act, rows, n, k, splits, next));
+  if (cluster_reduce)
+    ORION_CUDA_CHECK("gemm_tc", launch_pdl_cluster(gemm_tc_kernel<TOKN, WST, XST>, grid, dim3(kThreads), dim3(1, 1, splits),
+                                                   Cfg::kSmemBytes, stream, *mw, *mx, partial, act, rows, n, k, splits,
+                                                   1u, next));
+  else
+    ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, WST, XST>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
+                                           *mw, *mx, partial, act, rows, n, k, splits, 0u, next));
   count_launch();
   ORION_CUDA_CHECK("gemm_tc", cudaGetLastError());
   return ORION_OK;
@@ -399,8 +455,10 @@ bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint
 
 int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
                    uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream,
-                   PrefetchHint next, bf16 *act) {
+                   PrefetchHint next, bf16 *act, bool cluster_reduce) {
   const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
+  if (cluster_reduce && (splits < 2 || splits > 8 || act != nullptr))
+    return set_error(ORION_ERR_INTERNAL, "cluster split-K needs 2..8 splits and f32 output");
   if (act != nullptr && (splits != 1 || n % 2 != 0))
     return set_error(ORION_ERR_INTERNAL, "the fused SwiGLU epilogue needs one k split and an even row count");
   if (splits < 1 || splits > nkb)
@@ -408,16 +466,16 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
   const bool deep = g_small_stages >= 5;
   switch (token_tile(rows)) {
     case 16:
-      return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream)
-                  : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream);
+      return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream)
+                  : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
     case 32:
-      return deep ? launch_tc<32, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream)
-                  : launch_tc<32, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream);
+      return deep ? launch_tc<32, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream)
+                  : launch_tc<32, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
     case 64:
-      return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream)
-                  : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream);
-    case 128: return launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream);
-    default: return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, next, stream);
+      return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream)
+                  : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
+    case 128: return launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
+    default: return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
   }
 }
 
@@ -456,6 +514,12 @@ int gemm_tc_poll_error(uint32_t *code) {
 
 namespace {
 uint32_t g_target_ctas = 296;  // two CTAs fit on each of the 148 SMs
+// Split-K reduction inside a thread-block cluster (distributed shared memory) instead of one f32
+// slab per split summed by the consumer. Off by default: measured on the headline step it removes
+// 8/9 of the slab traffic but costs more than it saves (5.27 vs 5.01 ms per step): clusters of 8
+// CTAs of 105 KiB must be co-scheduled, which delays the dependent-launch overlap, and each GEMM
+// gains two cluster barriers. ORION_CLUSTER_SPLITK=1 turns it on (tests cover both).
+bool g_cluster_splitk = std::getenv("ORION_CLUSTER_SPLITK") ? std::atoi(std::getenv("ORION_CLUSTER_SPLITK")) != 0 : false;
 }
 
 void gemm_set_target_ctas(uint32_t v) { g_target_ctas = v ? v : 296; }
@@ -463,7 +527,7 @@ void gemm_set_small_stages(int stages) { g_small_stages = stages >= 5 ? 5 : 4; }
 
 GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx,
                    uint32_t ldw) {
-  GemmPlan p{1, false};
+  GemmPlan p{1, false, false, 1};
   if (!is_bf16) return p;
   // alignment of the pointers is checked at launch; shapes decide the plan
   if (!(rows > 0 && n > 0 && k >= (uint32_t)kSlabK && k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 &&
@@ -477,7 +541,10 @@ GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t
   const uint32_t cap = nkb / 4 ? nkb / 4 : 1;  // at least four k slabs per split
   if (s > cap) s = cap;
   if (s > 16) s = 16;
+  if (g_cluster_splitk && s > 8) s = 8;  // portable cluster size
   p.splits = s < 1 ? 1 : s;
+  p.cluster_reduce = g_cluster_splitk && p.splits > 1;
+  p.out_slabs = p.cluster_reduce ? 1 : p.splits;
   return p;
 }
 
@@ -497,7 +564,7 @@ int launch_gemm_swiglu(const bf16 *x, uint32_t ldx, const bf16 *w_interleaved, u
                        uint32_t ffn, uint32_t k, cudaStream_t stream, PrefetchHint next) {
   if (!gemm_tc_supported(rows, 2 * ffn, k, ldx, ldw, x, w_interleaved))
     return set_error(ORION_ERR_INTERNAL, "tensor-core GEMM planned for an unaligned operand");
-  return launch_gemm_tc(x, ldx, w_interleaved, ldw, nullptr, rows, 2 * ffn, k, 1, stream, next, act);
+  return launch_gemm_tc(x, ldx, w_interleaved, ldw, nullptr, rows, 2 * ffn, k, 1, stream, next, act, false);
 }
 
 template <>
@@ -513,7 +580,7 @@ int launch_gemm<bf16>(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, 
   if (plan.tensor_core) {
     if (!gemm_tc_supported(rows, n, k, ldx, ldw, x, w))
       return set_error(ORION_ERR_INTERNAL, "tensor-core GEMM planned for an unaligned operand");
-    return launch_gemm_tc(x, ldx, w, ldw, partial, rows, n, k, plan.splits, stream, next);
+    return launch_gemm_tc(x, ldx, w, ldw, partial, rows, n, k, plan.splits, stream, next, nullptr, plan.cluster_reduce);
   }
   return launch_gemm_simt<bf16>(x, ldx, w, ldw, partial, rows, n, k, stream);
 }

@@ -648,7 +648,7 @@ int Model<T>::run_step(bool want_argmax) {
     const Layer &L = layers_[l];
     GemmPlan p = gemm_plan(kBf16, Tn, nqkv, H, H, H);
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_qkv, H, partial_, Tn, nqkv, H, p, stream_); }));
-    ORION_TRY(timed(kProfElementwise, [&] { return launch_rope_kvwrite<T>(partial_, p.splits, (size_t)Tn * nqkv, L.b_qkv, positions, slot_block,
+    ORION_TRY(timed(kProfElementwise, [&] { return launch_rope_kvwrite<T>(partial_, p.out_slabs, (size_t)Tn * nqkv, L.b_qkv, positions, slot_block,
                                      slot_slot, rope_cos_, rope_sin_, qbuf_, arena_, kv_, l, Tn, lq_, stream_); }));
     if (tuned_decode) {
       if constexpr (kBf16) {
@@ -678,7 +678,7 @@ int Model<T>::run_step(bool want_argmax) {
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(attn_, qd, L.w_o, qd, partial_, Tn, H, qd, p, stream_,
                                                               hint(L.w_gu, (size_t)2 * lf_ * H)); }));
     const int handover_cat = nccl_ ? kProfCollective : kProfElementwise;
-    ORION_TRY(timed(handover_cat, [&] { return handover(p.splits, L.post_norm, normed_, nullptr, Tn); }));
+    ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, L.post_norm, normed_, nullptr, Tn); }));
     p = gemm_plan(kBf16, Tn, 2 * lf_, H, H, H);
     bool fused_swiglu = false;
     if constexpr (kBf16) {
@@ -691,7 +691,7 @@ int Model<T>::run_step(bool want_argmax) {
     if (!fused_swiglu) {
       ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_gu, H, partial_, Tn, 2 * lf_, H, p, stream_,
                                                                 hint(L.w_down, (size_t)H * lf_)); }));
-      ORION_TRY(timed(kProfElementwise, [&] { return launch_swiglu<T>(partial_, p.splits, (size_t)Tn * 2 * lf_, act_, Tn, lf_, stream_,
+      ORION_TRY(timed(kProfElementwise, [&] { return launch_swiglu<T>(partial_, p.out_slabs, (size_t)Tn * 2 * lf_, act_, Tn, lf_, stream_,
                                                                        kInterleaveGateUp); }));
     }
     p = gemm_plan(kBf16, Tn, H, lf_, lf_, lf_);
@@ -699,19 +699,19 @@ int Model<T>::run_step(bool want_argmax) {
                                                               l + 1 < d.num_layers ? hint(layers_[l + 1].w_qkv, (size_t)nqkv * H)
                                                                                    : hint(lm_head_, (size_t)d.vocab_size * H)); }));
     if (l + 1 < d.num_layers) {
-      ORION_TRY(timed(handover_cat, [&] { return handover(p.splits, layers_[l + 1].in_norm, normed_, nullptr, Tn); }));
+      ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, layers_[l + 1].in_norm, normed_, nullptr, Tn); }));
     } else if (!meta_.zero_count) {
       // Final norm over the last row of every sequence (transformer.rs:401-428;
       // the norm is row-wise, so gathering first gives the same rows).
-      ORION_TRY(timed(handover_cat, [&] { return handover(p.splits, final_norm_, tail_, last_rows, S); }));
+      ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, final_norm_, tail_, last_rows, S); }));
     } else if (nccl_) {
       // keep the ranks in lock step even though this step ends in an error
-      ORION_TRY(timed(handover_cat, [&] { return handover(p.splits, final_norm_, normed_, nullptr, Tn); }));
+      ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, final_norm_, normed_, nullptr, Tn); }));
     }
   }
   if (meta_.zero_count) return ORION_OK;
   GemmPlan hp = gemm_plan(kBf16, S, d.vocab_size, H, H, H);
-  hp.splits = 1;  // logits are written in place, row-major [S][V]
+  hp.splits = hp.out_slabs = 1, hp.cluster_reduce = false;  // logits are written in place, row-major [S][V]
   ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(tail_, H, lm_head_, H, logits_, S, d.vocab_size, H, hp, stream_); }));
   if (want_argmax) ORION_TRY(timed(kProfElementwise, [&] { return launch_argmax(logits_, S, d.vocab_size, argmax_, stream_); }));
   return ORION_OK;

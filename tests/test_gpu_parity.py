@@ -511,3 +511,19 @@ def test_qwen2_shape_with_qkv_bias(pkg, backend, oracle):
         b = pkg.ForwardBatch(toks, np.arange(40), [1], [40], [40], [[9, 2, 7]])
         exp = ref.forward(oracle.Batch(toks, np.arange(40), [40], [40], [[9, 2, 7]]))
         assert check(dev.forward(b).logits, exp)
+
+
+def test_cluster_split_k_variant_matches_the_oracle(pkg, backend):
+    """The GEMM's split-K reduction inside a thread-block cluster is off by default (measured
+    slower); the switch is read when the library loads, so the parity cases that reach split-K
+    GEMMs run once more in a child process with it on."""
+    import os
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+    env = dict(os.environ, ORION_CLUSTER_SPLITK="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_parity.py"), "-q", "-x",
+                        "-m", "gpu", "-k", "linear_bf16_tensor_core or config1_greedy or chunked_prefill"],
+                       cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:]
