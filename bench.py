@@ -27,6 +27,9 @@ if ROOT not in sys.path:
 LLAMA3_8B = dict(hidden_size=4096, num_layers=32, num_attention_heads=32, num_kv_heads=8, head_dim=128,
                  vocab_size=128256, ffn_dim=14336, max_position_embeddings=8192, rope_theta=500000.0,
                  rms_norm_eps=1e-5)
+QWEN2_7B = dict(hidden_size=3584, num_layers=28, num_attention_heads=28, num_kv_heads=4, head_dim=128,
+                vocab_size=152064, ffn_dim=18944, max_position_embeddings=8192, rope_theta=1000000.0,
+                rms_norm_eps=1e-6, has_qkv_bias=True)
 BATCH, CONTEXT, BLOCK = 64, 1024, 16
 WORKLOAD = "llama3_8b_decode_batch64_ctx1024_bf16"
 METRIC = "decode tokens/s at batch 64 (Llama-3-8B shape)"
@@ -242,11 +245,23 @@ def run_serving(args):
     pkg = ge.load_package()
     E = pkg.engine
     backend = pkg.CudaBackend(0)
-    m = dict(LLAMA3_8B, num_layers=args.layers)
-    meta = pkg.ModelMetadata(architecture="llama", name="llama3-8b-shape", dtype=pkg.DType.BF16, **m)
     rng = np.random.default_rng(11)
-    prompts = [rng.integers(0, m["vocab_size"], int(rng.integers(128, 2049))).astype(np.uint32) for _ in range(args.requests)]
-    outputs = [int(rng.integers(64, 513)) for _ in range(args.requests)]
+    if args.workload == "prefix":
+        # the fourth configuration: Qwen2-7B shape, one shared 1024-token prefix + unique 64-256-token
+        # suffixes, 128 output tokens each (blocks are shared; compute is skipped only with the flag)
+        m = dict(QWEN2_7B, num_layers=min(args.layers, QWEN2_7B["num_layers"]))
+        meta = pkg.ModelMetadata(architecture="qwen2", name="qwen2-7b-shape", dtype=pkg.DType.BF16, **m)
+        shared = rng.integers(0, m["vocab_size"], 1024)
+        prompts = [np.concatenate([shared, rng.integers(0, m["vocab_size"], int(rng.integers(64, 257)))]).astype(np.uint32)
+                   for _ in range(args.requests)]
+        outputs = [128] * args.requests
+        name, shape = "qwen2_7b_shared_prefix_bf16", "1024 shared + U[64,256]"
+    else:
+        m = dict(LLAMA3_8B, num_layers=args.layers)
+        meta = pkg.ModelMetadata(architecture="llama", name="llama3-8b-shape", dtype=pkg.DType.BF16, **m)
+        prompts = [rng.integers(0, m["vocab_size"], int(rng.integers(128, 2049))).astype(np.uint32) for _ in range(args.requests)]
+        outputs = [int(rng.integers(64, 513)) for _ in range(args.requests)]
+        name, shape = "llama3_8b_continuous_batching_bf16", "U[128,2048]"
     # every sequence fully resident at once, plus the slot the reference's decode position skips
     num_blocks = sum((len(p) + o + 2) // BLOCK + 1 for p, o in zip(prompts, outputs)) + 64
     budget = 512
@@ -254,7 +269,8 @@ def run_serving(args):
                                      max_batch_tokens=budget, max_batch_sequences=min(256, args.requests))
     model.init_random(seed=1, std=0.02)
     cfg = E.SchedulerConfig(max_num_seqs=min(256, args.requests), max_num_batched_tokens=budget, max_model_len=4096,
-                            enable_chunked_prefill=True, max_waiting_requests=4096, request_timeout_secs=None)
+                            enable_chunked_prefill=True, max_waiting_requests=4096, request_timeout_secs=None,
+                            skip_cached_prefix=args.skip_cached_prefix)
     eng = E.Engine(model, cfg, num_blocks, BLOCK, True, [])
     for p, o in zip(prompts, outputs):
         eng.submit(p, E.SamplingParams(temperature=0.0, max_tokens=o))
@@ -275,11 +291,14 @@ def run_serving(args):
     stats = eng.scheduler().stats()
     out_tokens, prompt_tokens = sum(outputs), int(sum(len(p) for p in prompts))
     print(json.dumps({
-        "metric": "continuous-batching output tokens/s (Llama-3-8B shape)", "value": out_tokens / dt, "unit": "tokens/s",
+        "metric": f"continuous-batching output tokens/s ({meta.name})", "value": out_tokens / dt, "unit": "tokens/s",
         "n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "llama3_8b_continuous_batching_bf16", "requests": args.requests, "prompts": "U[128,2048]",
-                   "outputs": "U[64,512]", "step_token_budget": budget, "block_size": BLOCK, "layers": args.layers,
-                   "num_blocks": num_blocks, "sampling": "greedy on the device"},
+        "config": {"workload": name, "requests": args.requests, "prompts": shape,
+                   "outputs": "128" if args.workload == "prefix" else "U[64,512]", "step_token_budget": budget,
+                   "block_size": BLOCK, "layers": m["num_layers"], "num_blocks": num_blocks,
+                   "sampling": "greedy on the device", "skip_cached_prefix": bool(args.skip_cached_prefix)},
+        "prefix_cache_hits": eng.scheduler().cache().stats()["prefix_cache_hits"],
+        "skipped_prefill_tokens": stats["total_skipped_prefill_tokens"],
         "seconds": dt, "engine_steps": steps, "refused_steps": failed, "prompt_tokens": prompt_tokens,
         "output_tokens": out_tokens, "total_tokens_per_s": (prompt_tokens + out_tokens) / dt,
         "preemptions": stats["total_preempted"], "mean_batch_tokens": stats["total_batched_tokens"] / max(1, stats["total_steps"]),
@@ -288,7 +307,7 @@ def run_serving(args):
 
 
 def run_ours(args):
-    if args.workload == "serving":
+    if args.workload in ("serving", "prefix"):
         return run_serving(args)
     import __graft_entry__ as ge
 
@@ -444,8 +463,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=("decode", "serving"), default="decode",
-                    help="decode = the headline step (default); serving = continuous batching through the engine loop")
+    ap.add_argument("--workload", choices=("decode", "serving", "prefix"), default="decode",
+                    help="decode = the headline step (default); serving = continuous batching through the engine "
+                         "loop; prefix = shared-prefix requests on the Qwen2-7B shape through the engine loop")
+    ap.add_argument("--skip-cached-prefix", action="store_true",
+                    help="engine workloads: start prefill after the tokens adopted from the prefix cache "
+                         "(an extension; the reference shares the blocks but recomputes them)")
     ap.add_argument("--requests", type=int, default=256, help="requests of the serving workload")
     ap.add_argument("--layers", type=int, default=32,
                     help="layers of the Llama-3-8B shape to build; fewer than 32 gives a small case with the "

@@ -36,12 +36,16 @@ typedef struct OrionCacheStats {
 
 /* SchedulerConfig (crates/orion-core/src/config.rs:107-156). max_model_len and
  * request_timeout_secs: 0 = None. Defaults of the reference: 256, 8192, None, chunked, 1024,
- * Some(300), decode first. */
+ * Some(300), decode first.
+ * skip_cached_prefix has no reference counterpart (the reference shares cached blocks but
+ * recomputes them, manager.rs:449-451): non-zero starts a new sequence's prefill after the tokens
+ * whose blocks came from the prefix cache. 0 = the reference's behaviour. */
 typedef struct OrionSchedulerConfig {
   uint64_t max_num_seqs, max_num_batched_tokens, max_model_len;
   uint32_t enable_chunked_prefill;
   uint64_t max_waiting_requests, request_timeout_secs;
   uint32_t prioritize_decode;
+  uint32_t skip_cached_prefix;
 } OrionSchedulerConfig;
 
 /* SamplingParams (crates/orion-core/src/sampling.rs:25-70), the fields the driver reads. */
@@ -62,6 +66,7 @@ typedef struct OrionScheduledSequence {
 typedef struct OrionSchedulerStats {
   uint64_t total_steps, total_admitted, total_finished, total_preempted, total_rejected;
   uint64_t total_batched_tokens, total_prefill_tokens, total_decode_tokens;
+  uint64_t total_skipped_prefill_tokens; /* only with skip_cached_prefix */
 } OrionSchedulerStats;
 
 /* FinishReason (crates/orion-core/src/sequence.rs:73-87) */

@@ -318,6 +318,7 @@ class Config:  # config.rs:107-156
     enable_chunked_prefill: bool = True
     max_waiting_requests: int = 1024
     prioritize_decode: bool = True
+    skip_cached_prefix: bool = False  # not in the reference: prefill starts after the adopted cached tokens
 
 
 @dataclass(frozen=True)
@@ -334,7 +335,8 @@ class Scheduler:  # scheduler.rs:127-580
         self.waiting: deque = deque()
         self.running: List[Sequence] = []
         self.stats = dict(total_steps=0, total_admitted=0, total_finished=0, total_preempted=0, total_rejected=0,
-                          total_batched_tokens=0, total_prefill_tokens=0, total_decode_tokens=0)
+                          total_batched_tokens=0, total_prefill_tokens=0, total_decode_tokens=0,
+                          total_skipped_prefill_tokens=0)
 
     def has_work(self) -> bool:
         return bool(self.waiting) or bool(self.running)
@@ -453,11 +455,17 @@ class Scheduler:  # scheduler.rs:127-580
             seq = self.waiting.popleft()
             if first:
                 try:
-                    self.cache.allocate(seq.id, seq.prompt)
+                    _, _, cached = self.cache.allocate(seq.id, seq.prompt)
                 except OracleError:
                     seq.preempt()
                     self.waiting.appendleft(seq)
                     break
+                if self.config.skip_cached_prefix and cached > 0:
+                    skip = min(cached, prompt_len - 1)  # the last prompt token is always computed
+                    seq.advance(skip)
+                    self.stats["total_skipped_prefill_tokens"] += skip
+                    already = skip
+                    chunk = min(chunk, prompt_len - skip)
             seq.advance(chunk)
             if seq.state == WAITING:
                 seq.transition(PREFILLING)

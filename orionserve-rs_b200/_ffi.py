@@ -115,7 +115,8 @@ class OrionCacheStats(C.Structure):
 class OrionSchedulerConfig(C.Structure):
     _fields_ = [("max_num_seqs", C.c_uint64), ("max_num_batched_tokens", C.c_uint64), ("max_model_len", C.c_uint64),
                 ("enable_chunked_prefill", C.c_uint32), ("max_waiting_requests", C.c_uint64),
-                ("request_timeout_secs", C.c_uint64), ("prioritize_decode", C.c_uint32)]
+                ("request_timeout_secs", C.c_uint64), ("prioritize_decode", C.c_uint32),
+                ("skip_cached_prefix", C.c_uint32)]
 
 
 class OrionSamplingParams(C.Structure):
@@ -132,7 +133,7 @@ class OrionScheduledSequence(C.Structure):
 class OrionSchedulerStats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("total_steps", "total_admitted", "total_finished", "total_preempted",
                                           "total_rejected", "total_batched_tokens", "total_prefill_tokens",
-                                          "total_decode_tokens")]
+                                          "total_decode_tokens", "total_skipped_prefill_tokens")]
 
 
 class OrionEngineEvent(C.Structure):

@@ -192,6 +192,10 @@ struct SchedulerConfig {  // crates/orion-core/src/config.rs:107-156
   size_t max_waiting_requests = 1024;
   std::optional<uint64_t> request_timeout_secs = 300;
   bool prioritize_decode = true;
+  // Not in the reference (which plumbs AllocationOutcome.cached_tokens nowhere, manager.rs:449-451,
+  // and always prefills from position 0): when set, a new sequence starts its prefill after the
+  // tokens whose blocks it adopted from the prefix cache. Off = the reference's behaviour.
+  bool skip_cached_prefix = false;
 };
 
 struct ScheduledSequence {  // scheduler.rs:36-50
@@ -209,6 +213,7 @@ struct SchedulerOutput {  // scheduler.rs:53-61
 struct SchedulerStats {  // scheduler.rs:99-109
   uint64_t total_steps = 0, total_admitted = 0, total_finished = 0, total_preempted = 0, total_rejected = 0,
            total_batched_tokens = 0, total_prefill_tokens = 0, total_decode_tokens = 0;
+  uint64_t total_skipped_prefill_tokens = 0;  // only with skip_cached_prefix
 };
 
 class Scheduler {  // scheduler.rs:127-580

@@ -36,6 +36,7 @@ SchedulerConfig to_config(const OrionSchedulerConfig *c) {
   out.max_waiting_requests = c->max_waiting_requests;
   out.request_timeout_secs = c->request_timeout_secs ? std::optional<uint64_t>(c->request_timeout_secs) : std::nullopt;
   out.prioritize_decode = c->prioritize_decode != 0;
+  out.skip_cached_prefix = c->skip_cached_prefix != 0;
   return out;
 }
 
@@ -214,7 +215,8 @@ int orion_scheduler_stats(const OrionScheduler *s, OrionSchedulerStats *out) {
   if (!s || !out) return null_handle();
   const SchedulerStats &t = s->p->stats();
   *out = OrionSchedulerStats{t.total_steps,    t.total_admitted,       t.total_finished,       t.total_preempted,
-                             t.total_rejected, t.total_batched_tokens, t.total_prefill_tokens, t.total_decode_tokens};
+                             t.total_rejected, t.total_batched_tokens, t.total_prefill_tokens, t.total_decode_tokens,
+                             t.total_skipped_prefill_tokens};
   return ORION_OK;
 }
 int orion_scheduler_running_sequence(const OrionScheduler *s, uint64_t id, int *state, uint64_t *computed_prefix_len,

@@ -229,14 +229,25 @@ void Scheduler::schedule_prefills(SchedulerOutput &out, size_t budget, size_t &u
     Sequence seq = std::move(waiting_.front());
     waiting_.pop_front();
     const SequenceId id = seq.id();
+    size_t start_position = already;
     if (is_first_chunk) {
-      if (cache_.allocate(id, seq.prompt().data(), seq.prompt().size(), nullptr) != ORION_OK) {
+      AllocationOutcome outcome;
+      if (cache_.allocate(id, seq.prompt().data(), seq.prompt().size(), &outcome) != ORION_OK) {
         seq.preempt();
         waiting_.push_front(std::move(seq));
         break;
       }
+      if (config_.skip_cached_prefix && outcome.cached_tokens > 0) {
+        // The adopted blocks already hold the keys and values of these tokens (published only
+        // after their prefill ran). At least the last prompt token is still computed: its logits
+        // are what the first sampled token comes from.
+        const size_t skip = std::min(outcome.cached_tokens, prompt_len - 1);
+        seq.advance_prefill(skip);
+        stats_.total_skipped_prefill_tokens += skip;
+        start_position = skip;
+        chunk = std::min(chunk, prompt_len - skip);
+      }
     }
-    const size_t start_position = already;
     seq.advance_prefill(chunk);  // progress is recorded at schedule time
     if (seq.state() == SequenceState::Waiting) seq.transition_to(SequenceState::Prefilling);
     if (seq.is_prefill_complete()) seq.transition_to(SequenceState::Decoding);

@@ -61,11 +61,15 @@ class SchedulerConfig:
     max_waiting_requests: int = 1024
     request_timeout_secs: Optional[int] = 300
     prioritize_decode: bool = True
+    #: not in the reference: start a new sequence's prefill after the tokens whose blocks came from
+    #: the prefix cache (the reference shares those blocks but recomputes them)
+    skip_cached_prefix: bool = False
 
     def _c(self):
         return _ffi.OrionSchedulerConfig(self.max_num_seqs, self.max_num_batched_tokens, self.max_model_len or 0,
                                          int(self.enable_chunked_prefill), self.max_waiting_requests,
-                                         self.request_timeout_secs or 0, int(self.prioritize_decode))
+                                         self.request_timeout_secs or 0, int(self.prioritize_decode),
+                                         int(self.skip_cached_prefix))
 
 
 @dataclass(frozen=True)

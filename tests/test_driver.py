@@ -455,6 +455,25 @@ def test_an_injected_append_failure_is_handled(impl):
     assert s.num_running() + s.num_waiting() == 2
 
 
+def test_prefix_hits_do_not_skip_compute_unless_asked(impl):
+    """The reference shares cached blocks but always prefills from position 0 (scheduler.rs:397-399,
+    manager.rs:449-451). The opt-in extension starts after the adopted tokens and always computes at
+    least the last prompt token."""
+    prompt = list(range(100, 112))  # three full blocks of four
+    for skip, expect_second, expect_full in ((False, (12, 0), (12, 0)), (True, (4, 8), (1, 11))):
+        s = Sched(impl, 32, 4, True, **{**CFG, "skip_cached_prefix": skip})
+        a = s.add(prompt[:8] + [7, 7, 7, 7], 4)
+        s.schedule()
+        s.commit_prefill(a)
+        b = s.add(prompt, 4)  # shares the first two blocks with a
+        assert s.schedule()[0][-1] == (b, expect_second[0], expect_second[1], True)
+        s.commit_prefill(b)
+        c = s.add(prompt, 4)  # every block cached: only the last token is computed when skipping
+        assert s.schedule()[0][-1] == (c, expect_full[0], expect_full[1], True)
+        assert s.stats()["total_skipped_prefill_tokens"] == (8 + 11 if skip else 0)
+        assert s.cache.table(b)[0][:3] == s.cache.table(c)[0], "the prompt blocks are shared either way"
+
+
 # ---- engine.rs with the mock model ------------------------------------------------------------------
 
 def mock(favoured):

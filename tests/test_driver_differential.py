@@ -62,6 +62,11 @@ CASES = [
     (14, 4, True, dict(max_num_seqs=8, max_num_batched_tokens=20, max_model_len=256, enable_chunked_prefill=True,
                        prioritize_decode=False)),
     (200, 16, True, dict(max_num_seqs=16, max_num_batched_tokens=128, max_model_len=2048, enable_chunked_prefill=True)),
+    # the opt-in extension: prefill starts after the tokens whose blocks came from the prefix cache
+    (24, 4, True, dict(max_num_seqs=6, max_num_batched_tokens=24, max_model_len=256, enable_chunked_prefill=True,
+                       skip_cached_prefix=True)),
+    (60, 4, True, dict(max_num_seqs=8, max_num_batched_tokens=64, max_model_len=256, enable_chunked_prefill=False,
+                       skip_cached_prefix=True)),
 ]
 
 
@@ -135,3 +140,5 @@ def test_engines_agree_step_by_step(pkg, case, seed):
         assert hits > 0
     if case in (0, 1, 2):
         assert failed_steps > 0, "the reference's off-by-one decode position should fail a step now and then"
+    skipped = ref.sched.stats()["total_skipped_prefill_tokens"]
+    assert (skipped > 0) == bool(cfg.get("skip_cached_prefix")), "only the opt-in extension skips prefill compute"
