@@ -122,6 +122,13 @@ typedef struct OrionModelDesc {
 int orion_cuda_model_create(OrionBackend *backend, const OrionModelDesc *desc, OrionModel **out);
 void orion_cuda_model_destroy(OrionModel *model);
 
+/* CheckpointLoader::open + ModelWeights::load for a whole directory
+ * (crates/orion-models/src/loader.rs:112-235, transformer.rs:62-120,180-205): every
+ * `*.safetensors` file in name order (the first file wins for a duplicated tensor name),
+ * memory-mapped; each tensor the model uses goes from the mapping to the device through
+ * orion_cuda_model_load_tensor (this rank's slice only), tensors it does not use are ignored;
+ * ends with orion_cuda_model_finalize. `tensors_loaded` may be NULL. */
+int orion_cuda_model_load_checkpoint(OrionModel *model, const char *directory, uint64_t *tensors_loaded);
 /* ModelWeights::load, one tensor at a time (transformer.rs:62-120). `name` is
  * the Hugging Face tensor name (transformer.rs:12-18); `dtype` the stored type
  * (F32, F16 or BF16, widened or narrowed once at load like loader.rs:74-96);

@@ -393,6 +393,12 @@ int orion_cuda_model_forward(OrionModel *model, const uint32_t *tokens, uint64_t
                                          logits_out, logits_capacity);
 }
 
+int orion_cuda_model_load_checkpoint(OrionModel *model, const char *directory, uint64_t *tensors_loaded) {
+  clear_error();
+  if (!model) return set_error(ORION_ERR_INVALID_REQUEST, "null model handle");
+  return load_checkpoint(model->impl.get(), directory, tensors_loaded);
+}
+
 int orion_cuda_model_replay(OrionModel *model, int iterations, float *elapsed_ms) {
   clear_error();
   if (!model) return set_error(ORION_ERR_INVALID_REQUEST, "null model handle");

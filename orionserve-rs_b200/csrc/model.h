@@ -71,6 +71,9 @@ class ModelBase {
 void model_set_prefetch_budget(size_t bytes);
 
 int create_model(OrionBackend *backend, const OrionModelDesc *desc, ModelBase **out);
+// Loads every tensor the model uses from the `*.safetensors` files of a directory and finalizes
+// (CheckpointLoader, crates/orion-models/src/loader.rs:112-235).
+int load_checkpoint(ModelBase *model, const char *directory, uint64_t *tensors_loaded);
 
 }  // namespace orion
 

@@ -212,24 +212,19 @@ class CudaTransformerModel:
         """transformer.rs:180-205: config.json + one or more safetensors shards."""
         cfg = HfConfig.load(directory)
         meta = cfg.to_metadata(os.path.basename(os.path.normpath(directory)) or "model")
-        shards = sorted(f for f in os.listdir(directory) if f.endswith(".safetensors"))
-        if not shards:
-            raise ModelError(f"no .safetensors file in {directory}")
-        names = set()
-        tensors = []
-        for s in shards:
-            for name, rec in read_safetensors(os.path.join(directory, s)).items():
-                names.add(name)
-                tensors.append((name, rec))
-        if cfg.ties_embeddings() or "lm_head.weight" not in names:  # transformer.rs:108-112
+        if cfg.ties_embeddings():  # transformer.rs:108-112; an absent lm_head falls back to the embedding too
             meta.tied_lm_head = True
         m = cls(meta, num_blocks, block_size, backend, **kw)
-        for name, (dt, shape, arr) in tensors:
-            if name.endswith("rotary_emb.inv_freq"):
-                continue
-            m.load_tensor(name, arr, shape, dt)
-        m.finalize()
+        m.load_checkpoint(directory)
         return m
+
+    def load_checkpoint(self, directory: str) -> int:
+        """Every ``*.safetensors`` file of ``directory`` straight from its memory mapping to the
+        device (this rank's slices only), then ``finalize``; returns the number of tensors used.
+        The files are opened and parsed inside the library (``CheckpointLoader``, loader.rs:112-235)."""
+        n = C.c_uint64()
+        check(_ffi.lib().orion_cuda_model_load_checkpoint(self._h, os.fsencode(directory), C.byref(n)))
+        return int(n.value)
 
     def load_tensor(self, name: str, data: np.ndarray, shape=None, dtype: Optional[DType] = None) -> None:
         if dtype is None:
