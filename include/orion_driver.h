@@ -39,13 +39,17 @@ typedef struct OrionCacheStats {
  * Some(300), decode first.
  * skip_cached_prefix has no reference counterpart (the reference shares cached blocks but
  * recomputes them, manager.rs:449-451): non-zero starts a new sequence's prefill after the tokens
- * whose blocks came from the prefix cache. 0 = the reference's behaviour. */
+ * whose blocks came from the prefix cache. 0 = the reference's behaviour.
+ * logical_decode_positions has none either: non-zero feeds a decode token at position
+ * total_len - 1, its logical place, instead of the reference's total_len (scheduler.rs:283), so
+ * that no cache slot is skipped and no step is refused. 0 = the reference's behaviour. */
 typedef struct OrionSchedulerConfig {
   uint64_t max_num_seqs, max_num_batched_tokens, max_model_len;
   uint32_t enable_chunked_prefill;
   uint64_t max_waiting_requests, request_timeout_secs;
   uint32_t prioritize_decode;
   uint32_t skip_cached_prefix;
+  uint32_t logical_decode_positions;
 } OrionSchedulerConfig;
 
 /* SamplingParams (crates/orion-core/src/sampling.rs:25-70), the fields the driver reads. */

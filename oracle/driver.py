@@ -319,6 +319,7 @@ class Config:  # config.rs:107-156
     max_waiting_requests: int = 1024
     prioritize_decode: bool = True
     skip_cached_prefix: bool = False  # not in the reference: prefill starts after the adopted cached tokens
+    logical_decode_positions: bool = False  # not in the reference: decode at total_len - 1 instead of total_len
 
 
 @dataclass(frozen=True)
@@ -394,7 +395,8 @@ class Scheduler:  # scheduler.rs:127-580
             return False
 
     def _decodes(self, sched, preempted, budget, used) -> None:  # scheduler.rs:267-313
-        for sid, total in [(s.id, s.total_len()) for s in self.running if s.state == DECODING]:
+        shift = 1 if self.config.logical_decode_positions else 0
+        for sid, total in [(s.id, max(0, s.total_len() - shift)) for s in self.running if s.state == DECODING]:
             if used[0] >= budget:
                 break
             if self._try_append(sid):

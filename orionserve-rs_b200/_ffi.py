@@ -117,7 +117,7 @@ class OrionSchedulerConfig(C.Structure):
     _fields_ = [("max_num_seqs", C.c_uint64), ("max_num_batched_tokens", C.c_uint64), ("max_model_len", C.c_uint64),
                 ("enable_chunked_prefill", C.c_uint32), ("max_waiting_requests", C.c_uint64),
                 ("request_timeout_secs", C.c_uint64), ("prioritize_decode", C.c_uint32),
-                ("skip_cached_prefix", C.c_uint32)]
+                ("skip_cached_prefix", C.c_uint32), ("logical_decode_positions", C.c_uint32)]
 
 
 class OrionSamplingParams(C.Structure):

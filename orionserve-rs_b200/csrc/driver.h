@@ -196,6 +196,10 @@ struct SchedulerConfig {  // crates/orion-core/src/config.rs:107-156
   // and always prefills from position 0): when set, a new sequence starts its prefill after the
   // tokens whose blocks it adopted from the prefix cache. Off = the reference's behaviour.
   bool skip_cached_prefix = false;
+  // Not in the reference either: feed a decode token at its logical position total_len - 1
+  // instead of total_len (scheduler.rs:283 counts the token that was just sampled), so no cache
+  // slot is skipped and no step is refused for a block the table does not hold yet.
+  bool logical_decode_positions = false;
 };
 
 struct ScheduledSequence {  // scheduler.rs:36-50

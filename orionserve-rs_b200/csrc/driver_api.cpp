@@ -37,6 +37,7 @@ SchedulerConfig to_config(const OrionSchedulerConfig *c) {
   out.request_timeout_secs = c->request_timeout_secs ? std::optional<uint64_t>(c->request_timeout_secs) : std::nullopt;
   out.prioritize_decode = c->prioritize_decode != 0;
   out.skip_cached_prefix = c->skip_cached_prefix != 0;
+  out.logical_decode_positions = c->logical_decode_positions != 0;
   return out;
 }
 

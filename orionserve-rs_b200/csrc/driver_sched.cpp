@@ -148,8 +148,9 @@ SchedulerOutput Scheduler::schedule() {  // scheduler.rs:239-263
 
 void Scheduler::schedule_decodes(SchedulerOutput &out, size_t budget, size_t &used) {  // scheduler.rs:267-313
   std::vector<std::pair<SequenceId, size_t>> candidates;  // collected first: the loop below mutates `running`
+  const size_t shift = config_.logical_decode_positions ? 1 : 0;
   for (const Sequence &s : running_)
-    if (s.state() == SequenceState::Decoding) candidates.emplace_back(s.id(), s.total_len());
+    if (s.state() == SequenceState::Decoding) candidates.emplace_back(s.id(), s.total_len() - std::min(shift, s.total_len()));
   for (const auto &[id, total_len] : candidates) {
     if (used >= budget) break;
     // Room for the token about to be generated. Note the position: total_len counts the token

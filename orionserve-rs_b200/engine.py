@@ -64,12 +64,15 @@ class SchedulerConfig:
     #: not in the reference: start a new sequence's prefill after the tokens whose blocks came from
     #: the prefix cache (the reference shares those blocks but recomputes them)
     skip_cached_prefix: bool = False
+    #: not in the reference: decode tokens at position total_len - 1 (their logical place) instead of
+    #: total_len, so no cache slot is skipped and no step is refused
+    logical_decode_positions: bool = False
 
     def _c(self):
         return _ffi.OrionSchedulerConfig(self.max_num_seqs, self.max_num_batched_tokens, self.max_model_len or 0,
                                          int(self.enable_chunked_prefill), self.max_waiting_requests,
                                          self.request_timeout_secs or 0, int(self.prioritize_decode),
-                                         int(self.skip_cached_prefix))
+                                         int(self.skip_cached_prefix), int(self.logical_decode_positions))
 
 
 @dataclass(frozen=True)

@@ -474,6 +474,19 @@ def test_prefix_hits_do_not_skip_compute_unless_asked(impl):
         assert s.cache.table(b)[0][:3] == s.cache.table(c)[0], "the prompt blocks are shared either way"
 
 
+def test_decode_positions_follow_the_reference_unless_asked(impl):
+    """scheduler.rs:283 feeds the decode token at total_len (pinned by its own test at :621); the
+    opt-in alternative uses the token's logical position total_len - 1."""
+    for logical, first, second in ((False, 9, 10), (True, 8, 9)):
+        s = sched(impl, 16, logical_decode_positions=logical)
+        sid = s.add(8, 4)
+        s.schedule()
+        s.on_token(sid, 100)
+        assert s.schedule()[0] == [(sid, 1, first, False)]
+        s.on_token(sid, 101)
+        assert s.schedule()[0] == [(sid, 1, second, False)]
+
+
 # ---- engine.rs with the mock model ------------------------------------------------------------------
 
 def mock(favoured):

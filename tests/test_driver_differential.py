@@ -67,6 +67,13 @@ CASES = [
                        skip_cached_prefix=True)),
     (60, 4, True, dict(max_num_seqs=8, max_num_batched_tokens=64, max_model_len=256, enable_chunked_prefill=False,
                        skip_cached_prefix=True)),
+    # the other opt-in extension: decode tokens at their logical position, so no step is ever refused
+    # (a pool large enough that nothing is preempted: a preempted sequence keeps its output tokens but
+    # gets a table for its prompt only, scheduler.rs:311-324, and then fails steps under either rule)
+    (400, 4, True, dict(max_num_seqs=6, max_num_batched_tokens=24, max_model_len=256, enable_chunked_prefill=True,
+                        logical_decode_positions=True)),
+    (20, 4, True, dict(max_num_seqs=6, max_num_batched_tokens=24, max_model_len=256, enable_chunked_prefill=True,
+                       logical_decode_positions=True)),
 ]
 
 
@@ -140,5 +147,7 @@ def test_engines_agree_step_by_step(pkg, case, seed):
         assert hits > 0
     if case in (0, 1, 2):
         assert failed_steps > 0, "the reference's off-by-one decode position should fail a step now and then"
+    if cfg.get("logical_decode_positions") and preemptions == 0:
+        assert failed_steps == 0, "with logical decode positions every scheduled position has its block"
     skipped = ref.sched.stats()["total_skipped_prefill_tokens"]
     assert (skipped > 0) == bool(cfg.get("skip_cached_prefix")), "only the opt-in extension skips prefill compute"

@@ -134,3 +134,28 @@ def test_skipping_the_cached_prefix_keeps_the_tokens(pkg, backend, oracle):
     skipped = runs[True][1]["total_skipped_prefill_tokens"]
     assert skipped == 64 * 3 + 63 + 47, "three suffixed prompts, then two bare prefixes (all but their last token)"
     assert runs[True][1]["total_prefill_tokens"] == runs[False][1]["total_prefill_tokens"] - skipped
+
+
+def test_logical_decode_positions_give_the_plain_greedy_decode(pkg, backend, oracle):
+    """The other opt-in extension: decode tokens at position total_len - 1. No step is refused, no
+    cache slot is skipped, and the tokens are those of a forward driven by hand with the same
+    positions (prefill, then one token per step at its logical place)."""
+    oracle.set_threads(8)
+    p = Pair(pkg, backend, oracle, logical_decode_positions=True)
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, 1024, n).tolist() for n in (31, 47, 16, 80)]  # 31 + 1 and 47 + 1 hit block boundaries
+    ids = [p.submit(prompt, 20) for prompt in prompts]
+    assert p.drain() == 0, "no refused step"
+    # by hand on a fresh oracle model: contiguous tables, logical positions
+    model = oracle.Model(num_blocks=160, block_size=16, **C1_META).load(c1_tensors(seed=1234))
+    for sid, prompt in zip(ids, prompts):
+        table = list(range(100, 100 + (len(prompt) + 20) // 16 + 1))
+        logits = model.forward(oracle.Batch(prompt, list(range(len(prompt))), [len(prompt)], [len(prompt)], [table]))
+        out = [oracle.argmax(logits[0])]
+        for step in range(19):
+            pos = len(prompt) + step
+            logits = model.forward(oracle.Batch([out[-1]], [pos], [1], [pos + 1], [table]))
+            out.append(oracle.argmax(logits[0]))
+        assert p.tokens[sid] == out
+    oracle.set_threads(1)
+    p.arenas_agree()
