@@ -378,6 +378,14 @@ def run_ours(args):
             model.forward(batch, out=logits)
         barrier()
         e2e_s = max_over_ranks(time.perf_counter() - t0)
+        # (2b) the same through forward_greedy(): argmax on the device, token ids out (what the
+        # engine loop uses); reported beside the headline e2e, not instead of it
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            model.forward_greedy(batch)
+        barrier()
+        greedy_s = max_over_ranks(time.perf_counter() - t0)
     # (3) per-kernel device time for the roofline, event pair around every launch
     prof = model.profile(args.steps)
     barrier()
@@ -412,6 +420,9 @@ def run_ours(args):
                    "parallelism": f"tp{world}", "l2": "inputs exceed L2: 15.0 GB of weights + 8.6 GB of KV read per step"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes,
                 "d2h_bytes_per_step": BATCH * m["vocab_size"] * 4},
+        "e2e_greedy": {"value": BATCH * args.steps / greedy_s, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes,
+                       "d2h_bytes_per_step": BATCH * 4,
+                       "note": "forward_greedy: host batch in, argmax on the device, 4 bytes per sequence out"},
         "gpu_launches": int(launches_per_step * args.steps),
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel (projection weights streamed once per step)",
