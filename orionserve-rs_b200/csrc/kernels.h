@@ -179,7 +179,8 @@ constexpr int kMaxTpWorld = 8;
 constexpr uint32_t kTpFusedMaxRows = 256;
 // Peer-mapped inboxes of every rank of the tensor-parallel group (index = rank; the entry of
 // this rank is its own local pointer). An inbox is [parity 2][sender world][slot_floats] units
-// of 8 bytes: one f32 of a partial sum and the epoch of the hand-over that wrote it.
+// of 8 bytes (one f32 of a partial sum and the epoch of the hand-over that wrote it), followed by
+// [parity 2][slot_floats] units for the normalised rows of the two-shot variant.
 struct TpPeers {
   uint32_t *inbox[kMaxTpWorld];
   int rank, world;
@@ -188,10 +189,12 @@ struct TpPeers {
 // All-reduce of the partial sums over ranks and split-K slabs + residual add + RMSNorm for
 // `rows` batch rows; every rank ends up with the full residual stream in `hidden` and all
 // normalised rows in `out`. `epoch` cycles 1, 2, ..., 0xFFFFFFFE, 1, ...: one step per call.
+// `two_shot`: reduce-scatter to the owner of each row + all-gather of the normalised rows (only
+// the owner of a row then holds its current residual); else every rank reduces every row.
 template <typename T>
 int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, const float *partial, uint32_t splits,
                                          size_t split_stride, float *hidden, const float *norm_w, float eps, T *out,
-                                         uint32_t rows, uint32_t hidden_size, cudaStream_t stream);
+                                         uint32_t rows, uint32_t hidden_size, bool two_shot, cudaStream_t stream);
 int tp_poll_error(uint32_t *code);
 
 // ---- GEMM ----------------------------------------------------------------------

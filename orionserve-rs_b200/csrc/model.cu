@@ -323,12 +323,12 @@ int Model<T>::init() {
   if (d.tp_world > 1) {
     nccl_.reset(new NcclCollective());
     ORION_TRY(nccl_->init(d.nccl_unique_id, (int)d.tp_rank, (int)d.tp_world));
-    // The one-shot peer-memory hand-over sends every partial sum to every peer: the fastest way at
-    // 2 ranks (4.01 vs 4.53 ms per headline step), bandwidth-bound beyond (4 ranks: 4.29 vs 3.98 ms
-    // through NCCL; 8 ranks: 6.10 vs 4.09 ms), so it is the default at 2 ranks only.
-    // ORION_TP_ALLREDUCE=fused / nccl forces either.
+    // Peer-memory hand-over (one kernel: all-reduce + residual + norm): one-shot at 2 ranks (every
+    // partial sum to the peer: 4.01 vs 4.53 ms per headline step through NCCL), two-shot beyond
+    // (one-shot is bandwidth-bound there: 4.29 vs 3.98 ms at 4 ranks, 6.10 vs 4.09 ms at 8).
+    // ORION_TP_ALLREDUCE=fused / nccl forces either path.
     const char *mode = std::getenv("ORION_TP_ALLREDUCE");
-    const bool want_fused = mode ? !strcmp(mode, "fused") : d.tp_world == 2;
+    const bool want_fused = mode ? !strcmp(mode, "fused") : true;
     if (want_fused && d.tp_world <= (uint32_t)kMaxTpWorld && H % 4 == 0 && H / 4 <= 4096)
       ORION_TRY(setup_peer_handover());
   }
@@ -343,7 +343,7 @@ template <typename T>
 int Model<T>::setup_peer_handover() {
   const int world = (int)d_.tp_world, rank = (int)d_.tp_rank;
   const size_t slot_floats = (size_t)std::min(d_.max_batch_tokens, kTpFusedMaxRows) * d_.hidden_size;
-  const size_t inbox_words = 2 * (size_t)world * slot_floats * 2;
+  const size_t inbox_words = (2 * (size_t)world + 2) * slot_floats * 2;  // reduce-scatter slots + all-gather slots
   ORION_TRY(alloc(&tp_inbox_, inbox_words));
   ORION_CUDA_CHECK("clear inbox", cudaMemset(tp_inbox_, 0, inbox_words * sizeof(uint32_t)));  // epoch 0 is never sent
   constexpr int kFloatsPerHandle = sizeof(cudaIpcMemHandle_t) / sizeof(float);
@@ -607,7 +607,7 @@ int Model<T>::handover(uint32_t splits, const float *norm_w, T *out, const uint3
   if (nccl_ && tp_fused_ && Tn <= kTpFusedMaxRows) {
     // every rank ends up with the whole residual stream and all Tn normalised rows
     ORION_TRY(launch_tp_allreduce_residual_rmsnorm<T>(peers_, tp_epoch_, partial_, splits, slab, hidden_, norm_w,
-                                                      d_.rms_norm_eps, normed_, Tn, H, stream_));
+                                                      d_.rms_norm_eps, normed_, Tn, H, d_.tp_world > 2, stream_));
     tp_epoch_ = tp_epoch_ == 0xFFFFFFFEu ? 1u : tp_epoch_ + 1;
     if (row_map) return launch_gather_rows<T>(normed_, row_map, out, out_rows, H, stream_);
     if (out != normed_) return set_error(ORION_ERR_INTERNAL, "fused hand-over writes the activation buffer only");

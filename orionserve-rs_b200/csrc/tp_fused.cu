@@ -168,12 +168,115 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
   trace(3);
 }
 
+// Two-shot variant for more than two ranks. Row r belongs to rank r / ceil(rows / world). Every
+// rank folds its split-K slabs for every row and pushes the sums of a row to the row's owner only
+// (reduce-scatter); the owner adds them in rank order, updates its residual row, normalises it
+// and pushes the normalised row to every peer (all-gather). Both pushes use the self-validating
+// 8-byte units of the one-shot kernel, so there is still no barrier and no fence; a rank now
+// sends rows x H x 8 B once instead of world - 1 times, and only the owner keeps a row's
+// residual current (each rank's rows are the same for every hand-over of a step).
+// Inbox of a rank: [parity 2][sender world][slot] units for the reduce-scatter, then
+// [parity 2][slot] units for the all-gather. One CTA per row, on every rank.
+template <typename T, typename Acc>
+__global__ void __launch_bounds__(1024)
+tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ partial, uint32_t splits,
+                  size_t split_stride, float *__restrict__ hidden, const float *__restrict__ w, float eps,
+                  T *__restrict__ out, uint32_t rows, uint32_t H) {
+  __shared__ Acc red[32];
+  pdl_trigger();
+  pdl_wait();  // this rank's projection has finished
+  trace(0);
+  const uint32_t nvec = H / 4, row = blockIdx.x;
+  const uint32_t per = (rows + peers.world - 1) / peers.world;
+  const int owner = (int)(row / per);
+  const size_t slot = (size_t)peers.slot_floats * 2;  // u32 words per slot
+  const size_t scatter = ((size_t)(epoch & 1u) * peers.world) * slot;               // + sender * slot
+  const size_t gather = (size_t)2 * peers.world * slot + (size_t)(epoch & 1u) * slot;
+  float4 v[4];  // H / 4 <= 4 * blockDim.x is guaranteed by the launcher
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t idx = threadIdx.x + c * blockDim.x;
+    if (idx < nvec) v[c] = sum_slabs_local(partial + (size_t)row * H + 4 * (size_t)idx, splits, split_stride);
+  }
+  if (peers.rank != owner) {
+    // ---- not the owner: hand the sums over, then wait for the normalised row ----
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t idx = threadIdx.x + c * blockDim.x;
+      if (idx < nvec) {
+        uint32_t *dst = peers.inbox[owner] + scatter + (size_t)peers.rank * slot + ((size_t)row * H + 4 * (size_t)idx) * 2;
+        st_unit2(dst, v[c].x, v[c].y, epoch);
+        st_unit2(dst + 4, v[c].z, v[c].w, epoch);
+      }
+    }
+    trace(1);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t idx = threadIdx.x + c * blockDim.x;
+      if (idx < nvec) {
+        const size_t off = (size_t)row * H + 4 * (size_t)idx;
+        st_row4<T>(out + off, receive4(peers.inbox[peers.rank] + gather + off * 2, epoch));
+      }
+    }
+    trace(3);
+    return;
+  }
+  // ---- the owner: collect, add in rank order, residual, norm, publish ----
+  trace(1);
+  Acc ss = Acc(0);
+  float *h = hidden + (size_t)row * H;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t idx = threadIdx.x + c * blockDim.x;
+    if (idx < nvec) {
+      const size_t off = (size_t)row * H + 4 * (size_t)idx;
+      float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < peers.world; ++r) {
+        const float4 x = r == peers.rank ? v[c]
+                                         : receive4(peers.inbox[peers.rank] + scatter + (size_t)r * slot + off * 2, epoch);
+        add.x += x.x; add.y += x.y; add.z += x.z; add.w += x.w;
+      }
+      const float4 old = *reinterpret_cast<const float4 *>(h + 4 * (size_t)idx);
+      v[c] = make_float4(old.x + add.x, old.y + add.y, old.z + add.z, old.w + add.w);
+      *reinterpret_cast<float4 *>(h + 4 * (size_t)idx) = v[c];
+      ss += (Acc)v[c].x * (Acc)v[c].x + (Acc)v[c].y * (Acc)v[c].y + (Acc)v[c].z * (Acc)v[c].z +
+            (Acc)v[c].w * (Acc)v[c].w;
+    }
+  }
+  trace(2);
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  Acc total = Acc(0);
+  for (uint32_t i = 0; i < (blockDim.x + 31) / 32; ++i) total += red[i];
+  const float scale = sizeof(Acc) == 8 ? (float)(1.0 / sqrt((double)total / (double)H + (double)eps))
+                                       : rsqrtf((float)total / (float)H + eps);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t idx = threadIdx.x + c * blockDim.x;
+    if (idx < nvec) {
+      const size_t off = (size_t)row * H + 4 * (size_t)idx;
+      const float4 g = *reinterpret_cast<const float4 *>(w + 4 * (size_t)idx);
+      const float4 o = make_float4(__fmul_rn(__fmul_rn(v[c].x, scale), g.x), __fmul_rn(__fmul_rn(v[c].y, scale), g.y),
+                                   __fmul_rn(__fmul_rn(v[c].z, scale), g.z), __fmul_rn(__fmul_rn(v[c].w, scale), g.w));
+      st_row4<T>(out + off, o);
+      for (int r = 0; r < peers.world; ++r)
+        if (r != peers.rank) {
+          uint32_t *dst = peers.inbox[r] + gather + off * 2;
+          st_unit2(dst, o.x, o.y, epoch);
+          st_unit2(dst + 4, o.z, o.w, epoch);
+        }
+    }
+  }
+  trace(3);
+}
+
 }  // namespace
 
 template <typename T>
 int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, const float *partial, uint32_t splits,
                                          size_t split_stride, float *hidden, const float *norm_w, float eps, T *out,
-                                         uint32_t rows, uint32_t hidden_size, cudaStream_t stream) {
+                                         uint32_t rows, uint32_t hidden_size, bool two_shot, cudaStream_t stream) {
   if (hidden_size % 4 != 0 || hidden_size / 4 > 4096 || split_stride % 4 != 0 ||
       (size_t)rows * hidden_size > peers.slot_floats || epoch == 0 || epoch == 0xFFFFFFFFu)
     return set_error(ORION_ERR_INTERNAL, "fused tensor-parallel hand-over: unsupported shape or epoch");
@@ -182,19 +285,24 @@ int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, c
   uint32_t threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
   if (threads < 32) threads = 32;
   using Acc = typename std::conditional<sizeof(T) == 4, double, float>::type;
-  ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
-                   launch_pdl(tp_allreduce_residual_rmsnorm_kernel<T, Acc>, dim3(rows), dim3(threads), 0, stream, peers,
-                              epoch, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size));
+  if (two_shot)
+    ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
+                     launch_pdl(tp_twoshot_kernel<T, Acc>, dim3(rows), dim3(threads), 0, stream, peers, epoch, partial,
+                                splits, split_stride, hidden, norm_w, eps, out, rows, hidden_size));
+  else
+    ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
+                     launch_pdl(tp_allreduce_residual_rmsnorm_kernel<T, Acc>, dim3(rows), dim3(threads), 0, stream, peers,
+                                epoch, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size));
   count_launch();
   ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm", cudaGetLastError());
   return ORION_OK;
 }
 template int launch_tp_allreduce_residual_rmsnorm<float>(const TpPeers &, uint32_t, const float *, uint32_t, size_t,
                                                          float *, const float *, float, float *, uint32_t, uint32_t,
-                                                         cudaStream_t);
+                                                         bool, cudaStream_t);
 template int launch_tp_allreduce_residual_rmsnorm<bf16>(const TpPeers &, uint32_t, const float *, uint32_t, size_t,
                                                         float *, const float *, float, bf16 *, uint32_t, uint32_t,
-                                                        cudaStream_t);
+                                                        bool, cudaStream_t);
 
 int tp_poll_error(uint32_t *code) {
   static const bool tracing = std::getenv("ORION_TP_TRACE") != nullptr;
