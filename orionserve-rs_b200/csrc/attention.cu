@@ -129,7 +129,10 @@ constexpr int kChunkBytes = 2 * kBlk * kHd * 2;  // K rows + V rows of one (bloc
 constexpr int kMaxGroup = 8;      // query heads per kv head (N of the MMA)
 // Ring depth per warp is a template parameter: 2 stages = 65 KiB per CTA (3 CTAs per SM),
 // 3 = 97 KiB (2 per SM), 4 = 129 KiB (1 per SM). The merge buffers (16.3 KiB) reuse the ring.
-constexpr uint32_t decode_smem_bytes(int stages) { return kWarps * stages * kChunkBytes + 1024; }
+// After the ring: 512 bytes of barriers, then the bf16 q / k / v of the row when the kernel makes
+// them itself (kMaxGroup + 2 vectors of 256 bytes).
+constexpr int kStashOffset = 512;
+constexpr uint32_t decode_smem_bytes(int stages) { return kWarps * stages * kChunkBytes + 4096; }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -164,6 +167,20 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
+__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ float4 add4(float4 a, float4 b) {
+  return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+template <typename T>
+__device__ __forceinline__ void st4(T *dst, float4 v);
+template <>
+__device__ __forceinline__ void st4<bf16>(bf16 *dst, float4 v) {
+  uint2 packed;
+  packed.x = pack_bf16x2(v.x, v.y);
+  packed.y = pack_bf16x2(v.z, v.w);
+  *reinterpret_cast<uint2 *>(dst) = packed;
+}
+
 // Device error word: bit 0 = a ring wait ran out of polls.
 __device__ uint32_t g_decode_error = 0;
 
@@ -171,10 +188,11 @@ template <int kStages>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, KvLayout kv,
                     uint32_t layer, AttnBatch batch, uint32_t q_heads, uint32_t splits,
-                    DecodeScratch scratch, bf16 *__restrict__ out, PrefetchHint next) {
+                    DecodeScratch scratch, bf16 *__restrict__ out, PrefetchHint next, FusedQkv fq) {
   extern __shared__ __align__(1024) uint8_t dsmem[];
   uint8_t *ring = dsmem;  // [kWarps][kStages][kChunkBytes]
   uint64_t *bars = reinterpret_cast<uint64_t *>(dsmem + kWarps * kStages * kChunkBytes);
+  bf16 *stash = reinterpret_cast<bf16 *>(dsmem + kWarps * kStages * kChunkBytes + kStashOffset);  // [group + 2][kHd]
 
   const uint32_t kvh = blockIdx.x, row = blockIdx.y, split = blockIdx.z;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -233,11 +251,50 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
     if (lane == 0) issue(deferred, pb);
   }
 
+  if (fq.partial != nullptr) {
+    // q heads of the group, then k, then v of this kv head, from the projection's partial sums:
+    // 16 threads per head, four dims of each RoPE half per thread (tensor.rs:283-298, products
+    // rounded separately like the reference).
+    const uint32_t total_heads = q_heads + 2 * kv.num_kv_heads, half = kHd / 2;
+    const uint32_t pos = ctx - 1, i = (threadIdx.x & 15) * 4;
+    for (uint32_t hh = threadIdx.x >> 4; hh < group + 2; hh += (kWarps * 32) / 16) {
+      const uint32_t head = hh < group ? kvh * group + hh
+                                       : (hh == group ? q_heads + kvh : q_heads + kv.num_kv_heads + kvh);
+      const float *p = fq.partial + ((size_t)row * total_heads + head) * kHd;
+      float4 x0 = ld4(p + i), x1 = ld4(p + i + half);
+      for (uint32_t s = 1; s < fq.slabs; ++s) {
+        x0 = add4(x0, ld4(p + s * fq.slab_stride + i));
+        x1 = add4(x1, ld4(p + s * fq.slab_stride + i + half));
+      }
+      if (fq.bias) {
+        x0 = add4(x0, ld4(fq.bias + (size_t)head * kHd + i));
+        x1 = add4(x1, ld4(fq.bias + (size_t)head * kHd + i + half));
+      }
+      if (hh <= group) {
+        const float4 c = ld4(fq.rope_cos + (size_t)pos * half + i), s = ld4(fq.rope_sin + (size_t)pos * half + i);
+        const float4 r0 = make_float4(__fsub_rn(__fmul_rn(x0.x, c.x), __fmul_rn(x1.x, s.x)),
+                                      __fsub_rn(__fmul_rn(x0.y, c.y), __fmul_rn(x1.y, s.y)),
+                                      __fsub_rn(__fmul_rn(x0.z, c.z), __fmul_rn(x1.z, s.z)),
+                                      __fsub_rn(__fmul_rn(x0.w, c.w), __fmul_rn(x1.w, s.w)));
+        const float4 r1 = make_float4(__fadd_rn(__fmul_rn(x0.x, s.x), __fmul_rn(x1.x, c.x)),
+                                      __fadd_rn(__fmul_rn(x0.y, s.y), __fmul_rn(x1.y, c.y)),
+                                      __fadd_rn(__fmul_rn(x0.z, s.z), __fmul_rn(x1.z, c.z)),
+                                      __fadd_rn(__fmul_rn(x0.w, s.w), __fmul_rn(x1.w, c.w)));
+        x0 = r0;
+        x1 = r1;
+      }
+      st4<bf16>(stash + hh * kHd + i, x0);
+      st4<bf16>(stash + hh * kHd + i + half, x1);
+    }
+    __syncthreads();
+  }
+
   // Q^T as the B operand (k = dim, n = head): per 16-dim chunk two packed regs.
   uint32_t qb[kHd / 16][2];
   {
     const uint32_t g = lane >> 2;
-    const bf16 *qrow = q + ((size_t)row * q_heads + (size_t)kvh * group + g) * kHd;
+    const bf16 *qrow = fq.partial != nullptr ? stash + (g < group ? g : 0) * kHd
+                                             : q + ((size_t)row * q_heads + (size_t)kvh * group + g) * kHd;
 #pragma unroll
     for (int c = 0; c < kHd / 16; ++c) {
       if (g < group) {
@@ -275,6 +332,18 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
     const uint32_t vbase = kbase + kBlk * kHd * 2;
     const uint32_t lb = b_begin + warp + i * kWarps;
     const uint32_t valid = min((uint32_t)kBlk, ctx - lb * kBlk);  // tokens of this block in context
+    if (fq.partial != nullptr && lb == nblocks - 1) {
+      // The block that holds this step's token: its k and v rows come from the stash. Lanes 0-15
+      // copy the sixteen 16-byte groups of k, lanes 16-31 those of v, into the landed chunk (for
+      // this step) and into the arena (for the steps to come), both in the arena's swizzled order.
+      const uint32_t slot = (ctx - 1) % kBlk, j = lane & 15, is_v = lane >> 4;
+      const uint4 val = *reinterpret_cast<const uint4 *>(stash + (group + is_v) * kHd + j * 8);
+      const uint32_t at = (j ^ (slot & 7u)) * 8;  // element offset of the group inside the row
+      *reinterpret_cast<uint4 *>(my_ring + stage * kChunkBytes + ((is_v * kBlk + slot) * kHd + at) * 2) = val;
+      bf16 *dst = fq.arena + kv.row(layer, fq.slot_block[row], kvh, is_v, slot);
+      *reinterpret_cast<uint4 *>(dst + at) = val;
+      __syncwarp();
+    }
 
     // S^T[t][g] = sum_d K[t][d] * Q[g][d]
     float s[4] = {0.f, 0.f, 0.f, 0.f};
@@ -471,7 +540,7 @@ namespace {
 template <int STAGES>
 int launch_decode_stages(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer, AttnBatch batch,
                          uint32_t q_heads, uint32_t splits, DecodeScratch scratch, bf16 *out,
-                         PrefetchHint next, cudaStream_t stream) {
+                         PrefetchHint next, FusedQkv fq, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
     ORION_CUDA_CHECK("paged_decode attr",
@@ -482,7 +551,7 @@ int launch_decode_stages(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t
   ORION_CUDA_CHECK("paged_decode",
                    launch_pdl(paged_decode_kernel<STAGES>, dim3(kv.num_kv_heads, batch.rows, splits),
                               dim3(kWarps * 32), (size_t)decode_smem_bytes(STAGES), stream, q, arena, kv, layer,
-                              batch, q_heads, splits, scratch, out, next));
+                              batch, q_heads, splits, scratch, out, next, fq));
   return ORION_OK;
 }
 }  // namespace
@@ -494,7 +563,8 @@ void decode_set_tuning(int stages, uint32_t cta_target) {
 
 int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer,
                                   AttnBatch batch, uint32_t q_heads, uint32_t splits,
-                                  DecodeScratch scratch, bf16 *out, cudaStream_t stream, PrefetchHint next) {
+                                  DecodeScratch scratch, bf16 *out, cudaStream_t stream, PrefetchHint next,
+                                  FusedQkv fq) {
   if (batch.rows == 0) return ORION_OK;
   if (!decode_attention_supported(kv, q_heads))
     return set_error(ORION_ERR_INTERNAL, "decode attention kernel does not cover this shape");
@@ -503,9 +573,9 @@ int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv,
     return set_error(ORION_ERR_INTERNAL, "decode attention scratch too small for %u splits",
                      splits);
   switch (g_decode_stages) {
-    case 2: ORION_TRY(launch_decode_stages<2>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, next, stream)); break;
-    case 4: ORION_TRY(launch_decode_stages<4>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, next, stream)); break;
-    default: ORION_TRY(launch_decode_stages<3>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, next, stream)); break;
+    case 2: ORION_TRY(launch_decode_stages<2>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, next, fq, stream)); break;
+    case 4: ORION_TRY(launch_decode_stages<4>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, next, fq, stream)); break;
+    default: ORION_TRY(launch_decode_stages<3>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, next, fq, stream)); break;
   }
   ORION_TRY(after_launch("paged_decode"));
   if (splits > 1) {

@@ -162,10 +162,23 @@ size_t decode_scratch_floats(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
                              uint32_t max_splits);
 uint32_t decode_choose_splits(uint32_t rows, uint32_t kv_heads, uint32_t max_position,
                               uint32_t block_size, uint32_t max_splits);
+// With `partial` set the kernel takes the row's q, k and v straight from the QKV projection's
+// f32 partial sums: it folds the split-K slabs, adds the bias, applies RoPE at the row's position
+// (transformer.rs:248-297), writes k and v into the arena slot and uses them for this step, so no
+// separate RoPE / KV-write kernel runs and `q` is not read.
+struct FusedQkv {
+  const float *partial = nullptr;  // [slabs][rows][(q_heads + 2 kv_heads) * head_dim]
+  uint32_t slabs = 0;
+  size_t slab_stride = 0;
+  const float *bias = nullptr;     // [(q_heads + 2 kv_heads) * head_dim] or null
+  const float *rope_cos = nullptr, *rope_sin = nullptr;  // [max_pos][head_dim / 2]
+  const uint32_t *slot_block = nullptr;                  // [rows] physical block of the row's position
+  bf16 *arena = nullptr;           // writable view of the arena
+};
 int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer,
                                   AttnBatch batch, uint32_t q_heads, uint32_t splits,
                                   DecodeScratch scratch, bf16 *out, cudaStream_t stream,
-                                  PrefetchHint next = {});
+                                  PrefetchHint next = {}, FusedQkv fused = {});
 // Tuning: ring depth per warp (2..4) and the CTA count the context split aims for (0 keeps it).
 void decode_set_tuning(int stages, uint32_t cta_target);
 // Device error word of the decode kernel (0 = none); reading clears it.

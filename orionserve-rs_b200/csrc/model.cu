@@ -46,6 +46,8 @@ int compute_layout(uint32_t heads, uint32_t kv_heads, uint32_t ffn, uint32_t ran
 // Off by default: measured at batch 64 on the Llama-3-8B shape, 16..96 MiB of prefetch per
 // hand-over changed the step time by less than the run-to-run noise (5.11-5.20 vs 5.14 ms).
 size_t g_prefetch_budget = 0;
+// Tuning A/B: ORION_FUSE_QKV=0 keeps the separate RoPE / KV-write kernel before decode attention.
+bool g_fuse_qkv = std::getenv("ORION_FUSE_QKV") ? std::atoi(std::getenv("ORION_FUSE_QKV")) != 0 : true;
 // Tuning A/B: ORION_FUSE_SWIGLU=0 keeps the separate SwiGLU kernel after the gate/up projection.
 bool g_fuse_swiglu = std::getenv("ORION_FUSE_SWIGLU") ? std::atoi(std::getenv("ORION_FUSE_SWIGLU")) != 0 : true;
 void model_set_prefetch_budget(size_t bytes) { g_prefetch_budget = bytes; }
@@ -648,13 +650,28 @@ int Model<T>::run_step(bool want_argmax) {
     const Layer &L = layers_[l];
     GemmPlan p = gemm_plan(kBf16, Tn, nqkv, H, H, H);
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_qkv, H, partial_, Tn, nqkv, H, p, stream_); }));
-    ORION_TRY(timed(kProfElementwise, [&] { return launch_rope_kvwrite<T>(partial_, p.out_slabs, (size_t)Tn * nqkv, L.b_qkv, positions, slot_block,
-                                     slot_slot, rope_cos_, rope_sin_, qbuf_, arena_, kv_, l, Tn, lq_, stream_); }));
+    // Pure decode batches on the tuned path: the attention kernel folds the QKV partials, applies
+    // RoPE and writes the KV slot itself, so the separate kernel (and its launch hop) is left out.
+    const bool fuse_qkv = tuned_decode && g_fuse_qkv;
+    if (!fuse_qkv)
+      ORION_TRY(timed(kProfElementwise, [&] { return launch_rope_kvwrite<T>(partial_, p.out_slabs, (size_t)Tn * nqkv, L.b_qkv, positions, slot_block,
+                                       slot_slot, rope_cos_, rope_sin_, qbuf_, arena_, kv_, l, Tn, lq_, stream_); }));
     if (tuned_decode) {
       if constexpr (kBf16) {
         DecodeScratch sc{dscratch_, dscratch_ + (size_t)Tn * lq_ * dsplits * hd, dsplits};
+        FusedQkv fq;
+        if (fuse_qkv) {
+          fq.partial = partial_;
+          fq.slabs = p.out_slabs;
+          fq.slab_stride = (size_t)Tn * nqkv;
+          fq.bias = L.b_qkv;
+          fq.rope_cos = rope_cos_;
+          fq.rope_sin = rope_sin_;
+          fq.slot_block = slot_block;
+          fq.arena = arena_;
+        }
         ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_decode(qbuf_, arena_, kv_, l, ab, lq_, dsplits, sc, attn_, stream_,
-                                                                                     hint(L.w_o, (size_t)H * qd)); }));
+                                                                                     hint(L.w_o, (size_t)H * qd), fq); }));
       }
     } else if (meta_.num_tiles > 0 || meta_.dec_rows > 0) {
       if constexpr (kBf16) {
