@@ -223,7 +223,8 @@ int orion_cuda_set_programmatic_launch(int enabled);
 int orion_cuda_attention_set_tuning(int stages, uint32_t cta_target);
 /* Tuning knob of the projection GEMM: number of CTAs the split-K planner aims
  * for on decode batches (0 restores the default of two per SM) and the ring
- * depth for token tiles of at most 64 (3 or 4 stages; 0 keeps it). */
+ * layout for token tiles of at most 64 (5 = deep weight ring + short activation ring, the
+ * default; 4 = two equal rings; 0 keeps it). */
 int orion_cuda_gemm_set_tuning(uint32_t ctas, int small_batch_stages);
 
 /* ---- tensor parallelism (orion-distributed/src/lib.rs) ---- */

@@ -226,9 +226,9 @@ template <typename T>
 int launch_gemm(const T *x, uint32_t ldx, const T *w, uint32_t ldw, float *partial, uint32_t rows,
                 uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream, PrefetchHint next = {});
 size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t k);
-// Number of CTAs split-K aims for on small batches (default 148, one per SM).
+// Number of CTAs split-K aims for on small batches (default 296, two per SM).
 void gemm_set_target_ctas(uint32_t ctas);
-// Ring depth of the decode-batch GEMM (3 or 4 stages).
+// Ring layout of the decode-batch GEMM: 5 = deep weight ring + short activation ring, 4 = equal rings.
 void gemm_set_small_stages(int stages);
 
 // SIMT GEMM: exact k-ascending accumulation per output, no FMA for f32.

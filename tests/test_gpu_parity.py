@@ -2,7 +2,9 @@
 
 Tolerances: integer / index results are bit-exact; the f32 build must match logits
 within 1e-3 relative error; the bf16 build within 2e-2 max-abs after softmax with
-identical greedy tokens.
+identical greedy tokens, except where the oracle's own top-2 logit gap is below the bf16 logit
+noise (BF16_TIE_MARGIN): there a token may differ, the oracle's token is fed back, and at least
+98 % of all tokens must still be identical. The f32 build is identical on every token.
 """
 import numpy as np
 import pytest
