@@ -62,7 +62,9 @@ def test_linear_f32_is_bit_exact(pkg, backend, oracle, kats):
 
 @pytest.mark.parametrize("rows,n,k", [(1, 128, 64), (3, 256, 4096), (16, 384, 512), (17, 1000, 1024),
                                       (64, 6144, 4096), (64, 4096, 14336), (100, 512, 256),
-                                      (129, 640, 1024), (300, 1152, 2048), (8, 200, 72)])
+                                      (129, 640, 1024), (300, 1152, 2048), (8, 200, 72),
+                                      # Llama-3-70B projections on one of 8 ranks: qkv, o, gate|up, down
+                                      (16, 1280, 8192), (16, 8192, 1024), (16, 7168, 8192), (16, 8192, 3584)])
 def test_linear_bf16_tensor_core_matches_the_oracle(pkg, backend, oracle, rows, n, k):
     rng = np.random.default_rng(rows * 7 + n)
     x = oracle.round_to_bf16(rng.standard_normal((rows, k)).astype(np.float32))
@@ -162,7 +164,9 @@ def test_attention_kats(pkg, backend, oracle, kats):
 
 @pytest.mark.parametrize("dtype_name,hq,hkv,hd,bs", [("F32", 4, 2, 64, 16), ("F32", 6, 3, 20, 8),
                                                      ("BF16", 4, 2, 64, 16), ("BF16", 32, 8, 128, 16),
-                                                     ("BF16", 28, 4, 128, 16), ("BF16", 8, 8, 128, 16)])
+                                                     ("BF16", 28, 4, 128, 16), ("BF16", 8, 8, 128, 16),
+                                                     # Llama-3-70B: eight query heads per KV head
+                                                     ("BF16", 64, 8, 128, 16), ("BF16", 8, 1, 128, 16)])
 def test_attention_ragged_batches(pkg, backend, oracle, dtype_name, hq, hkv, hd, bs):
     """Decode rows and prefill rows through scattered tables; the 128/16 bf16 cases take the
     tuned decode kernel (one row per sequence), the rest the generic kernel."""
@@ -396,7 +400,7 @@ def test_config1_greedy_decode_matches_the_oracle(pkg, backend, oracle, dtype_na
     assert rep.passed(), rep.render()
 
 
-@pytest.mark.parametrize("heads,kv_heads", [(8, 2), (14, 2)])
+@pytest.mark.parametrize("heads,kv_heads", [(8, 2), (14, 2), (16, 2)])
 def test_chunked_prefill_and_mixed_batches_on_the_tuned_path(pkg, backend, oracle, heads, kv_heads):
     """head_dim 128 / block 16 / bf16: chunked prefill rows, decode rows and both in one batch
     (the tensor-core prefill attention and decode attention kernels), against the oracle."""
