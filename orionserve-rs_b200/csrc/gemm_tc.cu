@@ -52,15 +52,20 @@ __device__ __forceinline__ void gtrace(uint32_t slot, int k) {
 // XST stages of TOKN x 128 B are enough. Measured on decode shapes, weight bandwidth follows
 // the weight bytes in flight per SM (160 KiB -> 6.0 TB/s, 128 KiB -> 5.3 TB/s), so shared
 // memory goes to the W ring first.
-template <int TOKN, int WST, int XST>
+// MT = weight tiles of 128 rows per CTA. Decode batches stream weights (MT = 1, as many CTAs as
+// possible); prefill batches are tensor-bound and limited by the shared-memory fill rate, so a
+// CTA there takes two weight tiles against one activation tile (MT = 2: 64 KiB of operands per
+// 2.1 MFLOP instead of 48 KiB per 1.05), with two accumulators in tensor memory.
+template <int TOKN, int WST, int XST, int MT = 1>
 struct TcConfig {
-  static constexpr int kWBytes = kTileN * kSlabK * 2;
+  static constexpr int kWBytes = MT * kTileN * kSlabK * 2;
   static constexpr int kXBytes = TOKN * kSlabK * 2;
   static constexpr int kWStages = WST;
   static constexpr int kXStages = XST;
   static constexpr int kXRingOffset = WST * kWBytes;
   static constexpr int kBarrierOffset = kXRingOffset + XST * kXBytes;
-  static constexpr int kTmemCols = TOKN < 32 ? 32 : TOKN;
+  static constexpr int kTmemCols = MT * TOKN < 32 ? 32 : MT * TOKN;
+  static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "tensor memory columns: a power of two up to 512");
   static constexpr int kSmemBytes = kBarrierOffset + 1024 /*align*/ + 512 /*barriers*/;
 };
 
@@ -149,12 +154,12 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
          ((uint32_t)(kTileN >> 4) << 24);
 }
 
-template <int TOKN, int WST, int XST>
+template <int TOKN, int WST, int XST, int MT>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                float *__restrict__ partial, bf16 *__restrict__ act, uint32_t M, uint32_t N, uint32_t K,
                uint32_t splits, uint32_t cluster_reduce, PrefetchHint next) {
-  using Cfg = TcConfig<TOKN, WST, XST>;
+  using Cfg = TcConfig<TOKN, WST, XST, MT>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                               ~uintptr_t(1023));
@@ -167,7 +172,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t n0 = blockIdx.x * kTileN, t0 = blockIdx.y * TOKN, split = blockIdx.z;
+  const uint32_t n0 = blockIdx.x * (MT * kTileN), t0 = blockIdx.y * TOKN, split = blockIdx.z;
   const uint32_t nkb = (K + kSlabK - 1) / kSlabK;
   const uint32_t kb_begin = (uint32_t)((uint64_t)split * nkb / splits);
   const uint32_t kb_end = (uint32_t)((uint64_t)(split + 1) * nkb / splits);
@@ -214,7 +219,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t s = i % WST, use = i / WST;
         if (!mbar_wait(&empty_w[s], (use & 1) ^ 1)) { ok = false; break; }
         mbar_arrive_expect_tx(&full_w[s], Cfg::kWBytes);
-        tma_load_2d(w_ring + s * Cfg::kWBytes, &map_w, (int)((kb_begin + i) * kSlabK), (int)n0, &full_w[s]);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)  // rows past the matrix read as zeros and still count their bytes
+          tma_load_2d(w_ring + s * Cfg::kWBytes + mt * (kTileN * kSlabK * 2), &map_w, (int)((kb_begin + i) * kSlabK),
+                      (int)(n0 + mt * kTileN), &full_w[s]);
       }
       prefetch_slice(next);  // own loads are all issued: start pulling the next GEMM's weights into L2
     }
@@ -244,9 +252,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < kSlabK / kUmmaK; ++k) {
           // advancing 16 k elements inside the swizzle atom = +32 bytes on the start address
-          const uint64_t a = smem_desc_sw128(wt + k * kUmmaK * 2);
           const uint64_t b = smem_desc_sw128(xt + k * kUmmaK * 2);
-          umma_bf16(tmem_base, a, b, idesc, (i > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {  // one accumulator of TOKN columns per weight tile
+            const uint64_t a = smem_desc_sw128(wt + mt * (kTileN * kSlabK * 2) + k * kUmmaK * 2);
+            umma_bf16(tmem_base + (uint32_t)(mt * TOKN), a, b, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          }
         }
         umma_commit(&empty_w[sw]);  // both stages are free once these MMAs have read them
         umma_commit(&empty_x[sx]);
@@ -263,17 +274,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after();
     if (threadIdx.x == 128) gtrace(tslot, 5);
     pdl_wait();  // the partial buffer may still be read by the kernel before the producer of x
-    const uint32_t n = n0 + lq * 32 + lane;
     float *dst = partial + (size_t)split * M * N;
     // Split-K inside a cluster: the tile goes to shared memory as stage[token][128 weight rows]
     // (the rings are idle: every load has landed and every MMA has read its operands).
     float *stage = reinterpret_cast<float *>(smem);
 #pragma unroll 1
-    for (int c = 0; c < TOKN; c += 16) {
-      if (t0 + c >= M) break;  // warp-uniform
+    for (int mc = 0; mc < MT * TOKN; mc += 16) {
+      const int mt = mc / TOKN, c = mc % TOKN;  // weight tile, first token column of this chunk
+      const uint32_t n = n0 + mt * kTileN + lq * 32 + lane;
+      if (t0 + c >= M) continue;  // warp-uniform
       uint32_t r[16];
       if (ok && my_kb > 0) {
-        tmem_ld16(tmem_base + ((lq * 32u) << 16) + (uint32_t)c, r);
+        tmem_ld16(tmem_base + ((lq * 32u) << 16) + (uint32_t)mc, r);
         tmem_ld_wait();
       } else {
 #pragma unroll
@@ -404,16 +416,17 @@ int cached_map(const void *base, uint64_t rows, uint64_t k, uint64_t ld, uint32_
   return ORION_OK;
 }
 
-template <int TOKN, int WST, int XST>
+template <int TOKN, int WST, int XST, int MT = 1>
 int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial, bf16 *act,
               uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, bool cluster_reduce, PrefetchHint next,
               cudaStream_t stream) {
-  using Cfg = TcConfig<TOKN, WST, XST>;
+  using Cfg = TcConfig<TOKN, WST, XST, MT>;
   static_assert(Cfg::kSmemBytes <= 232448, "ring exceeds the shared memory of an SM");
+  if (MT > 1 && cluster_reduce) return set_error(ORION_ERR_INTERNAL, "cluster split-K is built for one weight tile per CTA");
   static bool attr_set = false;
   if (!attr_set) {
     ORION_CUDA_CHECK("gemm_tc attr",
-                     cudaFuncSetAttribute(gemm_tc_kernel<TOKN, WST, XST>,
+                     cudaFuncSetAttribute(gemm_tc_kernel<TOKN, WST, XST, MT>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           Cfg::kSmemBytes));
     attr_set = true;
@@ -421,19 +434,27 @@ int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *p
   const CUtensorMap *mw, *mx;
   ORION_TRY(cached_map(w, n, k, ldw, kTileN, &mw));
   ORION_TRY(cached_map(x, rows, k, ldx, TOKN, &mx));
-  dim3 grid((n + kTileN - 1) / kTileN, (rows + TOKN - 1) / TOKN, splits);
+  dim3 grid((n + MT * kTileN - 1) / (MT * kTileN), (rows + TOKN - 1) / TOKN, splits);
   if (cluster_reduce)
-    ORION_CUDA_CHECK("gemm_tc", launch_pdl_cluster(gemm_tc_kernel<TOKN, WST, XST>, grid, dim3(kThreads), dim3(1, 1, splits),
+    ORION_CUDA_CHECK("gemm_tc", launch_pdl_cluster(gemm_tc_kernel<TOKN, WST, XST, MT>, grid, dim3(kThreads), dim3(1, 1, splits),
                                                    Cfg::kSmemBytes, stream, *mw, *mx, partial, act, rows, n, k, splits,
                                                    1u, next));
   else
-    ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, WST, XST>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
+    ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, WST, XST, MT>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
                                            *mw, *mx, partial, act, rows, n, k, splits, 0u, next));
   count_launch();
   ORION_CUDA_CHECK("gemm_tc", cudaGetLastError());
   return ORION_OK;
 }
 
+// Tuning A/B: ORION_GEMM_PREFILL_TILES=1 keeps one weight tile per CTA for prefill-sized batches
+// (two tiles measured 3 % faster on the continuous-batching workload, gate/up only: the other
+// projections have too few tiles to halve their grid).
+int g_prefill_tiles = std::getenv("ORION_GEMM_PREFILL_TILES") ? std::atoi(std::getenv("ORION_GEMM_PREFILL_TILES")) : 2;
+// How a prefill-sized projection with fewer than 148 tiles of 256 tokens reaches every SM: 2 = k
+// splits (default), 1 = 128-token tiles, 0 = not at all. Measured on the continuous-batching
+// workload at the 8B shape: 12.07 / 12.46 / 12.32 s. ORION_GEMM_PREFILL_FILL overrides.
+int g_prefill_fill = std::getenv("ORION_GEMM_PREFILL_FILL") ? std::atoi(std::getenv("ORION_GEMM_PREFILL_FILL")) : 2;
 int g_small_stages = 5;  // 5: deep weight ring + short activation ring for decode batches; 4: equal rings
 
 uint32_t token_tile(uint32_t rows) {
@@ -464,7 +485,10 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
   if (splits < 1 || splits > nkb)
     return set_error(ORION_ERR_INTERNAL, "gemm split count %u outside 1..%u", splits, nkb);
   const bool deep = g_small_stages >= 5;
-  switch (token_tile(rows)) {
+  uint32_t tt = token_tile(rows);
+  // prefill batches whose 256-token tiles would leave SMs idle take 128-token tiles instead
+  if (rows > 256 && g_prefill_fill == 1 && ((n + kTileN - 1) / kTileN) * ((rows + 255) / 256) < 148) tt = 128;
+  switch (tt) {
     case 16:
       return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream)
                   : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
@@ -475,7 +499,12 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
       return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream)
                   : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
     case 128: return launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
-    default: return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
+    default:
+      // prefill with enough weight tiles to keep every SM busy anyway: two weight tiles per CTA
+      if (rows > 256 && splits == 1 && !cluster_reduce && g_prefill_tiles == 2 &&
+          ((n + kTileN - 1) / kTileN) * ((rows + 255) / 256) >= 296)
+        return launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
+      return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
   }
 }
 
@@ -534,7 +563,21 @@ GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t
         encode_fn() != nullptr))
     return p;
   p.tensor_core = true;
-  if (rows > 256) return p;  // many token tiles already fill the machine
+  if (rows > 256) {
+    // Prefill-sized batches are tensor-bound; the 256-token tiles take a whole SM each (192 KiB of
+    // rings), so a projection with few weight tiles (N = 4096: 32) needs k splits to reach all SMs.
+    const uint32_t big = ((n + kTileN - 1) / kTileN) * ((rows + 255) / 256);
+    const uint32_t nkb_big = (k + kSlabK - 1) / kSlabK;
+    if (big < 148 && g_prefill_fill == 2) {
+      uint32_t s = 296 / big;
+      const uint32_t cap = nkb_big / 8 ? nkb_big / 8 : 1;  // at least eight k slabs per split
+      if (s > cap) s = cap;
+      if (s > 4) s = 4;
+      p.splits = p.out_slabs = s < 1 ? 1 : s;
+    }
+    (void)nkb_big;
+    return p;
+  }
   const uint32_t tiles = ((n + kTileN - 1) / kTileN) * ((rows + token_tile(rows) - 1) / token_tile(rows));
   const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
   uint32_t s = g_target_ctas / (tiles ? tiles : 1);
@@ -551,8 +594,7 @@ GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t
 size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t k) {
   size_t best = (size_t)max_rows * n;
   if (!is_bf16) return best;
-  const uint32_t lim = max_rows < 256 ? max_rows : 256;
-  for (uint32_t r = 1; r <= lim; ++r) {
+  for (uint32_t r = 1; r <= max_rows; ++r) {
     const GemmPlan p = gemm_plan(true, r, n, k, k, k);
     const size_t need = (size_t)p.splits * r * n;
     if (need > best) best = need;

@@ -63,6 +63,8 @@ def test_linear_f32_is_bit_exact(pkg, backend, oracle, kats):
 @pytest.mark.parametrize("rows,n,k", [(1, 128, 64), (3, 256, 4096), (16, 384, 512), (17, 1000, 1024),
                                       (64, 6144, 4096), (64, 4096, 14336), (100, 512, 256),
                                       (129, 640, 1024), (300, 1152, 2048), (8, 200, 72),
+                                      # prefill-sized batches: two weight tiles per CTA, ragged last tile
+                                      (512, 384, 512), (260, 128, 64), (700, 2176, 256),
                                       # Llama-3-70B projections on one of 8 ranks: qkv, o, gate|up, down
                                       (16, 1280, 8192), (16, 8192, 1024), (16, 7168, 8192), (16, 8192, 3584)])
 def test_linear_bf16_tensor_core_matches_the_oracle(pkg, backend, oracle, rows, n, k):
