@@ -35,9 +35,9 @@ WORKLOAD = "llama3_8b_decode_batch64_ctx1024_bf16"
 METRIC = "decode tokens/s at batch 64 (Llama-3-8B shape)"
 # DRAM bytes (read + write) of the projection GEMM launches of one 32-layer step, from the ncu
 # capture summarised in profiles/gemm_tc_kernel_decode_batch64_llama3_8b_shape.md: the four
-# projections of one layer moved 450.13 MB (algorithmic 436.21 MB); 32 layers of that plus the LM
+# projections of one layer moved 449.09 MB (algorithmic 436.21 MB); 32 layers of that plus the LM
 # head at its algorithmic 1050.67 MB of weights + 32.83 MB of logits (the head was not captured).
-GEMM_TRAFFIC_BYTES_PER_STEP = int(32 * 450.13e6 + 1050.67e6 + 32.83e6)
+GEMM_TRAFFIC_BYTES_PER_STEP = int(32 * 449.09e6 + 1050.67e6 + 32.83e6)
 
 
 def measured_peaks():

@@ -380,20 +380,33 @@ __global__ void finish_linear_kernel(const float *__restrict__ partial, uint32_t
   }
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 argmax_kernel(const float *__restrict__ logits, uint32_t cols, uint32_t *__restrict__ out) {
-  __shared__ float s_val[8];
-  __shared__ uint32_t s_idx[8];
+  __shared__ float s_val[32];
+  __shared__ uint32_t s_idx[32];
   pdl_trigger();
   pdl_wait();
   const float *row = logits + (size_t)blockIdx.x * cols;
   float best = -INFINITY;
   uint32_t best_i = UINT32_MAX;
-  for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
-    const float v = row[c];
-    if (v > best) {  // strict: the lowest index of equal maxima survives; NaN never wins
-      best = v;
-      best_i = c;
+  // strict comparisons in ascending index order: the lowest index of equal maxima survives and
+  // NaN never wins (sampling.rs:196-206)
+  if ((cols & 3u) == 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+    const float4 *row4 = reinterpret_cast<const float4 *>(row);
+    for (uint32_t c = threadIdx.x; c < cols / 4; c += blockDim.x) {
+      const float4 v = row4[c];
+      if (v.x > best) { best = v.x; best_i = 4 * c; }
+      if (v.y > best) { best = v.y; best_i = 4 * c + 1; }
+      if (v.z > best) { best = v.z; best_i = 4 * c + 2; }
+      if (v.w > best) { best = v.w; best_i = 4 * c + 3; }
+    }
+  } else {
+    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float v = row[c];
+      if (v > best) {
+        best = v;
+        best_i = c;
+      }
     }
   }
 #pragma unroll
@@ -411,7 +424,7 @@ argmax_kernel(const float *__restrict__ logits, uint32_t cols, uint32_t *__restr
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int w = 1; w < 8; ++w) {
+    for (uint32_t w = 1; w < blockDim.x / 32; ++w) {
       if (s_val[w] > best || (s_val[w] == best && s_idx[w] < best_i)) {
         best = s_val[w];
         best_i = s_idx[w];
@@ -649,7 +662,8 @@ int launch_finish_linear(const float *partial, uint32_t splits, size_t split_str
 int launch_argmax(const float *logits, uint32_t rows, uint32_t cols, uint32_t *out,
                   cudaStream_t stream) {
   if (rows == 0) return ORION_OK;
-  ORION_CUDA_CHECK("argmax", launch_pdl(argmax_kernel, dim3(rows), dim3(256), 0, stream, logits, cols, out));
+  const uint32_t threads = cols >= 16384 ? 1024 : 256;
+  ORION_CUDA_CHECK("argmax", launch_pdl(argmax_kernel, dim3(rows), dim3(threads), 0, stream, logits, cols, out));
   return after_launch("argmax");
 }
 
