@@ -268,29 +268,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else if (warp >= 4) {
     // Epilogue warps: warp w may touch tensor-memory lanes 32*(w%4) .. +31.
     const uint32_t lq = warp & 3;
+    // The partial buffer may still be read by the kernel before the producer of x: wait for the
+    // predecessor here, while the main loop runs, rather than after the accumulator is ready.
+    pdl_wait();
     if (my_kb > 0) {
       if (!mbar_wait(acc_ready, 0)) ok = false;
     }
     tc_fence_after();
     if (threadIdx.x == 128) gtrace(tslot, 5);
-    pdl_wait();  // the partial buffer may still be read by the kernel before the producer of x
     float *dst = partial + (size_t)split * M * N;
     // Split-K inside a cluster: the tile goes to shared memory as stage[token][128 weight rows]
     // (the rings are idle: every load has landed and every MMA has read its operands).
     float *stage = reinterpret_cast<float *>(smem);
+    // Tensor-memory loads are issued for up to four 16-column chunks before the one wait, so the
+    // round trips of a batch overlap; stores follow chunk by chunk.
+    constexpr int kBatch = TOKN >= 64 ? 4 : TOKN / 16;
 #pragma unroll 1
-    for (int mc = 0; mc < MT * TOKN; mc += 16) {
-      const int mt = mc / TOKN, c = mc % TOKN;  // weight tile, first token column of this chunk
-      const uint32_t n = n0 + mt * kTileN + lq * 32 + lane;
-      if (t0 + c >= M) continue;  // warp-uniform
-      uint32_t r[16];
+    for (int mb = 0; mb < MT * TOKN; mb += 16 * kBatch) {
+      uint32_t rr[kBatch][16];
       if (ok && my_kb > 0) {
-        tmem_ld16(tmem_base + ((lq * 32u) << 16) + (uint32_t)mc, r);
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) tmem_ld16(tmem_base + ((lq * 32u) << 16) + (uint32_t)(mb + 16 * b), rr[b]);
         tmem_ld_wait();
       } else {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) r[j] = 0u;
+        for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+          for (int j = 0; j < 16; ++j) rr[b][j] = 0u;
       }
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+      const int mc = mb + 16 * b;
+      const int mt = mc / TOKN, c = mc % TOKN;  // weight tile, first token column of this chunk
+      const uint32_t n = n0 + mt * kTileN + lq * 32 + lane;
+      if (t0 + c >= M) continue;  // warp-uniform
+      uint32_t (&r)[16] = rr[b];
       if (cluster_reduce) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) stage[(c + j) * kTileN + lq * 32 + lane] = __uint_as_float(r[j]);
@@ -315,6 +327,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const uint32_t tok = t0 + c + j;
           if (tok < M) dst[(size_t)tok * N + n] = __uint_as_float(r[j]);
         }
+      }
       }
     }
   }
