@@ -468,6 +468,13 @@ int g_prefill_tiles = std::getenv("ORION_GEMM_PREFILL_TILES") ? std::atoi(std::g
 // splits (default), 1 = 128-token tiles, 0 = not at all. Measured on the continuous-batching
 // workload at the 8B shape: 12.07 / 12.46 / 12.32 s. ORION_GEMM_PREFILL_FILL overrides.
 int g_prefill_fill = std::getenv("ORION_GEMM_PREFILL_FILL") ? std::atoi(std::getenv("ORION_GEMM_PREFILL_FILL")) : 2;
+// Weight tiles per CTA for a prefill-sized batch: two share one activation tile (less shared-memory
+// fill per flop). Mode 2: only where the grid stays full without k splits; mode 3: always.
+uint32_t prefill_weight_tiles(uint32_t rows, uint32_t n) {
+  if (rows <= 256 || g_prefill_tiles < 2) return 1;
+  if (g_prefill_tiles >= 3) return 2;
+  return ((n + kTileN - 1) / kTileN) * ((rows + 255) / 256) >= 296 ? 2 : 1;
+}
 int g_small_stages = 5;  // 5: deep weight ring + short activation ring for decode batches; 4: equal rings
 
 uint32_t token_tile(uint32_t rows) {
@@ -513,9 +520,7 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
                   : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
     case 128: return launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
     default:
-      // prefill with enough weight tiles to keep every SM busy anyway: two weight tiles per CTA
-      if (rows > 256 && splits == 1 && !cluster_reduce && g_prefill_tiles == 2 &&
-          ((n + kTileN - 1) / kTileN) * ((rows + 255) / 256) >= 296)
+      if (rows > 256 && !cluster_reduce && prefill_weight_tiles(rows, n) == 2)
         return launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
       return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
   }
@@ -579,7 +584,8 @@ GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t
   if (rows > 256) {
     // Prefill-sized batches are tensor-bound; the 256-token tiles take a whole SM each (192 KiB of
     // rings), so a projection with few weight tiles (N = 4096: 32) needs k splits to reach all SMs.
-    const uint32_t big = ((n + kTileN - 1) / kTileN) * ((rows + 255) / 256);
+    const uint32_t rows_per_cta = kTileN * prefill_weight_tiles(rows, n);
+    const uint32_t big = ((n + rows_per_cta - 1) / rows_per_cta) * ((rows + 255) / 256);
     const uint32_t nkb_big = (k + kSlabK - 1) / kSlabK;
     if (big < 148 && g_prefill_fill == 2) {
       uint32_t s = 296 / big;
