@@ -213,10 +213,11 @@ def run_reference(args):
 def make_decode_batch(pkg, rng, num_blocks):
     perm = rng.permutation(num_blocks)
     nblk = (CONTEXT + BLOCK - 1) // BLOCK
-    tables = [perm[s * nblk:(s + 1) * nblk].tolist() for s in range(BATCH)]
-    tokens = rng.integers(0, LLAMA3_8B["vocab_size"], BATCH)
-    return pkg.ForwardBatch(tokens, [CONTEXT - 1] * BATCH, list(range(1, BATCH + 1)), [1] * BATCH,
-                            [CONTEXT] * BATCH, tables, has_prefill=False)
+    # the batch as contiguous host arrays, the form the reference's ForwardBatch vectors have
+    tables = np.ascontiguousarray(perm[:BATCH * nblk].reshape(BATCH, nblk), dtype=np.uint32)
+    tokens = rng.integers(0, LLAMA3_8B["vocab_size"], BATCH).astype(np.uint32)
+    return pkg.ForwardBatch(tokens, np.full(BATCH, CONTEXT - 1, np.uint32), np.arange(1, BATCH + 1, dtype=np.uint64),
+                            np.ones(BATCH, np.uint64), np.full(BATCH, CONTEXT, np.uint64), tables, has_prefill=False)
 
 
 def attention_sweep(pkg, backend, peak):

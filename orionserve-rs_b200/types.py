@@ -117,12 +117,16 @@ class ForwardBatch:
         positions = np.ascontiguousarray(self.positions, dtype=np.uint32)
         counts = np.ascontiguousarray(self.slot_token_counts, dtype=np.uint64)
         ctx = np.ascontiguousarray(self.context_lens, dtype=np.uint64)
-        lens = np.fromiter((len(t) for t in self.block_tables), dtype=np.uint64,
-                           count=len(self.block_tables))
-        offsets = np.zeros(len(self.block_tables) + 1, np.uint64)
+        tables = self.block_tables
+        if isinstance(tables, np.ndarray) and tables.ndim == 2:  # equal-length tables kept as one array
+            offsets = np.arange(tables.shape[0] + 1, dtype=np.uint64) * np.uint64(tables.shape[1])
+            flat = np.append(np.ascontiguousarray(tables, dtype=np.uint32).ravel(), np.uint32(0))
+            return tokens, positions, counts, ctx, flat, offsets
+        lens = np.fromiter((len(t) for t in tables), dtype=np.uint64, count=len(tables))
+        offsets = np.zeros(len(tables) + 1, np.uint64)
         np.cumsum(lens, out=offsets[1:])
-        if len(self.block_tables):
-            flat = np.concatenate([np.asarray(t, dtype=np.uint32).ravel() for t in self.block_tables]
+        if len(tables):
+            flat = np.concatenate([np.asarray(t, dtype=np.uint32).ravel() for t in tables]
                                   + [np.zeros(1, np.uint32)])
         else:
             flat = np.zeros(1, np.uint32)
