@@ -158,7 +158,7 @@ template <int TOKN, int WST, int XST, int MT>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                float *__restrict__ partial, bf16 *__restrict__ act, uint32_t M, uint32_t N, uint32_t K,
-               uint32_t splits, uint32_t cluster_reduce, PrefetchHint next) {
+               uint32_t splits, uint32_t cluster_reduce, uint32_t ldc, PrefetchHint next) {
   using Cfg = TcConfig<TOKN, WST, XST, MT>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
@@ -325,7 +325,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const uint32_t tok = t0 + c + j;
-          if (tok < M) dst[(size_t)tok * N + n] = __uint_as_float(r[j]);
+          if (tok < M) dst[(size_t)tok * ldc + n] = __uint_as_float(r[j]);  // ldc: row stride of the output
         }
       }
       }
@@ -431,8 +431,11 @@ int cached_map(const void *base, uint64_t rows, uint64_t k, uint64_t ld, uint32_
 
 template <int TOKN, int WST, int XST, int MT = 1>
 int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial, bf16 *act,
-              uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, bool cluster_reduce, PrefetchHint next,
-              cudaStream_t stream) {
+              uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, bool cluster_reduce, uint32_t ldc,
+              PrefetchHint next, cudaStream_t stream) {
+  if (ldc == 0) ldc = n;
+  if (ldc != n && (splits != 1 || act != nullptr))
+    return set_error(ORION_ERR_INTERNAL, "a strided GEMM output needs one k split and f32 results");
   using Cfg = TcConfig<TOKN, WST, XST, MT>;
   static_assert(Cfg::kSmemBytes <= 232448, "ring exceeds the shared memory of an SM");
   if (MT > 1 && cluster_reduce) return set_error(ORION_ERR_INTERNAL, "cluster split-K is built for one weight tile per CTA");
@@ -451,10 +454,10 @@ int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *p
   if (cluster_reduce)
     ORION_CUDA_CHECK("gemm_tc", launch_pdl_cluster(gemm_tc_kernel<TOKN, WST, XST, MT>, grid, dim3(kThreads), dim3(1, 1, splits),
                                                    Cfg::kSmemBytes, stream, *mw, *mx, partial, act, rows, n, k, splits,
-                                                   1u, next));
+                                                   1u, ldc, next));
   else
     ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, WST, XST, MT>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
-                                           *mw, *mx, partial, act, rows, n, k, splits, 0u, next));
+                                           *mw, *mx, partial, act, rows, n, k, splits, 0u, ldc, next));
   count_launch();
   ORION_CUDA_CHECK("gemm_tc", cudaGetLastError());
   return ORION_OK;
@@ -497,7 +500,7 @@ bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint
 
 int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
                    uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream,
-                   PrefetchHint next, bf16 *act, bool cluster_reduce) {
+                   PrefetchHint next, bf16 *act, bool cluster_reduce, uint32_t ldc) {
   const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
   if (cluster_reduce && (splits < 2 || splits > 8 || act != nullptr))
     return set_error(ORION_ERR_INTERNAL, "cluster split-K needs 2..8 splits and f32 output");
@@ -511,19 +514,19 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
   if (rows > 256 && g_prefill_fill == 1 && ((n + kTileN - 1) / kTileN) * ((rows + 255) / 256) < 148) tt = 128;
   switch (tt) {
     case 16:
-      return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream)
-                  : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
+      return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
+                  : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
     case 32:
-      return deep ? launch_tc<32, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream)
-                  : launch_tc<32, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
+      return deep ? launch_tc<32, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
+                  : launch_tc<32, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
     case 64:
-      return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream)
-                  : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
-    case 128: return launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
+      return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
+                  : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
+    case 128: return launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
     default:
       if (rows > 256 && !cluster_reduce && prefill_weight_tiles(rows, n) == 2)
-        return launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
-      return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, next, stream);
+        return launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
+      return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
   }
 }
 
@@ -575,7 +578,7 @@ void gemm_set_small_stages(int stages) { g_small_stages = stages >= 5 ? 5 : 4; }
 
 GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx,
                    uint32_t ldw) {
-  GemmPlan p{1, false, false, 1};
+  GemmPlan p{1, false, false, 1, 0};
   if (!is_bf16) return p;
   // alignment of the pointers is checked at launch; shapes decide the plan
   if (!(rows > 0 && n > 0 && k >= (uint32_t)kSlabK && k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 &&
@@ -642,8 +645,10 @@ int launch_gemm<bf16>(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, 
   if (plan.tensor_core) {
     if (!gemm_tc_supported(rows, n, k, ldx, ldw, x, w))
       return set_error(ORION_ERR_INTERNAL, "tensor-core GEMM planned for an unaligned operand");
-    return launch_gemm_tc(x, ldx, w, ldw, partial, rows, n, k, plan.splits, stream, next, nullptr, plan.cluster_reduce);
+    return launch_gemm_tc(x, ldx, w, ldw, partial, rows, n, k, plan.splits, stream, next, nullptr, plan.cluster_reduce,
+                          plan.ldc);
   }
+  if (plan.ldc != 0 && plan.ldc != n) return set_error(ORION_ERR_INTERNAL, "a strided GEMM output needs the tensor-core path");
   return launch_gemm_simt<bf16>(x, ldx, w, ldw, partial, rows, n, k, stream);
 }
 

@@ -220,6 +220,7 @@ struct GemmPlan {
   bool tensor_core;     // tcgen05 path (bf16 only)
   bool cluster_reduce;  // the k splits of a tile form a cluster and reduce in shared memory
   uint32_t out_slabs;   // slabs the consumer has to sum: 1 with cluster_reduce, else `splits`
+  uint32_t ldc;         // row stride of the output when it is a column block of a wider matrix (0 = n)
 };
 GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint32_t ldw);
 template <typename T>
@@ -240,7 +241,7 @@ bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint
                        const void *x, const void *w);
 int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
                    uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream,
-                   PrefetchHint next = {}, bf16 *act = nullptr, bool cluster_reduce = false);
+                   PrefetchHint next = {}, bf16 *act = nullptr, bool cluster_reduce = false, uint32_t ldc = 0);
 // Gate/up projection with SwiGLU in the epilogue: `w_interleaved` is [2 * ffn][k] with gate row f
 // at 2f and up row f at 2f + 1; writes act[r][f] = silu(x.gate_f) * (x.up_f) and no partials.
 // One k split only (gemm_plan(...).splits == 1 and .tensor_core).

@@ -89,6 +89,9 @@ class Model final : public ModelBase {
     if (h_meta_) cudaFreeHost(h_meta_);
     if (stage_raw_) cudaFree(stage_raw_);
     if (stage_f32_) cudaFree(stage_f32_);
+    for (cudaEvent_t e : head_ev_)
+      if (e) cudaEventDestroy(e);
+    if (copy_stream_) cudaStreamDestroy(copy_stream_);
     if (ev0_) cudaEventDestroy(ev0_);
     if (ev1_) cudaEventDestroy(ev1_);
     for (cudaEvent_t e : prof_pool_) cudaEventDestroy(e);
@@ -187,6 +190,12 @@ class Model final : public ModelBase {
   int ordinal_;
   OrionModelDesc d_;
   cudaStream_t stream_ = nullptr;
+  // LM head in column blocks with the download of block i overlapping the computation of i + 1
+  static constexpr int kHeadChunks = 4;
+  cudaStream_t copy_stream_ = nullptr;
+  cudaEvent_t head_ev_[kHeadChunks] = {};
+  uint32_t head_off_[kHeadChunks] = {}, head_cols_[kHeadChunks] = {};
+  int head_chunks_ = 0;
   cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
   std::vector<void *> allocs_;
   ParallelLayout lay_;
@@ -252,6 +261,8 @@ int Model<T>::init() {
 
   ORION_CUDA_CHECK("set device", cudaSetDevice(ordinal_));
   ORION_CUDA_CHECK("create stream", cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+  ORION_CUDA_CHECK("create stream", cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
+  for (cudaEvent_t &e : head_ev_) ORION_CUDA_CHECK("create event", cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   ORION_CUDA_CHECK("create event", cudaEventCreate(&ev0_));
   ORION_CUDA_CHECK("create event", cudaEventCreate(&ev1_));
 
@@ -729,6 +740,23 @@ int Model<T>::run_step(bool want_argmax) {
   if (meta_.zero_count) return ORION_OK;
   GemmPlan hp = gemm_plan(kBf16, S, d.vocab_size, H, H, H);
   hp.splits = hp.out_slabs = 1, hp.cluster_reduce = false;  // logits are written in place, row-major [S][V]
+  head_chunks_ = 0;
+  if (kBf16 && hp.tensor_core && d.vocab_size >= 4 * 8192 && !want_argmax) {
+    // A large vocabulary goes out in column blocks, an event after each: forward() copies block i
+    // to the host (copy engine, second stream) while block i + 1 is being computed.
+    const uint32_t per = (((d.vocab_size + 127) / 128 + kHeadChunks - 1) / kHeadChunks) * 128;
+    for (uint32_t c = 0; c < (uint32_t)kHeadChunks && c * per < d.vocab_size; ++c) {
+      const uint32_t n0 = c * per, nn = std::min(per, d.vocab_size - n0);
+      GemmPlan cp = hp;
+      cp.ldc = d.vocab_size;
+      ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(tail_, H, lm_head_ + (size_t)n0 * H, H, logits_ + n0, S, nn, H, cp, stream_); }));
+      ORION_CUDA_CHECK("lm head", cudaEventRecord(head_ev_[c], stream_));
+      head_off_[c] = n0;
+      head_cols_[c] = nn;
+      head_chunks_ = c + 1;
+    }
+    return ORION_OK;
+  }
   ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(tail_, H, lm_head_, H, logits_, S, d.vocab_size, H, hp, stream_); }));
   if (want_argmax) ORION_TRY(timed(kProfElementwise, [&] { return launch_argmax(logits_, S, d.vocab_size, argmax_, stream_); }));
   return ORION_OK;
@@ -898,9 +926,19 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
   if (d.tp_world > 1 && d.tp_rank != 0) {  // only the leader returns logits (Rank::is_leader)
     ORION_CUDA_CHECK("forward", cudaStreamSynchronize(stream_));
   } else {
-    if (logits_out)
+    if (logits_out && head_chunks_ > 0) {
+      const size_t pitch = (size_t)d.vocab_size * sizeof(float);
+      for (int c = 0; c < head_chunks_; ++c) {  // block c leaves while the blocks after it are computed
+        ORION_CUDA_CHECK("download logits", cudaStreamWaitEvent(copy_stream_, head_ev_[c], 0));
+        ORION_CUDA_CHECK("download logits", cudaMemcpy2DAsync(logits_out + head_off_[c], pitch, logits_ + head_off_[c], pitch,
+                                                              (size_t)head_cols_[c] * sizeof(float), S, cudaMemcpyDeviceToHost,
+                                                              copy_stream_));
+      }
+      ORION_CUDA_CHECK("download logits", cudaStreamSynchronize(copy_stream_));
+    } else if (logits_out) {
       ORION_CUDA_CHECK("download logits", cudaMemcpyAsync(logits_out, logits_, S * (size_t)d.vocab_size * sizeof(float),
                                                           cudaMemcpyDeviceToHost, stream_));
+    }
     if (token_ids_out)
       ORION_CUDA_CHECK("download tokens", cudaMemcpyAsync(token_ids_out, argmax_, S * sizeof(uint32_t),
                                                           cudaMemcpyDeviceToHost, stream_));

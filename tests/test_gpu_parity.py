@@ -504,6 +504,34 @@ def test_mixed_batch_with_a_run_of_decode_rows(pkg, backend, oracle, decodes_fir
     assert pkg.validate("kv_arena", kv_ref, kv_dev, pkg.Tolerance(0.1, 0.1)).passed()
 
 
+def test_large_vocabulary_head_goes_out_in_column_blocks(pkg, backend, oracle):
+    """From 32768 vocabulary entries on, forward() computes the LM head in four column blocks and
+    copies each to the host while the next is computed; the logits must be those of one GEMM."""
+    meta_d = dict(hidden_size=128, num_layers=1, num_attention_heads=2, num_kv_heads=1, head_dim=64,
+                  vocab_size=40004, ffn_dim=256, max_position_embeddings=64, rope_theta=10000.0,
+                  rms_norm_eps=1e-5, has_qkv_bias=False, tied_lm_head=False, num_blocks=8, block_size=16)
+    t = {k: (oracle.round_to_bf16(v) if v.ndim == 2 else v)
+         for k, v in random_tensors(np.random.default_rng(3), meta_d, std=0.05).items()}
+    ref = oracle.Model(**meta_d).load(t)
+    meta = pkg.ModelMetadata(architecture="llama", name="v",
+                             **{k: v for k, v in meta_d.items() if k not in ("num_blocks", "block_size")})
+    dev = pkg.CudaTransformerModel.new(meta, t, 8, 16, backend, compute_dtype=pkg.DType.BF16,
+                                       max_batch_tokens=64, max_batch_sequences=4)
+    toks, pos = [5, 9, 40003, 1, 7, 8, 2], [0, 1, 2, 0, 1, 2, 3]
+    counts, ctx, tabs = [3, 4], [3, 4], [[2], [5]]
+    oracle.set_threads(8)
+    exp = ref.forward(oracle.Batch(toks, pos, counts, ctx, tabs))
+    oracle.set_threads(1)
+    batch = pkg.ForwardBatch(toks, pos, [1, 2], counts, ctx, tabs, has_prefill=True)
+    got = dev.forward(batch).logits
+    assert got.shape == (2, 40004)
+    assert float(np.max(np.abs(softmax_rows(got) - softmax_rows(exp)))) < BF16_SOFTMAX
+    assert rel_err(got, exp) < 3e-2
+    ids, again = dev.forward_greedy(batch, want_logits=True)  # the one-GEMM path, same numbers
+    assert np.array_equal(again, got)
+    assert ids.tolist() == [int(np.argmax(r)) for r in got]
+
+
 def test_qwen2_shape_with_qkv_bias(pkg, backend, oracle):
     meta_d = dict(SMALL_META, hidden_size=128, head_dim=64, num_attention_heads=4, num_kv_heads=2,
                   ffn_dim=256, vocab_size=300, has_qkv_bias=True, num_blocks=16, block_size=16,
