@@ -122,6 +122,14 @@ typedef struct OrionModelDesc {
 int orion_cuda_model_create(OrionBackend *backend, const OrionModelDesc *desc, OrionModel **out);
 void orion_cuda_model_destroy(OrionModel *model);
 
+/* Failure-detection self-test (no reference counterpart): every device-side wait of this library
+ * gives up after a time limit, records an error word and lets its kernel finish, which the host
+ * reports as EngineError::Backend. This entry point runs the same bounded wait on a barrier that
+ * nothing ever arrives at, with a limit of `limit_us` (1 .. 1 000 000): it must come back with
+ * *timed_out = 1 after about that long, and the device must stay usable. */
+int orion_cuda_selftest_bounded_wait(OrionBackend *backend, uint64_t limit_us, uint32_t *timed_out,
+                                     uint32_t *waited_us);
+
 /* CheckpointLoader::open + ModelWeights::load for a whole directory
  * (crates/orion-models/src/loader.rs:112-235, transformer.rs:62-120,180-205): every
  * `*.safetensors` file in name order (the first file wins for a duplicated tensor name),

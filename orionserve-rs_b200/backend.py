@@ -54,5 +54,12 @@ class CudaBackend:
     def synchronize(self) -> None:
         check(_ffi.lib().orion_cuda_backend_synchronize(self._h))
 
+    def selftest_bounded_wait(self, limit_us: int):
+        """Runs a device wait that can never complete with a limit of ``limit_us``; returns
+        ``(timed_out, waited_us)``. The wait must give up and leave the device usable."""
+        t, w = C.c_uint32(), C.c_uint32()
+        check(_ffi.lib().orion_cuda_selftest_bounded_wait(self._h, limit_us, C.byref(t), C.byref(w)))
+        return bool(t.value), int(w.value)
+
     def supports_dtype(self, dtype: DType) -> bool:
         return bool(_ffi.lib().orion_cuda_backend_supports_dtype(self._h, int(dtype)))

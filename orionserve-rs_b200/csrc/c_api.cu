@@ -393,6 +393,12 @@ int orion_cuda_model_forward(OrionModel *model, const uint32_t *tokens, uint64_t
                                          logits_out, logits_capacity);
 }
 
+int orion_cuda_selftest_bounded_wait(OrionBackend *backend, uint64_t limit_us, uint32_t *timed_out, uint32_t *waited_us) {
+  clear_error();
+  ORION_TRY(check_backend(backend));
+  return selftest_bounded_wait(limit_us, timed_out, waited_us);
+}
+
 int orion_cuda_model_load_checkpoint(OrionModel *model, const char *directory, uint64_t *tensors_loaded) {
   clear_error();
   if (!model) return set_error(ORION_ERR_INVALID_REQUEST, "null model handle");

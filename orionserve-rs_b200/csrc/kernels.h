@@ -209,6 +209,9 @@ int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, c
                                          size_t split_stride, float *hidden, const float *norm_w, float eps, T *out,
                                          uint32_t rows, uint32_t hidden_size, bool two_shot, cudaStream_t stream);
 int tp_poll_error(uint32_t *code);
+// Launches a kernel whose only thread waits on a barrier that nothing arrives at, with the given
+// limit: the bounded wait must give up (timed_out = 1) and the kernel must end normally.
+int selftest_bounded_wait(uint64_t limit_us, uint32_t *timed_out, uint32_t *waited_us);
 
 // ---- GEMM ----------------------------------------------------------------------
 

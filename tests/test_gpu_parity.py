@@ -42,6 +42,17 @@ def test_backend_reports_the_device(pkg, backend):
         pkg.CudaBackend(pkg.device_count())
 
 
+def test_a_device_wait_that_cannot_complete_gives_up_and_the_device_stays_usable(pkg, backend):
+    """Failure detection without a fault: the bounded wait every kernel uses, on a barrier that
+    nothing arrives at, with a 20 ms limit. It reports the time-out instead of spinning forever."""
+    timed_out, waited_us = backend.selftest_bounded_wait(20_000)
+    assert timed_out and 20_000 <= waited_us < 200_000
+    backend.synchronize()
+    assert np.array_equal(pkg.ops.argmax(backend, np.array([[1.0, 3.0, 2.0]], np.float32)), [1])
+    with pytest.raises(pkg.InvalidRequest):
+        backend.selftest_bounded_wait(0)
+
+
 # ---- op-level parity: tensor.rs ---------------------------------------------------
 
 def test_linear_f32_is_bit_exact(pkg, backend, oracle, kats):
