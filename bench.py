@@ -30,6 +30,9 @@ LLAMA3_8B = dict(hidden_size=4096, num_layers=32, num_attention_heads=32, num_kv
 QWEN2_7B = dict(hidden_size=3584, num_layers=28, num_attention_heads=28, num_kv_heads=4, head_dim=128,
                 vocab_size=152064, ffn_dim=18944, max_position_embeddings=8192, rope_theta=1000000.0,
                 rms_norm_eps=1e-6, has_qkv_bias=True)
+LLAMA3_70B = dict(hidden_size=8192, num_layers=80, num_attention_heads=64, num_kv_heads=8, head_dim=128,
+                  vocab_size=128256, ffn_dim=28672, max_position_embeddings=8192, rope_theta=500000.0,
+                  rms_norm_eps=1e-5)
 BATCH, CONTEXT, BLOCK = 64, 1024, 16
 WORKLOAD = "llama3_8b_decode_batch64_ctx1024_bf16"
 METRIC = "decode tokens/s at batch 64 (Llama-3-8B shape)"
@@ -210,14 +213,22 @@ def run_reference(args):
 # GPU leg
 # ---------------------------------------------------------------------------------------------
 
-def make_decode_batch(pkg, rng, num_blocks):
-    perm = rng.permutation(num_blocks)
-    nblk = (CONTEXT + BLOCK - 1) // BLOCK
-    # the batch as contiguous host arrays, the form the reference's ForwardBatch vectors have
-    tables = np.ascontiguousarray(perm[:BATCH * nblk].reshape(BATCH, nblk), dtype=np.uint32)
-    tokens = rng.integers(0, LLAMA3_8B["vocab_size"], BATCH).astype(np.uint32)
-    return pkg.ForwardBatch(tokens, np.full(BATCH, CONTEXT - 1, np.uint32), np.arange(1, BATCH + 1, dtype=np.uint64),
-                            np.ones(BATCH, np.uint64), np.full(BATCH, CONTEXT, np.uint64), tables, has_prefill=False)
+def make_decode_batch(pkg, rng, num_blocks, contexts, vocab):
+    """One decode step: every sequence feeds one token at position context - 1; the block tables are
+    consecutive slices of one random permutation of the pool."""
+    perm = rng.permutation(num_blocks).astype(np.uint32)
+    n = len(contexts)
+    nblk = (np.asarray(contexts) + BLOCK - 1) // BLOCK
+    if int(nblk.min()) == int(nblk.max()):
+        # the batch as contiguous host arrays, the form the reference's ForwardBatch vectors have
+        tables = np.ascontiguousarray(perm[:n * int(nblk[0])].reshape(n, int(nblk[0])))
+    else:
+        ends = np.cumsum(nblk)
+        tables = [np.ascontiguousarray(perm[e - k:e]) for e, k in zip(ends, nblk)]
+    tokens = rng.integers(0, vocab, n).astype(np.uint32)
+    ctx = np.asarray(contexts, dtype=np.uint64)
+    return pkg.ForwardBatch(tokens, (ctx - 1).astype(np.uint32), np.arange(1, n + 1, dtype=np.uint64),
+                            np.ones(n, np.uint64), ctx, tables, has_prefill=False)
 
 
 def attention_sweep(pkg, backend, peak):
@@ -333,19 +344,33 @@ def run_ours(args):
         pkg._ffi.lib().orion_cuda_set_l2_prefetch_bytes(args.l2_prefetch_mb << 20)
     if args.gemm_ctas or args.gemm_stages:
         pkg._ffi.lib().orion_cuda_gemm_set_tuning(args.gemm_ctas, args.gemm_stages)
-    m = dict(LLAMA3_8B, num_layers=args.layers)
-    meta = pkg.ModelMetadata(architecture="llama", name="llama3-8b-shape", dtype=pkg.DType.BF16, **m)
-    num_blocks = BATCH * (CONTEXT // BLOCK + 1) + 64
+    rng = np.random.default_rng(3)
+    if args.shape == "llama3-70b":
+        # the fifth configuration of the benchmark definition (not the headline): Llama-3-70B shape under
+        # tensor parallelism, decode at batch 128, contexts uniform in [1024, 4096]
+        full_layers = LLAMA3_70B["num_layers"]
+        layers = full_layers if args.layers == 32 else args.layers
+        m = dict(LLAMA3_70B, num_layers=layers)
+        contexts = [int(c) for c in np.random.default_rng(5).integers(1024, 4097, 128)]
+        name, metric = "llama3-70b-shape", "decode tokens/s at batch 128 (Llama-3-70B shape, tensor parallel)"
+        workload = "llama3_70b_decode_batch128_ctx1024to4096_bf16"
+    else:
+        full_layers, layers = 32, args.layers
+        m = dict(LLAMA3_8B, num_layers=layers)
+        contexts = [CONTEXT] * BATCH
+        name, metric, workload = "llama3-8b-shape", METRIC, WORKLOAD
+    nbatch = len(contexts)
+    meta = pkg.ModelMetadata(architecture="llama", name=name, dtype=pkg.DType.BF16, **m)
+    num_blocks = sum(c // BLOCK + 1 for c in contexts) + 64
     model = pkg.CudaTransformerModel(meta, num_blocks, BLOCK, backend, compute_dtype=pkg.DType.BF16,
-                                     max_batch_tokens=BATCH, max_batch_sequences=BATCH, tp_rank=rank,
+                                     max_batch_tokens=nbatch, max_batch_sequences=nbatch, tp_rank=rank,
                                      tp_world=world, nccl_unique_id=nccl_id)
     model.init_random(seed=1, std=0.02)
     model.fill_kv_random(seed=2, std=1.0)
-    rng = np.random.default_rng(3)
-    batch = make_decode_batch(pkg, rng, num_blocks)
+    batch = make_decode_batch(pkg, rng, num_blocks, contexts, m["vocab_size"])
     from orionserve_rs_b200.model import pinned_empty
 
-    logits, owner = pinned_empty(BATCH * m["vocab_size"])
+    logits, owner = pinned_empty(nbatch * m["vocab_size"])
 
     def barrier():
         backend.synchronize()
@@ -400,35 +425,37 @@ def run_ours(args):
         return 0
 
     ms_per_step = dev_ms / args.steps
-    value = BATCH / (ms_per_step / 1000.0)
-    e2e_value = BATCH * args.steps / e2e_s
+    value = nbatch / (ms_per_step / 1000.0)
+    e2e_value = nbatch * args.steps / e2e_s
     peak, peak_src = measured_peaks()
     gemm_ms, gemm_n = prof["gemm"]
     attn_ms, attn_n = prof["attention"]
     wbytes = weight_bytes_per_step(m, world)
-    kbytes = kv_bytes_per_step(m, [CONTEXT] * BATCH, world)
+    kbytes = kv_bytes_per_step(m, contexts, world)
     gemm_gbs = wbytes * args.steps / (gemm_chain_ms / 1000.0) / 1e9
     attn_gbs = kbytes * args.steps / (attn_chain_ms / 1000.0) / 1e9
     gemm_gbs_serial = wbytes * args.steps / (gemm_ms / 1000.0) / 1e9 if gemm_ms > 0 else None
     attn_gbs_serial = kbytes * args.steps / (attn_ms / 1000.0) / 1e9 if attn_ms > 0 else None
-    meta_bytes = 4 * (5 * BATCH + 2 * BATCH + 1 + sum(len(t) for t in batch.block_tables))
+    meta_bytes = 4 * (5 * nbatch + 2 * nbatch + 1 + sum(len(t) for t in batch.block_tables))
     line = {
-        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD if args.layers == 32 else f"{WORKLOAD}_first{args.layers}layers",
-                   "batch": BATCH, "context": CONTEXT, "block_size": BLOCK, "layers": args.layers,
-                   "parallelism": f"tp{world}", "l2": "inputs exceed L2: 15.0 GB of weights + 8.6 GB of KV read per step"},
+        "config": {"workload": workload if layers == full_layers else f"{workload}_first{layers}layers",
+                   "batch": nbatch, "context": CONTEXT if args.shape == "llama3-8b" else "U[1024,4096]",
+                   "block_size": BLOCK, "layers": layers, "parallelism": f"tp{world}",
+                   "l2": f"inputs exceed L2: {wbytes / 1e9:.1f} GB of weights + {kbytes / 1e9:.1f} GB of KV read "
+                         f"per step and rank"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes,
-                "d2h_bytes_per_step": BATCH * m["vocab_size"] * 4},
-        "e2e_greedy": {"value": BATCH * args.steps / greedy_s, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes,
-                       "d2h_bytes_per_step": BATCH * 4,
+                "d2h_bytes_per_step": nbatch * m["vocab_size"] * 4},
+        "e2e_greedy": {"value": nbatch * args.steps / greedy_s, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes,
+                       "d2h_bytes_per_step": nbatch * 4,
                        "note": "forward_greedy: host batch in, argmax on the device, 4 bytes per sequence out"},
         "gpu_launches": int(launches_per_step * args.steps),
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel (projection weights streamed once per step)",
                      "achieved": gemm_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                     "frac": gemm_gbs / peak, "traffic": GEMM_TRAFFIC_BYTES_PER_STEP if world == 1 and args.layers == 32 else None,
+                     "frac": gemm_gbs / peak, "traffic": GEMM_TRAFFIC_BYTES_PER_STEP if world == 1 and args.layers == 32 and args.shape == "llama3-8b" else None,
                      "algorithmic_bytes_per_step": wbytes, "launches_per_step": gemm_n // max(args.steps, 1),
                      "ms_per_step": gemm_chain_ms / args.steps,
                      "timing": "CUDA events around the step's projection launches run back to back on the launch "
@@ -453,7 +480,7 @@ def run_ours(args):
     }
     if world == 1 and not args.no_attention_sweep:
         line["attention_microbench"] = attention_sweep(pkg, backend, peak)
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and args.shape == "llama3-8b":
         from oracle import binding as oracle
 
         oracle.build()
@@ -481,6 +508,9 @@ def main():
     ap.add_argument("--skip-cached-prefix", action="store_true",
                     help="engine workloads: start prefill after the tokens adopted from the prefix cache "
                          "(an extension; the reference shares the blocks but recomputes them)")
+    ap.add_argument("--shape", choices=("llama3-8b", "llama3-70b"), default="llama3-8b",
+                    help="decode workload: llama3-8b = the headline (batch 64, 1k contexts); llama3-70b = batch 128, "
+                         "contexts U[1024,4096], meant for --gpus 2..8 (141 GB of weights)")
     ap.add_argument("--requests", type=int, default=256, help="requests of the serving workload")
     ap.add_argument("--layers", type=int, default=32,
                     help="layers of the Llama-3-8B shape to build; fewer than 32 gives a small case with the "

@@ -543,6 +543,45 @@ def test_large_vocabulary_head_goes_out_in_column_blocks(pkg, backend, oracle):
     assert ids.tolist() == [int(np.argmax(r)) for r in got]
 
 
+def test_llama3_70b_layer_as_one_of_eight_tensor_parallel_ranks_sees(pkg, backend, oracle):
+    """One layer with the shapes a rank holds when Llama-3-70B is split eight ways
+    (`ParallelLayout::compute`, distributed/lib.rs:174-208): hidden 8192, 8 query heads on 1 KV head,
+    ffn 3584. Prefill of nine short prompts, then two decode steps on the tuned kernels."""
+    meta_d = dict(hidden_size=8192, num_layers=1, num_attention_heads=8, num_kv_heads=1, head_dim=128,
+                  vocab_size=512, ffn_dim=3584, max_position_embeddings=256, rope_theta=500000.0,
+                  rms_norm_eps=1e-5, has_qkv_bias=False, tied_lm_head=False, num_blocks=40, block_size=16)
+    t = {k: (oracle.round_to_bf16(v) if v.ndim == 2 else v)
+         for k, v in random_tensors(np.random.default_rng(70), meta_d, std=0.02).items()}
+    ref = oracle.Model(**meta_d).load(t)
+    meta = pkg.ModelMetadata(architecture="llama", name="r",
+                             **{k: v for k, v in meta_d.items() if k not in ("num_blocks", "block_size")})
+    dev = pkg.CudaTransformerModel.new(meta, t, 40, 16, backend, compute_dtype=pkg.DType.BF16,
+                                       max_batch_tokens=256, max_batch_sequences=16)
+    rng = np.random.default_rng(7)
+    lens = [21, 16, 30, 9, 17, 25, 12, 31, 20]
+    prompts = [rng.integers(0, 512, n).tolist() for n in lens]
+    perm = rng.permutation(40).tolist()
+    tables = [[perm.pop() for _ in range((n + 2 + 15) // 16)] for n in lens]
+    ids = list(range(1, 10))
+    oracle.set_threads(8)
+    toks = [x for p in prompts for x in p]
+    pos = [i for n in lens for i in range(n)]
+    exp = ref.forward(oracle.Batch(toks, pos, lens, lens, tables))
+    got = dev.forward(pkg.ForwardBatch(toks, pos, ids, lens, lens, tables, has_prefill=True)).logits
+    assert float(np.max(np.abs(softmax_rows(got) - softmax_rows(exp)))) < BF16_SOFTMAX
+    assert rel_err(got, exp) < 3e-2
+    last = [int(oracle.argmax(r)) for r in exp]
+    for step in range(2):
+        pos = [n + step for n in lens]
+        ctx = [p + 1 for p in pos]
+        exp = ref.forward(oracle.Batch(last, pos, [1] * 9, ctx, tables))
+        got = dev.forward(pkg.ForwardBatch(last, pos, ids, [1] * 9, ctx, tables, has_prefill=False)).logits
+        assert float(np.max(np.abs(softmax_rows(got) - softmax_rows(exp)))) < BF16_SOFTMAX, f"decode step {step}"
+        assert rel_err(got, exp) < 3e-2, f"decode step {step}"
+        last = [int(oracle.argmax(r)) for r in exp]
+    oracle.set_threads(1)
+
+
 def test_qwen2_shape_with_qkv_bias(pkg, backend, oracle):
     meta_d = dict(SMALL_META, hidden_size=128, head_dim=64, num_attention_heads=4, num_kv_heads=2,
                   ffn_dim=256, vocab_size=300, has_qkv_bias=True, num_blocks=16, block_size=16,
