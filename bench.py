@@ -357,8 +357,11 @@ def run_ours(args):
     else:
         full_layers, layers = 32, args.layers
         m = dict(LLAMA3_8B, num_layers=layers)
-        contexts = [CONTEXT] * BATCH
+        contexts = [CONTEXT] * args.batch
         name, metric, workload = "llama3-8b-shape", METRIC, WORKLOAD
+        if args.batch != BATCH:  # not the headline: the same step at another batch size
+            metric = f"decode tokens/s at batch {args.batch} (Llama-3-8B shape)"
+            workload = f"llama3_8b_decode_batch{args.batch}_ctx1024_bf16"
     nbatch = len(contexts)
     meta = pkg.ModelMetadata(architecture="llama", name=name, dtype=pkg.DType.BF16, **m)
     num_blocks = sum(c // BLOCK + 1 for c in contexts) + 64
@@ -455,7 +458,8 @@ def run_ours(args):
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel (projection weights streamed once per step)",
                      "achieved": gemm_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                     "frac": gemm_gbs / peak, "traffic": GEMM_TRAFFIC_BYTES_PER_STEP if world == 1 and args.layers == 32 and args.shape == "llama3-8b" else None,
+                     "frac": gemm_gbs / peak, "traffic": GEMM_TRAFFIC_BYTES_PER_STEP
+                     if world == 1 and args.layers == 32 and args.shape == "llama3-8b" and args.batch == BATCH else None,
                      "algorithmic_bytes_per_step": wbytes, "launches_per_step": gemm_n // max(args.steps, 1),
                      "ms_per_step": gemm_chain_ms / args.steps,
                      "timing": "CUDA events around the step's projection launches run back to back on the launch "
@@ -480,7 +484,7 @@ def run_ours(args):
     }
     if world == 1 and not args.no_attention_sweep:
         line["attention_microbench"] = attention_sweep(pkg, backend, peak)
-    if world == 1 and not args.no_cpu_baseline and args.shape == "llama3-8b":
+    if world == 1 and not args.no_cpu_baseline and args.shape == "llama3-8b" and args.batch == BATCH:
         from oracle import binding as oracle
 
         oracle.build()
@@ -511,6 +515,8 @@ def main():
     ap.add_argument("--shape", choices=("llama3-8b", "llama3-70b"), default="llama3-8b",
                     help="decode workload: llama3-8b = the headline (batch 64, 1k contexts); llama3-70b = batch 128, "
                          "contexts U[1024,4096], meant for --gpus 2..8 (141 GB of weights)")
+    ap.add_argument("--batch", type=int, default=BATCH,
+                    help="sequences of the llama3-8b decode step; anything but 64 is not the headline")
     ap.add_argument("--requests", type=int, default=256, help="requests of the serving workload")
     ap.add_argument("--layers", type=int, default=32,
                     help="layers of the Llama-3-8B shape to build; fewer than 32 gives a small case with the "

@@ -480,6 +480,11 @@ uint32_t prefill_weight_tiles(uint32_t rows, uint32_t n) {
   return ((n + kTileN - 1) / kTileN) * ((rows + 255) / 256) >= 296 ? 2 : 1;
 }
 int g_small_stages = 5;  // 5: deep weight ring + short activation ring for decode batches; 4: equal rings
+// Batches of 65..128 rows: 0 (default) = 4 weight + 2 activation stages, 96 KiB, two CTAs per SM like the
+// smaller tiles (the split-K planner counts on two); 1 = 6 + 6 stages, 192 KiB, one CTA per SM, k splits
+// sized for one wave of 148; 2 = the same tile with k splits sized for 296 CTAs, also for 129..256 rows
+// (two waves of uneven length). ORION_GEMM_MID_TILE overrides (tuning A/B).
+int g_mid_tile = std::getenv("ORION_GEMM_MID_TILE") ? std::atoi(std::getenv("ORION_GEMM_MID_TILE")) : 0;
 
 uint32_t token_tile(uint32_t rows) {
   if (rows <= 16) return 16;
@@ -522,7 +527,10 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
     case 64:
       return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
                   : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
-    case 128: return launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
+    case 128:
+      return g_mid_tile == 0
+                 ? launch_tc<128, 4, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
+                 : launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
     default:
       if (rows > 256 && !cluster_reduce && prefill_weight_tiles(rows, n) == 2)
         return launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
@@ -603,7 +611,9 @@ GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t
   }
   const uint32_t tiles = ((n + kTileN - 1) / kTileN) * ((rows + token_tile(rows) - 1) / token_tile(rows));
   const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
-  uint32_t s = g_target_ctas / (tiles ? tiles : 1);
+  // the 256-token tile (and the 6 + 6 stage 128-token one) fills an SM by itself: one wave is 148 CTAs
+  const bool one_per_sm = g_mid_tile != 2 && (token_tile(rows) == 256 || (token_tile(rows) == 128 && g_mid_tile == 1));
+  uint32_t s = (one_per_sm ? g_target_ctas / 2 : g_target_ctas) / (tiles ? tiles : 1);
   const uint32_t cap = nkb / 4 ? nkb / 4 : 1;  // at least four k slabs per split
   if (s > cap) s = cap;
   if (s > 16) s = 16;

@@ -157,6 +157,7 @@ class Model final : public ModelBase {
   uint32_t *tp_inbox_ = nullptr;  // where the peers push their partial sums (peer-mapped)
   uint32_t tp_epoch_ = 1;
   bool tp_fused_ = false;
+  bool tp_two_shot_ = false;
   std::vector<void *> ipc_opened_;
   // Per-launch event pairs of a profiled step, resolved after the stream drains.
   struct ProfRec { int cat; cudaEvent_t a, b; };
@@ -339,9 +340,11 @@ int Model<T>::init() {
     // Peer-memory hand-over (one kernel: all-reduce + residual + norm): one-shot at 2 ranks (every
     // partial sum to the peer: 4.01 vs 4.53 ms per headline step through NCCL), two-shot beyond
     // (one-shot is bandwidth-bound there: 4.29 vs 3.98 ms at 4 ranks, 6.10 vs 4.09 ms at 8).
-    // ORION_TP_ALLREDUCE=fused / nccl forces either path.
+    // ORION_TP_ALLREDUCE=fused / nccl forces either path; twoshot = fused, with the two-shot kernel
+    // at 2 ranks as well (so that a 2-GPU machine can exercise it).
     const char *mode = std::getenv("ORION_TP_ALLREDUCE");
-    const bool want_fused = mode ? !strcmp(mode, "fused") : true;
+    const bool want_fused = mode ? (!strcmp(mode, "fused") || !strcmp(mode, "twoshot")) : true;
+    tp_two_shot_ = d.tp_world > 2 || (mode && !strcmp(mode, "twoshot"));
     if (want_fused && d.tp_world <= (uint32_t)kMaxTpWorld && H % 4 == 0 && H / 4 <= 4096)
       ORION_TRY(setup_peer_handover());
   }
@@ -620,7 +623,7 @@ int Model<T>::handover(uint32_t splits, const float *norm_w, T *out, const uint3
   if (nccl_ && tp_fused_ && Tn <= kTpFusedMaxRows) {
     // every rank ends up with the whole residual stream and all Tn normalised rows
     ORION_TRY(launch_tp_allreduce_residual_rmsnorm<T>(peers_, tp_epoch_, partial_, splits, slab, hidden_, norm_w,
-                                                      d_.rms_norm_eps, normed_, Tn, H, d_.tp_world > 2, stream_));
+                                                      d_.rms_norm_eps, normed_, Tn, H, tp_two_shot_, stream_));
     tp_epoch_ = tp_epoch_ == 0xFFFFFFFEu ? 1u : tp_epoch_ + 1;
     if (row_map) return launch_gather_rows<T>(normed_, row_map, out, out_rows, H, stream_);
     if (out != normed_) return set_error(ORION_ERR_INTERNAL, "fused hand-over writes the activation buffer only");

@@ -63,6 +63,47 @@ __device__ __forceinline__ float4 receive4(const uint32_t *src, uint32_t epoch) 
   return make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x), __uint_as_float(hi.z));
 }
 
+// A group of four elements as the two-shot kernel sends it. Wide: four {f32, epoch} units (32 bytes at
+// word offset 2 x element). Packed: two {bf16 pair, epoch} units (16 bytes at word offset = element),
+// the bf16 payload with f32 accumulation that orion-distributed/src/lib.rs:317-319 has in mind.
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&p);
+}
+__device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&u));
+}
+template <bool Packed>
+__device__ __forceinline__ void send_group(uint32_t *base, size_t element, float4 v, uint32_t epoch) {
+  if (Packed) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(base + element), "r"(pack_bf16x2(v.x, v.y)),
+                 "r"(epoch), "r"(pack_bf16x2(v.z, v.w)), "r"(epoch)
+                 : "memory");
+  } else {
+    st_unit2(base + element * 2, v.x, v.y, epoch);
+    st_unit2(base + element * 2 + 4, v.z, v.w, epoch);
+  }
+}
+template <bool Packed>
+__device__ __forceinline__ float4 receive_group(const uint32_t *base, size_t element, uint32_t epoch) {
+  if (!Packed) return receive4(base + element * 2, epoch);
+  const uint32_t *src = base + element;
+  uint4 u = ld_unit2(src);
+  if (u.y != epoch || u.w != epoch) {
+    const uint64_t start = global_timer_ns();
+    uint32_t spins = 0;
+    do {
+      u = ld_unit2(src);
+      if ((++spins & 1023u) == 0 && global_timer_ns() - start > 2000000000ull) {
+        atomicOr(&g_tp_error, 1u);
+        break;
+      }
+    } while (u.y != epoch || u.w != epoch);
+  }
+  const float2 lo = unpack_bf16x2(u.x), hi = unpack_bf16x2(u.z);
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
 template <typename T>
 __device__ __forceinline__ void st_row4(T *dst, float4 v);
 template <>
@@ -168,16 +209,22 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
   trace(3);
 }
 
-// Two-shot variant for more than two ranks. Row r belongs to rank r / ceil(rows / world). Every
-// rank folds its split-K slabs for every row and pushes the sums of a row to the row's owner only
-// (reduce-scatter); the owner adds them in rank order, updates its residual row, normalises it
-// and pushes the normalised row to every peer (all-gather). Both pushes use the self-validating
-// 8-byte units of the one-shot kernel, so there is still no barrier and no fence; a rank now
-// sends rows x H x 8 B once instead of world - 1 times, and only the owner keeps a row's
-// residual current (each rank's rows are the same for every hand-over of a step).
-// Inbox of a rank: [parity 2][sender world][slot] units for the reduce-scatter, then
-// [parity 2][slot] units for the all-gather. One CTA per row, on every rank.
-template <typename T, typename Acc>
+// Two-shot variant for more than two ranks. One CTA per row on every rank; inside a row the
+// four-float groups are dealt to the ranks in contiguous slices, and a rank owns its slice of
+// EVERY row, so all CTAs of all ranks send and receive the same amount in both phases (with rows
+// owned whole, only the owner's few CTAs would publish, and a handful of SMs cannot fill NVLink).
+//   reduce-scatter: a thread pushes the folded sums of the groups it does not own to their owners;
+//   reduce:         for a group it owns it collects the peers' sums, adds them in rank order and
+//   all-gather:     pushes the total to every peer;
+//   every thread then has the total of each of its groups (its own or received), adds it to the
+//   residual (all ranks add identical totals, so the residual streams stay bit-identical) and the
+//   CTA normalises the row.
+// Both pushes use the self-validating 8-byte units of the one-shot kernel: no barrier, no fence.
+// All pushes of a phase are issued before any poll of the next, so a thread never waits for data
+// whose sender waits for this thread. A rank sends rows x H x 8 B x (world-1)/world twice instead
+// of world - 1 times. Inbox of a rank: [parity 2][sender world][slot] units for the
+// reduce-scatter, then [parity 2][slot] units for the all-gather, both addressed by (row, element).
+template <typename T, typename Acc, bool Packed>
 __global__ void __launch_bounds__(1024)
 tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ partial, uint32_t splits,
                   size_t split_stride, float *__restrict__ hidden, const float *__restrict__ w, float eps,
@@ -186,43 +233,50 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
   pdl_trigger();
   pdl_wait();  // this rank's projection has finished
   trace(0);
+  (void)rows;
   const uint32_t nvec = H / 4, row = blockIdx.x;
-  const uint32_t per = (rows + peers.world - 1) / peers.world;
-  const int owner = (int)(row / per);
-  const size_t slot = (size_t)peers.slot_floats * 2;  // u32 words per slot
-  const size_t scatter = ((size_t)(epoch & 1u) * peers.world) * slot;               // + sender * slot
+  const uint32_t per = (nvec + peers.world - 1) / peers.world;  // groups per owner
+  const size_t slot = (size_t)peers.slot_floats * 2;            // u32 words per slot
+  const size_t scatter = ((size_t)(epoch & 1u) * peers.world) * slot;  // + sender * slot
   const size_t gather = (size_t)2 * peers.world * slot + (size_t)(epoch & 1u) * slot;
   float4 v[4];  // H / 4 <= 4 * blockDim.x is guaranteed by the launcher
+  // ---- fold the local split-K slabs; hand the groups of other owners over ----
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const uint32_t idx = threadIdx.x + c * blockDim.x;
-    if (idx < nvec) v[c] = sum_slabs_local(partial + (size_t)row * H + 4 * (size_t)idx, splits, split_stride);
-  }
-  if (peers.rank != owner) {
-    // ---- not the owner: hand the sums over, then wait for the normalised row ----
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const uint32_t idx = threadIdx.x + c * blockDim.x;
-      if (idx < nvec) {
-        uint32_t *dst = peers.inbox[owner] + scatter + (size_t)peers.rank * slot + ((size_t)row * H + 4 * (size_t)idx) * 2;
-        st_unit2(dst, v[c].x, v[c].y, epoch);
-        st_unit2(dst + 4, v[c].z, v[c].w, epoch);
-      }
+    if (idx < nvec) {
+      const size_t off = (size_t)row * H + 4 * (size_t)idx;
+      v[c] = sum_slabs_local(partial + off, splits, split_stride);
+      const int owner = (int)(idx / per);
+      if (owner != peers.rank)
+        send_group<Packed>(peers.inbox[owner] + scatter + (size_t)peers.rank * slot, off, v[c], epoch);
     }
-    trace(1);
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const uint32_t idx = threadIdx.x + c * blockDim.x;
-      if (idx < nvec) {
-        const size_t off = (size_t)row * H + 4 * (size_t)idx;
-        st_row4<T>(out + off, receive4(peers.inbox[peers.rank] + gather + off * 2, epoch));
-      }
-    }
-    trace(3);
-    return;
   }
-  // ---- the owner: collect, add in rank order, residual, norm, publish ----
   trace(1);
+  // ---- own groups: collect, add in rank order, publish the totals ----
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t idx = threadIdx.x + c * blockDim.x;
+    if (idx < nvec && (int)(idx / per) == peers.rank) {
+      const size_t off = (size_t)row * H + 4 * (size_t)idx;
+      float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < peers.world; ++r) {
+        const float4 x = r == peers.rank
+                             ? v[c]
+                             : receive_group<Packed>(peers.inbox[peers.rank] + scatter + (size_t)r * slot, off, epoch);
+        add.x += x.x; add.y += x.y; add.z += x.z; add.w += x.w;
+      }
+      if (Packed) {  // every rank must add exactly what the peers receive
+        const float2 lo = unpack_bf16x2(pack_bf16x2(add.x, add.y)), hi = unpack_bf16x2(pack_bf16x2(add.z, add.w));
+        add = make_float4(lo.x, lo.y, hi.x, hi.y);
+      }
+      v[c] = add;
+      for (int r = 0; r < peers.world; ++r)
+        if (r != peers.rank) send_group<Packed>(peers.inbox[r] + gather, off, add, epoch);
+    }
+  }
+  trace(2);
+  // ---- the other groups: receive the totals; residual update on every rank ----
   Acc ss = Acc(0);
   float *h = hidden + (size_t)row * H;
 #pragma unroll
@@ -230,12 +284,9 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
     const uint32_t idx = threadIdx.x + c * blockDim.x;
     if (idx < nvec) {
       const size_t off = (size_t)row * H + 4 * (size_t)idx;
-      float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r = 0; r < peers.world; ++r) {
-        const float4 x = r == peers.rank ? v[c]
-                                         : receive4(peers.inbox[peers.rank] + scatter + (size_t)r * slot + off * 2, epoch);
-        add.x += x.x; add.y += x.y; add.z += x.z; add.w += x.w;
-      }
+      const float4 add = (int)(idx / per) == peers.rank
+                             ? v[c]
+                             : receive_group<Packed>(peers.inbox[peers.rank] + gather, off, epoch);
       const float4 old = *reinterpret_cast<const float4 *>(h + 4 * (size_t)idx);
       v[c] = make_float4(old.x + add.x, old.y + add.y, old.z + add.z, old.w + add.w);
       *reinterpret_cast<float4 *>(h + 4 * (size_t)idx) = v[c];
@@ -243,7 +294,7 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
             (Acc)v[c].w * (Acc)v[c].w;
     }
   }
-  trace(2);
+  // ---- RMSNorm of the row (tensor.rs:143-163) ----
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
   __syncthreads();
@@ -255,17 +306,10 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
   for (int c = 0; c < 4; ++c) {
     const uint32_t idx = threadIdx.x + c * blockDim.x;
     if (idx < nvec) {
-      const size_t off = (size_t)row * H + 4 * (size_t)idx;
       const float4 g = *reinterpret_cast<const float4 *>(w + 4 * (size_t)idx);
-      const float4 o = make_float4(__fmul_rn(__fmul_rn(v[c].x, scale), g.x), __fmul_rn(__fmul_rn(v[c].y, scale), g.y),
-                                   __fmul_rn(__fmul_rn(v[c].z, scale), g.z), __fmul_rn(__fmul_rn(v[c].w, scale), g.w));
-      st_row4<T>(out + off, o);
-      for (int r = 0; r < peers.world; ++r)
-        if (r != peers.rank) {
-          uint32_t *dst = peers.inbox[r] + gather + off * 2;
-          st_unit2(dst, o.x, o.y, epoch);
-          st_unit2(dst + 4, o.z, o.w, epoch);
-        }
+      st_row4<T>(out + (size_t)row * H + 4 * (size_t)idx,
+                 make_float4(__fmul_rn(__fmul_rn(v[c].x, scale), g.x), __fmul_rn(__fmul_rn(v[c].y, scale), g.y),
+                             __fmul_rn(__fmul_rn(v[c].z, scale), g.z), __fmul_rn(__fmul_rn(v[c].w, scale), g.w)));
     }
   }
   trace(3);
@@ -285,10 +329,19 @@ int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, c
   uint32_t threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
   if (threads < 32) threads = 32;
   using Acc = typename std::conditional<sizeof(T) == 4, double, float>::type;
-  if (two_shot)
+  // ORION_TP_PAYLOAD=bf16|f32: what the two-shot kernel of the bf16 build sends (the f32 build always sends f32)
+  static const bool packed = [] {
+    const char *e = std::getenv("ORION_TP_PAYLOAD");
+    return e != nullptr && e[0] == 'b';
+  }();
+  if (two_shot && sizeof(T) == 2 && packed)
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
-                     launch_pdl(tp_twoshot_kernel<T, Acc>, dim3(rows), dim3(threads), 0, stream, peers, epoch, partial,
-                                splits, split_stride, hidden, norm_w, eps, out, rows, hidden_size));
+                     launch_pdl(tp_twoshot_kernel<T, Acc, true>, dim3(rows), dim3(threads), 0, stream, peers, epoch,
+                                partial, splits, split_stride, hidden, norm_w, eps, out, rows, hidden_size));
+  else if (two_shot)
+    ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
+                     launch_pdl(tp_twoshot_kernel<T, Acc, false>, dim3(rows), dim3(threads), 0, stream, peers, epoch,
+                                partial, splits, split_stride, hidden, norm_w, eps, out, rows, hidden_size));
   else
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
                      launch_pdl(tp_allreduce_residual_rmsnorm_kernel<T, Acc>, dim3(rows), dim3(threads), 0, stream, peers,

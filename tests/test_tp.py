@@ -21,7 +21,9 @@ def _run_ranks(world: int, *worker_args: str, timeout: int = 600, handover: str 
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(ROOT, "tests", "tp_worker.py"), *worker_args]
     env = dict(os.environ, OMP_NUM_THREADS="1", NCCL_NVLS_ENABLE="0")
-    if handover:  # "fused" = peer-memory all-reduce + residual + norm kernel, "nccl" = library all-reduce
+    # "fused" = peer-memory all-reduce + residual + norm kernel (one-shot at 2 ranks, two-shot beyond),
+    # "twoshot" = the same with the two-shot kernel at any rank count, "nccl" = library all-reduce
+    if handover:
         env["ORION_TP_ALLREDUCE"] = handover
     return subprocess.run(cmd, cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                           timeout=timeout)
@@ -38,7 +40,7 @@ def test_four_gloo_ranks_reproduce_the_unsharded_forward():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("handover", ["fused", "nccl"])
+@pytest.mark.parametrize("handover", ["fused", "twoshot", "nccl"])  # twoshot: the kernel of 3+ ranks, forced
 @pytest.mark.parametrize("dtype", ["F32", "BF16"])
 def test_two_gpu_ranks_match_the_oracle(pkg, dtype, handover):
     if pkg.device_count() < 2:
