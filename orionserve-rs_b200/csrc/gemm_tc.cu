@@ -474,7 +474,11 @@ int g_prefill_fill = std::getenv("ORION_GEMM_PREFILL_FILL") ? std::atoi(std::get
 // Weight tiles per CTA for a prefill-sized batch: two share one activation tile (less shared-memory
 // fill per flop). Mode 2 (default): only where the grid stays full without k splits; mode 3: always
 // (measured no better on the continuous-batching workload: 12.19 vs 11.94 s).
+// Batches of 129..256 rows stream weights like decode but already feel the fill rate (48 KiB of operands per
+// 4.2 MFLOP with one weight tile): ORION_GEMM_MID_MT=2 (default) gives a CTA two weight tiles there too.
+int g_mid_mt = std::getenv("ORION_GEMM_MID_MT") ? std::atoi(std::getenv("ORION_GEMM_MID_MT")) : 2;
 uint32_t prefill_weight_tiles(uint32_t rows, uint32_t n) {
+  if (rows > 128 && rows <= 256) return g_mid_mt >= 2 && n >= 2 * (uint32_t)kTileN ? 2 : 1;
   if (rows <= 256 || g_prefill_tiles < 2) return 1;
   if (g_prefill_tiles >= 3) return 2;
   return ((n + kTileN - 1) / kTileN) * ((rows + 255) / 256) >= 296 ? 2 : 1;
@@ -532,7 +536,7 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
                  ? launch_tc<128, 4, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
                  : launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
     default:
-      if (rows > 256 && !cluster_reduce && prefill_weight_tiles(rows, n) == 2)
+      if (!cluster_reduce && prefill_weight_tiles(rows, n) == 2)
         return launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
       return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
   }
@@ -609,7 +613,8 @@ GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t
     (void)nkb_big;
     return p;
   }
-  const uint32_t tiles = ((n + kTileN - 1) / kTileN) * ((rows + token_tile(rows) - 1) / token_tile(rows));
+  const uint32_t rows_per_cta = kTileN * (g_cluster_splitk ? 1 : prefill_weight_tiles(rows, n));
+  const uint32_t tiles = ((n + rows_per_cta - 1) / rows_per_cta) * ((rows + token_tile(rows) - 1) / token_tile(rows));
   const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
   // the 256-token tile (and the 6 + 6 stage 128-token one) fills an SM by itself: one wave is 148 CTAs
   const bool one_per_sm = g_mid_tile != 2 && (token_tile(rows) == 256 || (token_tile(rows) == 128 && g_mid_tile == 1));
