@@ -329,6 +329,8 @@ def run_ours(args):
     dist = None
     nccl_id = None
     if world > 1:
+        # NCCL prints its version banner on stdout; stdout carries the one JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import torch.distributed as dist  # plumbing only: rendezvous, id broadcast, max over ranks
 
         dist.init_process_group("gloo", rank=rank, world_size=world)
