@@ -328,9 +328,13 @@ def run_ours(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     dist = None
     nccl_id = None
+    json_out = sys.stdout
     if world > 1:
-        # NCCL prints its version banner on stdout; stdout carries the one JSON line only
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        # NCCL prints its version banner on stdout: keep the original stdout for the one JSON line and send
+        # everything else that is written to descriptor 1 to stderr
+        sys.stdout.flush()
+        json_out = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
         import torch.distributed as dist  # plumbing only: rendezvous, id broadcast, max over ranks
 
         dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -495,7 +499,7 @@ def run_ours(args):
             "value": cpu_tokens_per_s(t_layer, t_head, 16), "unit": "tokens/s", "cores": 1, "kind": "port",
             "sample": "1 of 32 layers at 16 decode tokens (ctx 1024) + 1/16 of the LM head rows, single thread like "
                       "the reference's engine loop, extrapolated to 32 layers + full head"}
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=json_out, flush=True)
     if dist is not None:
         dist.destroy_process_group()
     return 0
