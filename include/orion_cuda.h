@@ -130,6 +130,14 @@ void orion_cuda_model_destroy(OrionModel *model);
 int orion_cuda_selftest_bounded_wait(OrionBackend *backend, uint64_t limit_us, uint32_t *timed_out,
                                      uint32_t *waited_us);
 
+/* Reads and clears the time-out words of the backend's device (no reference counterpart): bit 0 the
+ * projection GEMM, bit 1 decode attention, bit 2 prefill attention, bit 3 the tensor-parallel
+ * hand-over. A set bit means a bounded device-side wait of that kernel family gave up since the last
+ * read. orion_cuda_model_forward reads the words itself after every step; a caller that launches
+ * kernels through the stand-alone entry points (orion_cuda_paged_decode_attention_noalloc) and wants
+ * to know whether one of its launches timed out synchronises its stream and calls this. */
+int orion_cuda_poll_wait_timeouts(OrionBackend *backend, uint32_t *mask);
+
 /* CheckpointLoader::open + ModelWeights::load for a whole directory
  * (crates/orion-models/src/loader.rs:112-235, transformer.rs:62-120,180-205): every
  * `*.safetensors` file in name order (the first file wins for a duplicated tensor name),
@@ -339,12 +347,24 @@ void orion_cuda_attn_bench_destroy(OrionAttnBench *bench);
  * library (held by every GPU that loads it until the process exits). A call
  * needing more — rows * num_query_heads * splits * 130 floats > 4 Mi floats —
  * is rejected with ORION_ERR_INVALID_REQUEST; splits == 1 needs none.
- * The first call on a device looks the array's address up; make that first
- * call before starting any stream capture. Every call on a device shares the
- * one array: calls whose kernels can overlap on the GPU (different streams
- * without ordering between them) race on it and must be serialised by the
- * caller. The array needs no clearing between calls: each call overwrites
- * every slot it later reads. */
+ * The first call on a device looks the array's address up and opts the kernel
+ * in to its shared-memory size on that device; make that first call before
+ * starting any stream capture. Every call on a device shares the one array:
+ * calls whose kernels can overlap on the GPU (different streams without
+ * ordering between them) race on it and must be serialised by the caller. The
+ * array needs no clearing between calls: each call overwrites every slot it
+ * later reads.
+ *
+ * `device` is made current for the duration of the call and the caller's
+ * current device is put back before returning. Nothing the pointers refer to is
+ * validated: block ids must be below num_blocks, every table must cover
+ * query_positions[r] / 16 + 1 entries and max_position must be the largest
+ * query position, or the kernel reads outside the arena (the model's forward
+ * checks these on the host; this entry point cannot, the arrays are on the
+ * device). The call only enqueues work. A bounded wait inside the kernel that
+ * gives up is recorded in the device's time-out word, which this call does not
+ * read: synchronise the stream and ask orion_cuda_poll_wait_timeouts (bit 1),
+ * otherwise the next orion_cuda_model_forward on that device reports it. */
 int orion_cuda_paged_decode_attention_noalloc(
     int device, const void *q, const void *kv_arena, uint32_t num_blocks, uint32_t num_kv_heads,
     uint32_t num_query_heads, const uint32_t *query_positions, const uint32_t *seq_of_row,

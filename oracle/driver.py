@@ -338,6 +338,9 @@ class Scheduler:  # scheduler.rs:127-580
         self.stats = dict(total_steps=0, total_admitted=0, total_finished=0, total_preempted=0, total_rejected=0,
                           total_batched_tokens=0, total_prefill_tokens=0, total_decode_tokens=0,
                           total_skipped_prefill_tokens=0)
+        # only with skip_cached_prefix: sequences one of whose prefill chunks was in a step whose
+        # forward failed (nothing written to the device cache although progress was recorded)
+        self.unwritten_prefill: set = set()
 
     def has_work(self) -> bool:
         return bool(self.waiting) or bool(self.running)
@@ -370,6 +373,7 @@ class Scheduler:  # scheduler.rs:127-580
         if s is not None:
             self.running.remove(s)
             self.cache.free(sid)
+            self.unwritten_prefill.discard(sid)
             return True
         return False
 
@@ -415,6 +419,7 @@ class Scheduler:  # scheduler.rs:127-580
         victim = self.running.pop()
         self.cache.free(victim.id)
         victim.preempt()
+        self.unwritten_prefill.discard(victim.id)
         self.waiting.appendleft(victim)
         preempted.append(victim.id)
         self.stats["total_preempted"] += 1
@@ -496,13 +501,20 @@ class Scheduler:  # scheduler.rs:127-580
         self.running = [s for s in self.running if s.state != FINISHED]
         for s in done:
             self.cache.free(s.id)
+            self.unwritten_prefill.discard(s.id)
         self.stats["total_finished"] += len(done)
         return done
 
     def commit_prefill(self, sid: int) -> None:  # scheduler.rs:557-564
         s = self.get(sid)
+        if self.config.skip_cached_prefix and sid in self.unwritten_prefill:
+            return
         if s is not None and s.prefill_complete():
             self.cache.commit_prefill(sid, s.prompt)
+
+    def note_failed_step(self, sched) -> None:
+        if self.config.skip_cached_prefix:
+            self.unwritten_prefill.update(x.id for x in sched if x.is_prefill)
 
 
 @dataclass
@@ -546,7 +558,11 @@ class Engine:  # engine.rs:186-487
             self._reap()
             return 0
         self.batch = self._build(sched)
-        ids = self.forward(self.batch) if self.batch.sequence_ids else []
+        try:
+            ids = self.forward(self.batch) if self.batch.sequence_ids else []
+        except Exception:
+            self.scheduler.note_failed_step(sched)
+            raise
         for row, sid in enumerate(self.batch.sequence_ids):
             s = self.scheduler.get(sid)
             if s is not None and not s.prefill_complete():

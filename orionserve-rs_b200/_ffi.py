@@ -67,6 +67,7 @@ SIGNATURES = {
     "orion_cuda_model_forward": (_int, [_vp, *_BATCH, _vp, _u64]),
     "orion_cuda_model_forward_greedy": (_int, [_vp, *_BATCH, _u32p, _vp, _u64]),
     "orion_cuda_model_load_checkpoint": (_int, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "orion_cuda_poll_wait_timeouts": (_int, [_vp, C.POINTER(C.c_uint32)]),
     "orion_cuda_selftest_bounded_wait": (_int, [_vp, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "orion_cuda_model_replay": (_int, [_vp, _int, _f32p]),
     "orion_cuda_model_replay_categories": (_int, [_vp, _int, C.c_uint32, _f32p]),

@@ -18,6 +18,10 @@ FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std
          "-I", "/usr/include"]
 
 
+if os.environ.get("ORION_TRACE"):  # phase traces of the GEMM and the hand-over kernels (rebuild with --force)
+    FLAGS.append("-DORION_TRACE")
+
+
 def _newer(a: str, b: str) -> bool:
     return (not os.path.exists(b)) or os.path.getmtime(a) > os.path.getmtime(b)
 

@@ -14,6 +14,9 @@
 //    merged in shared memory; context splits are merged by decode_combine_kernel.
 #include "kernels.h"
 
+#include <atomic>
+#include <mutex>
+
 namespace orion {
 namespace {
 
@@ -324,7 +327,9 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
       ++tgroup;
       tbl_b = load_group(tgroup + 1);
     }
-    if (!mbar_wait(&my_bars[stage], (i / kStages) & 1)) {
+    // the verdict of the bounded wait is taken by the whole warp, so that the lanes stay
+    // converged for the shuffles below even if they disagree at the deadline
+    if (!__all_sync(0xffffffffu, mbar_wait(&my_bars[stage], (i / kStages) & 1))) {
       ok = false;
       break;
     }
@@ -541,13 +546,9 @@ template <int STAGES>
 int launch_decode_stages(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer, AttnBatch batch,
                          uint32_t q_heads, uint32_t splits, DecodeScratch scratch, bf16 *out,
                          PrefetchHint next, FusedQkv fq, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    ORION_CUDA_CHECK("paged_decode attr",
-                     cudaFuncSetAttribute(paged_decode_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)decode_smem_bytes(STAGES)));
-    attr_set = true;
-  }
+  static bool attr_set[kMaxDeviceOrdinals] = {};
+  ORION_CUDA_CHECK("paged_decode attr",
+                   ensure_dynamic_smem(paged_decode_kernel<STAGES>, (int)decode_smem_bytes(STAGES), attr_set));
   ORION_CUDA_CHECK("paged_decode",
                    launch_pdl(paged_decode_kernel<STAGES>, dim3(kv.num_kv_heads, batch.rows, splits),
                               dim3(kWarps * 32), (size_t)decode_smem_bytes(STAGES), stream, q, arena, kv, layer,
@@ -614,11 +615,26 @@ constexpr size_t kNoAllocScratchFloats = size_t(4) << 20;
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
 
 namespace {
-constexpr int kMaxDevices = 64;
+constexpr int kMaxDevices = kMaxDeviceOrdinals;
 // Device address of g_noalloc_scratch per device ordinal. The symbol's name is
 // only a host-side handle; a kernel must be given the address looked up with
 // cudaGetSymbolAddress while that device is current.
-float *g_noalloc_ptr[kMaxDevices] = {};
+std::atomic<float *> g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mu;
+
+// Makes `device` current for the scope and puts the caller's device back afterwards.
+struct ScopedDevice {
+  int prev = -1;
+  cudaError_t status;
+  explicit ScopedDevice(int device) {
+    status = cudaGetDevice(&prev);
+    if (status == cudaSuccess && prev != device) status = cudaSetDevice(device);
+  }
+  ~ScopedDevice() {
+    int now = -1;
+    if (prev >= 0 && cudaGetDevice(&now) == cudaSuccess && now != prev) cudaSetDevice(prev);
+  }
+};
 }  // namespace
 
 int noalloc_decode_attention(int device, const bf16 *q, const bf16 *arena, uint32_t num_blocks,
@@ -642,14 +658,17 @@ int noalloc_decode_attention(int device, const bf16 *q, const bf16 *arena, uint3
                      "allocation-free decode attention: %u rows x %u heads x %u splits needs %zu scratch "
                      "floats, the built-in array holds %zu; use fewer splits or the allocating entry point",
                      rows, num_query_heads, splits, need, kNoAllocScratchFloats);
-  ORION_CUDA_CHECK("set device", cudaSetDevice(device));
-  if (!g_noalloc_ptr[device]) {
+  ScopedDevice current(device);  // the caller's current device is restored on return
+  ORION_CUDA_CHECK("set device", current.status);
+  float *base = g_noalloc_ptr[device].load(std::memory_order_acquire);
+  if (!base) {
     // One-time set-up for this device (no allocation: the array is part of the module).
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
     void *p = nullptr;
     ORION_CUDA_CHECK("scratch symbol address", cudaGetSymbolAddress(&p, g_noalloc_scratch));
-    g_noalloc_ptr[device] = static_cast<float *>(p);
+    base = static_cast<float *>(p);
+    g_noalloc_ptr[device].store(base, std::memory_order_release);
   }
-  float *base = g_noalloc_ptr[device];
   // Every (row, head, split) slot is written by the decode kernel before the
   // combine kernel reads it, so nothing has to be cleared between calls.
   DecodeScratch sc{base, base + (size_t)rows * num_query_heads * splits * kHd, splits};

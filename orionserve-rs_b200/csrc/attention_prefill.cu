@@ -229,12 +229,8 @@ int launch_paged_attention_prefill(const bf16 *q, const bf16 *arena, KvLayout kv
   if (num_tiles == 0) return ORION_OK;
   if (!prefill_attention_supported(kv, q_heads))
     return set_error(ORION_ERR_INTERNAL, "prefill attention kernel does not cover this shape");
-  static bool attr_set = false;
-  if (!attr_set) {
-    ORION_CUDA_CHECK("paged_prefill attr", cudaFuncSetAttribute(paged_prefill_kernel,
-                                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem));
-    attr_set = true;
-  }
+  static bool attr_set[kMaxDeviceOrdinals] = {};
+  ORION_CUDA_CHECK("paged_prefill attr", ensure_dynamic_smem(paged_prefill_kernel, (int)kSmem, attr_set));
   ORION_CUDA_CHECK("paged_prefill", launch_pdl(paged_prefill_kernel, dim3(kv.num_kv_heads, num_tiles), dim3(kThreads),
                                                (size_t)kSmem, stream, q, arena, kv, layer, batch, tiles, q_heads, out));
   count_launch();

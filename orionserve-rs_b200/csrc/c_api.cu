@@ -399,6 +399,19 @@ int orion_cuda_selftest_bounded_wait(OrionBackend *backend, uint64_t limit_us, u
   return selftest_bounded_wait(limit_us, timed_out, waited_us);
 }
 
+int orion_cuda_poll_wait_timeouts(OrionBackend *backend, uint32_t *mask) {
+  orion::clear_error();
+  ORION_TRY(orion::check_backend(backend));
+  if (!mask) return orion::set_error(ORION_ERR_INVALID_REQUEST, "null output pointer");
+  uint32_t gemm = 0, decode = 0, prefill = 0, tp = 0;
+  ORION_TRY(orion::gemm_tc_poll_error(&gemm));
+  ORION_TRY(orion::decode_poll_error(&decode));
+  ORION_TRY(orion::prefill_poll_error(&prefill));
+  ORION_TRY(orion::tp_poll_error(&tp));
+  *mask = (gemm ? 1u : 0u) | (decode ? 2u : 0u) | (prefill ? 4u : 0u) | (tp ? 8u : 0u);
+  return ORION_OK;
+}
+
 int orion_cuda_model_load_checkpoint(OrionModel *model, const char *directory, uint64_t *tensors_loaded) {
   clear_error();
   if (!model) return set_error(ORION_ERR_INVALID_REQUEST, "null model handle");

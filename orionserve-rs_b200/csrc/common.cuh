@@ -80,6 +80,22 @@ inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Opt-in to more than 48 KiB of dynamic shared memory for `kernel`. The attribute belongs to the
+// (kernel, device) pair, so it is set once per device ordinal: `done` is the caller's static
+// array of kMaxDeviceOrdinals flags for this kernel instantiation.
+constexpr int kMaxDeviceOrdinals = 64;
+template <typename K>
+inline cudaError_t ensure_dynamic_smem(K kernel, int bytes, bool *done) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const bool tracked = dev >= 0 && dev < kMaxDeviceOrdinals;
+  if (tracked && done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && tracked) done[dev] = true;
+  return e;
+}
+
 // ---- storage types ----------------------------------------------------------
 
 using bf16 = __nv_bfloat16;

@@ -22,6 +22,7 @@
 #include <string>
 #include <unordered_map>
 #include <utility>
+#include <unordered_set>
 #include <vector>
 
 namespace orion {
@@ -238,6 +239,12 @@ class Scheduler {  // scheduler.rs:127-580
   std::vector<SequenceId> expire_timeouts();
   const Sequence *running_sequence(SequenceId id) const;
   void commit_prefill(SequenceId id);
+  // Only with skip_cached_prefix: the forward of a step failed, so the prefill chunks it carried
+  // wrote no keys or values although their progress was recorded at schedule time. The prompts
+  // of these sequences are not published to the prefix cache (a later request would adopt blocks
+  // that were never written and skip their computation); they stay usable for their own sequence
+  // exactly as in the reference.
+  void note_failed_step(const SchedulerOutput &out);
 
  private:
   Sequence *running_mut(SequenceId id);
@@ -251,6 +258,7 @@ class Scheduler {  // scheduler.rs:127-580
   std::vector<Sequence> running_;  // admission order; the newest is the preemption victim (queue.rs:103-174)
   KvCacheManager cache_;
   SchedulerStats stats_;
+  std::unordered_set<SequenceId> unwritten_prefill_;  // see note_failed_step
 };
 
 // The batch handed to the forward function, laid out as the C ABI of the device model takes it

@@ -123,6 +123,7 @@ bool Scheduler::cancel(SequenceId id) {  // scheduler.rs:226-236
     if (it->id() == id) {
       running_.erase(it);
       cache_.free(id);
+      unwritten_prefill_.erase(id);
       return true;
     }
   return false;
@@ -177,6 +178,7 @@ bool Scheduler::preempt_one(SchedulerOutput &out) {  // scheduler.rs:317-330
   const SequenceId id = victim.id();
   cache_.free(id);
   victim.preempt();
+  unwritten_prefill_.erase(id);  // its prefill starts over, every chunk will be computed again
   waiting_.push_front(std::move(victim));
   out.preempted.push_back(id);
   stats_.total_preempted += 1;
@@ -282,7 +284,10 @@ std::vector<Sequence> Scheduler::reap_finished() {  // scheduler.rs:513-520, que
       ++i;
     }
   }
-  for (const Sequence &s : finished) cache_.free(s.id());
+  for (const Sequence &s : finished) {
+    cache_.free(s.id());
+    unwritten_prefill_.erase(s.id());
+  }
   stats_.total_finished += finished.size();
   return finished;
 }
@@ -310,7 +315,14 @@ std::vector<SequenceId> Scheduler::expire_timeouts() {  // scheduler.rs:527-549
 
 void Scheduler::commit_prefill(SequenceId id) {  // scheduler.rs:557-564
   const Sequence *seq = running_sequence(id);
+  if (config_.skip_cached_prefix && unwritten_prefill_.count(id)) return;  // some chunk never reached the device
   if (seq && seq->is_prefill_complete()) cache_.commit_prefill(id, seq->prompt().data(), seq->prompt().size());
+}
+
+void Scheduler::note_failed_step(const SchedulerOutput &out) {
+  if (!config_.skip_cached_prefix) return;
+  for (const ScheduledSequence &s : out.scheduled)
+    if (s.is_prefill) unwritten_prefill_.insert(s.id);
 }
 
 // ---- Engine ----------------------------------------------------------------------------------
@@ -372,7 +384,13 @@ int Engine::step(size_t *ran) {  // engine.rs:293-342
   ORION_TRY(build_batch(last_output_));
   const size_t S = batch_.sequence_ids.size();
   sampled_.assign(S, 0);
-  if (S > 0) ORION_TRY(forward_(batch_, sampled_.data()));  // on error nothing is sampled, committed or reaped
+  if (S > 0) {  // on error nothing is sampled, committed or reaped (engine.rs:310)
+    const int rc = forward_(batch_, sampled_.data());
+    if (rc != ORION_OK) {
+      scheduler_.note_failed_step(last_output_);
+      return rc;
+    }
+  }
   for (size_t row = 0; row < S; ++row) {
     const SequenceId seq_id = batch_.sequence_ids[row];
     const Sequence *seq = scheduler_.running_sequence(seq_id);

@@ -39,13 +39,19 @@ constexpr int kUmmaK = 16;
 constexpr int kThreads = 256;
 
 __device__ uint32_t g_gemm_error = 0;
-// Debug trace (ORION_GEMM_TRACE=1): %globaltimer stamps of CTA (0,0,0) of the last launches.
+#ifdef ORION_TRACE
+// Phase trace, compiled in with -DORION_TRACE only and switched on by ORION_GEMM_TRACE=1:
+// %globaltimer stamps of CTA (0,0,0) of the last launches.
 constexpr int kTraceLaunches = 160, kTraceStamps = 8;
 __device__ unsigned long long g_gemm_trace[kTraceLaunches][kTraceStamps];
 __device__ uint32_t g_gemm_trace_on = 0, g_gemm_trace_next = 0;
 __device__ __forceinline__ void gtrace(uint32_t slot, int k) {
   if (slot != 0xFFFFFFFFu) g_gemm_trace[slot][k] = global_timer_ns();
 }
+#define ORION_GTRACE(slot, k) gtrace(slot, k)
+#else
+#define ORION_GTRACE(slot, k) ((void)0)
+#endif
 
 // Two rings per CTA. Weight tiles come from HBM (long latency, the stream that must never
 // stall): WST stages of 16 KiB. Activation tiles come from L2 (every CTA re-reads them):
@@ -179,8 +185,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t my_kb = kb_end - kb_begin;
 
   pdl_trigger();
+#ifdef ORION_TRACE
   __shared__ uint32_t trace_slot_s;
+#endif
   if (threadIdx.x == 0) {
+#ifdef ORION_TRACE
     uint32_t slot = 0xFFFFFFFFu;
     if (g_gemm_trace_on && blockIdx.x + blockIdx.y + blockIdx.z == 0) {
       slot = atomicAdd(&g_gemm_trace_next, 1u) % kTraceLaunches;
@@ -188,6 +197,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     trace_slot_s = slot;
     gtrace(slot, 0);
+#endif
     for (int s = 0; s < WST; ++s) {
       mbar_init(&full_w[s], 1);
       mbar_init(&empty_w[s], 1);
@@ -207,14 +217,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+#ifdef ORION_TRACE
   const uint32_t tslot = trace_slot_s;
+#endif
   bool ok = true;
 
   if (warp == 0) {
     // Weight producer. Weights are immutable, so this stream starts while the kernel that
     // produces the activations is still running and never waits for it.
     if (lane == 0) {
-      gtrace(tslot, 1);
+      ORION_GTRACE(tslot, 1);
       for (uint32_t i = 0; i < my_kb; ++i) {
         const uint32_t s = i % WST, use = i / WST;
         if (!mbar_wait(&empty_w[s], (use & 1) ^ 1)) { ok = false; break; }
@@ -230,7 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // Activation producer: waits for the preceding kernel, then keeps the short x ring full.
     if (lane == 0) {
       pdl_wait();
-      gtrace(tslot, 3);
+      ORION_GTRACE(tslot, 3);
       for (uint32_t i = 0; i < my_kb; ++i) {
         const uint32_t s = i % XST, use = i / XST;
         if (!mbar_wait(&empty_x[s], (use & 1) ^ 1)) { ok = false; break; }
@@ -244,7 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (uint32_t i = 0; i < my_kb; ++i) {
         const uint32_t sw = i % WST, sx = i % XST;
         if (!mbar_wait(&full_w[sw], (i / WST) & 1)) { ok = false; break; }
-        if (i == 0) gtrace(tslot, 2);
+        if (i == 0) ORION_GTRACE(tslot, 2);
         if (!mbar_wait(&full_x[sx], (i / XST) & 1)) { ok = false; break; }
         tc_fence_after();
         const uint32_t wt = smem_u32(w_ring + sw * Cfg::kWBytes);
@@ -263,7 +275,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         umma_commit(&empty_x[sx]);
       }
       umma_commit(acc_ready);  // arrives when every MMA above has completed
-      gtrace(tslot, 4);
+      ORION_GTRACE(tslot, 4);
     }
   } else if (warp >= 4) {
     // Epilogue warps: warp w may touch tensor-memory lanes 32*(w%4) .. +31.
@@ -275,7 +287,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!mbar_wait(acc_ready, 0)) ok = false;
     }
     tc_fence_after();
-    if (threadIdx.x == 128) gtrace(tslot, 5);
+    if (threadIdx.x == 128) ORION_GTRACE(tslot, 5);
     float *dst = partial + (size_t)split * M * N;
     // Split-K inside a cluster: the tile goes to shared memory as stage[token][128 weight rows]
     // (the rings are idle: every load has landed and every MMA has read its operands).
@@ -358,7 +370,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     cluster_arrive_release();  // nobody leaves while a peer may still read its staged tile
     cluster_wait_acquire();
   }
-  if (threadIdx.x == 128) gtrace(tslot, 6);
+  if (threadIdx.x == 128) ORION_GTRACE(tslot, 6);
   if (!ok) atomicOr(&g_gemm_error, 1u);
   tc_fence_before();
   __syncthreads();
@@ -439,14 +451,8 @@ int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *p
   using Cfg = TcConfig<TOKN, WST, XST, MT>;
   static_assert(Cfg::kSmemBytes <= 232448, "ring exceeds the shared memory of an SM");
   if (MT > 1 && cluster_reduce) return set_error(ORION_ERR_INTERNAL, "cluster split-K is built for one weight tile per CTA");
-  static bool attr_set = false;
-  if (!attr_set) {
-    ORION_CUDA_CHECK("gemm_tc attr",
-                     cudaFuncSetAttribute(gemm_tc_kernel<TOKN, WST, XST, MT>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          Cfg::kSmemBytes));
-    attr_set = true;
-  }
+  static bool attr_set[kMaxDeviceOrdinals] = {};
+  ORION_CUDA_CHECK("gemm_tc attr", ensure_dynamic_smem(gemm_tc_kernel<TOKN, WST, XST, MT>, Cfg::kSmemBytes, attr_set));
   const CUtensorMap *mw, *mx;
   ORION_TRY(cached_map(w, n, k, ldw, kTileN, &mw));
   ORION_TRY(cached_map(x, rows, k, ldx, TOKN, &mx));
@@ -543,6 +549,7 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
 }
 
 int gemm_tc_poll_error(uint32_t *code) {
+#ifdef ORION_TRACE
   static const bool tracing = std::getenv("ORION_GEMM_TRACE") != nullptr;
   if (tracing) {
     static unsigned long long t[kTraceLaunches][kTraceStamps];
@@ -563,6 +570,7 @@ int gemm_tc_poll_error(uint32_t *code) {
       }
     }
   }
+#endif
   uint32_t v = 0;
   ORION_CUDA_CHECK("gemm error word", cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof v));
   if (v) {

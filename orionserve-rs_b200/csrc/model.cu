@@ -651,7 +651,23 @@ int Model<T>::run_step(bool want_argmax) {
   const uint32_t *last_rows = m + meta_.last_rows;
   AttnBatch ab{positions, m + meta_.seq_of_row, m + meta_.tables, m + meta_.offsets, Tn, meta_.max_position};
   const bool tuned_decode = kBf16 && meta_.decode && decode_attention_supported(kv_, lq_);
-  const uint32_t dsplits = tuned_decode ? decode_choose_splits(Tn, lkv_, meta_.max_position, d.block_size, 32) : 1;
+  // The work buffers were sized at creation under the tuning values of that moment; a tuning call
+  // made since may ask for more k splits or context splits than they hold, so every plan is cut
+  // back to the capacity before it is launched.
+  auto fit_context_splits = [&](uint32_t rows, uint32_t want) {
+    while (want > 1 && decode_scratch_floats(rows, lq_, hd, want) > dscratch_floats_) --want;
+    return want;
+  };
+  auto plan_for = [&](uint32_t rows, uint32_t n, uint32_t k) {
+    GemmPlan p = gemm_plan(kBf16, rows, n, k, k, k);
+    while (p.splits > 1 && (size_t)p.splits * rows * n > partial_floats_) {
+      --p.splits;
+      if (!p.cluster_reduce) p.out_slabs = p.splits;
+    }
+    if (p.splits == 1) p.cluster_reduce = false, p.out_slabs = 1;
+    return p;
+  };
+  const uint32_t dsplits = tuned_decode ? fit_context_splits(Tn, decode_choose_splits(Tn, lkv_, meta_.max_position, d.block_size, 32)) : 1;
   // L2 prefetch of the next projection's weights: only where the projections are bandwidth-bound
   // (decode-sized batches), and never more than a fraction of L2 per hand-over.
   const size_t budget = (kBf16 && Tn <= 256) ? g_prefetch_budget : 0;
@@ -667,7 +683,7 @@ int Model<T>::run_step(bool want_argmax) {
   ORION_TRY(timed(kProfElementwise, [&] { return launch_embed_rmsnorm<T>(embed_, tokens, layers_[0].in_norm, d.rms_norm_eps, hidden_, normed_, Tn, H, stream_); }));
   for (uint32_t l = 0; l < d.num_layers; ++l) {
     const Layer &L = layers_[l];
-    GemmPlan p = gemm_plan(kBf16, Tn, nqkv, H, H, H);
+    GemmPlan p = plan_for(Tn, nqkv, H);
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_qkv, H, partial_, Tn, nqkv, H, p, stream_); }));
     // Pure decode batches on the tuned path: the attention kernel folds the QKV partials, applies
     // RoPE and writes the KV slot itself, so the separate kernel (and its launch hop) is left out.
@@ -697,7 +713,7 @@ int Model<T>::run_step(bool want_argmax) {
         if (meta_.dec_rows > 0) {  // the decode rows of a mixed batch: one contiguous run of rows
           const uint32_t r0 = meta_.dec_row0, n = meta_.dec_rows;
           AttnBatch sub{positions + r0, m + meta_.seq_of_row + r0, ab.tables_flat, ab.table_offsets, n, meta_.max_position};
-          const uint32_t sp = decode_choose_splits(n, lkv_, meta_.max_position, d.block_size, 32);
+          const uint32_t sp = fit_context_splits(n, decode_choose_splits(n, lkv_, meta_.max_position, d.block_size, 32));
           DecodeScratch sc{dscratch_, dscratch_ + (size_t)n * lq_ * sp * hd, sp};
           ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_decode(qbuf_ + (size_t)r0 * qd, arena_, kv_, l, sub, lq_, sp, sc,
                                                                                        attn_ + (size_t)r0 * qd, stream_); }));
@@ -710,12 +726,12 @@ int Model<T>::run_step(bool want_argmax) {
     } else {
       ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_generic<T>(qbuf_, arena_, kv_, l, ab, lq_, attn_, stream_); }));
     }
-    p = gemm_plan(kBf16, Tn, H, qd, qd, qd);
+    p = plan_for(Tn, H, qd);
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(attn_, qd, L.w_o, qd, partial_, Tn, H, qd, p, stream_,
                                                               hint(L.w_gu, (size_t)2 * lf_ * H)); }));
     const int handover_cat = nccl_ ? kProfCollective : kProfElementwise;
     ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, L.post_norm, normed_, nullptr, Tn); }));
-    p = gemm_plan(kBf16, Tn, 2 * lf_, H, H, H);
+    p = plan_for(Tn, 2 * lf_, H);
     bool fused_swiglu = false;
     if constexpr (kBf16) {
       if (p.tensor_core && p.splits == 1 && g_fuse_swiglu) {  // SwiGLU in the GEMM epilogue: no partials, no extra launch
@@ -730,7 +746,7 @@ int Model<T>::run_step(bool want_argmax) {
       ORION_TRY(timed(kProfElementwise, [&] { return launch_swiglu<T>(partial_, p.out_slabs, (size_t)Tn * 2 * lf_, act_, Tn, lf_, stream_,
                                                                        kInterleaveGateUp); }));
     }
-    p = gemm_plan(kBf16, Tn, H, lf_, lf_, lf_);
+    p = plan_for(Tn, H, lf_);
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(act_, lf_, L.w_down, lf_, partial_, Tn, H, lf_, p, stream_,
                                                               l + 1 < d.num_layers ? hint(layers_[l + 1].w_qkv, (size_t)nqkv * H)
                                                                                    : hint(lm_head_, (size_t)d.vocab_size * H)); }));
@@ -786,6 +802,14 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
   if (b.num_positions != b.num_tokens)
     return set_error(ORION_ERR_INTERNAL, "ForwardBatch has %llu tokens but %llu positions",
                      (unsigned long long)b.num_tokens, (unsigned long long)b.num_positions);
+  // Malformed calls across the C boundary (the Rust vectors cannot be null or out of order).
+  if ((b.num_tokens > 0 && (!b.tokens || !b.positions)) || (S > 0 && (!b.slot_token_counts || !b.block_table_offsets)))
+    return set_error(ORION_ERR_INVALID_REQUEST, "null batch array");
+  for (uint64_t s = 0; s < S; ++s)
+    if (b.block_table_offsets[s + 1] < b.block_table_offsets[s])
+      return set_error(ORION_ERR_INVALID_REQUEST, "block table offsets decrease at sequence %llu", (unsigned long long)s);
+  if (S > 0 && b.block_table_offsets[S] > 0 && !b.block_tables_flat)
+    return set_error(ORION_ERR_INVALID_REQUEST, "null batch array");
   uint64_t summed = 0;
   for (uint64_t s = 0; s < S; ++s) summed += b.slot_token_counts[s];
   if (summed != b.num_tokens)
@@ -805,7 +829,7 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
                      (unsigned long long)logits_capacity, (unsigned long long)(S * (uint64_t)d.vocab_size));
 
   ORION_CUDA_CHECK("set device", cudaSetDevice(ordinal_));
-  const uint64_t table_entries = b.block_table_offsets[S];
+  const uint64_t table_entries = S ? b.block_table_offsets[S] : 0;
   Meta mt;
   mt.rows = (uint32_t)Tn;
   mt.seqs = (uint32_t)S;

@@ -28,12 +28,17 @@ namespace orion {
 namespace {
 
 __device__ uint32_t g_tp_error = 0;
-// Debug trace (ORION_TP_TRACE=1): %globaltimer at the phase boundaries of CTA 0 of the last launch.
+#ifdef ORION_TRACE
+// Phase trace, compiled in with -DORION_TRACE only and switched on by ORION_TP_TRACE=1:
+// %globaltimer at the phase boundaries of CTA 0 of the last launch.
 __device__ unsigned long long g_tp_trace[4];
 __device__ uint32_t g_tp_trace_on = 0;
 __device__ __forceinline__ void trace(int k) {
   if (g_tp_trace_on && blockIdx.x == 0 && threadIdx.x == 0) g_tp_trace[k] = global_timer_ns();
 }
+#else
+__device__ __forceinline__ void trace(int) {}
+#endif
 
 __device__ __forceinline__ void st_unit2(uint32_t *dst, float a, float b, uint32_t epoch) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(__float_as_uint(a)), "r"(epoch),
@@ -360,6 +365,7 @@ template int launch_tp_allreduce_residual_rmsnorm<bf16>(const TpPeers &, uint32_
                                                         bool, cudaStream_t);
 
 int tp_poll_error(uint32_t *code) {
+#ifdef ORION_TRACE
   static const bool tracing = std::getenv("ORION_TP_TRACE") != nullptr;
   if (tracing) {
     uint32_t on = 1;
@@ -369,6 +375,7 @@ int tp_poll_error(uint32_t *code) {
     fprintf(stderr, "tp trace of CTA 0 (us): fold+send %.2f receive %.2f norm %.2f total %.2f\n", (t[1] - t[0]) / 1e3,
             (t[2] - t[1]) / 1e3, (t[3] - t[2]) / 1e3, (t[3] - t[0]) / 1e3);
   }
+#endif
   uint32_t v = 0;
   ORION_CUDA_CHECK("tp error word", cudaMemcpyFromSymbol(&v, g_tp_error, sizeof v));
   if (v) {

@@ -572,3 +572,44 @@ def test_the_prefix_cache_serves_a_repeated_prompt(impl):
         e.submit(list(range(16)), 1)
         run(e, 20)
     assert e.sched.cache.hits() > 0
+
+
+def test_a_prompt_with_a_chunk_lost_to_a_failed_step_is_not_offered_for_skipping(impl):
+    """Prefill progress is recorded at schedule time and a failed forward rolls nothing back
+    (engine.rs:310). With skip_cached_prefix a prompt one of whose chunks was in a failed step must
+    not be published: a later request with the same prefix would adopt blocks that hold no keys and
+    values and skip computing them. Without the flag the reference's behaviour stays: published, and
+    recomputed by whoever adopts it."""
+    prompt = list(range(200, 224))  # six blocks of four, three chunks of eight
+    for skip in (True, False):
+        fail = {"on": False}
+
+        def forward(batch):
+            if fail["on"]:
+                raise RuntimeError("device refused the step")
+            return [3] * len(batch.sequence_ids)
+
+        e = Eng(impl, forward, 64, 4, True, eos=[15], max_num_seqs=4, max_num_batched_tokens=8, max_model_len=256,
+                skip_cached_prefix=skip)
+        a = e.submit(prompt, 1)
+        assert e.step() == 1                      # chunk [0, 8)
+        fail["on"] = True
+        with pytest.raises(Exception):
+            e.step()                              # chunk [8, 16) is scheduled, its forward fails
+        fail["on"] = False
+        assert e.batch()["positions"] == list(range(8, 16))
+        assert e.step() == 1                      # chunk [16, 24) completes the prompt and samples
+        assert e.batch()["positions"] == list(range(16, 24))
+        assert ("done", a, "length", 24, 1) in e.events()
+        assert (e.sched.cache.entries() == 0) == skip, "a prompt with an unwritten chunk is withheld only when skipping"
+        b = e.submit(prompt, 1)
+        e.step()
+        first = e.batch()
+        assert first["sequence_ids"] == [b] and first["positions"][0] == 0, "nothing to skip: prefill starts at 0"
+        while e.has_work():
+            e.step()
+        assert e.sched.stats()["total_skipped_prefill_tokens"] == 0
+        assert e.sched.cache.entries() == 6       # b ran every chunk, so its prompt is published
+        c = e.submit(prompt, 1)
+        e.step()
+        assert e.batch()["positions"] == ([23] if skip else list(range(0, 8)))
