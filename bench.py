@@ -36,11 +36,25 @@ LLAMA3_70B = dict(hidden_size=8192, num_layers=80, num_attention_heads=64, num_k
 BATCH, CONTEXT, BLOCK = 64, 1024, 16
 WORKLOAD = "llama3_8b_decode_batch64_ctx1024_bf16"
 METRIC = "decode tokens/s at batch 64 (Llama-3-8B shape)"
-# DRAM bytes (read + write) of the projection GEMM launches of one 32-layer step, from the ncu
-# capture summarised in profiles/gemm_tc_kernel_decode_batch64_llama3_8b_shape.md: the four
-# projections of one layer moved 449.09 MB (algorithmic 436.21 MB); 32 layers of that plus the LM
-# head at its algorithmic 1050.67 MB of weights + 32.83 MB of logits (the head was not captured).
-GEMM_TRAFFIC_BYTES_PER_STEP = int(32 * 449.09e6 + 1050.67e6 + 32.83e6)
+GEMM_PROFILE = os.path.join(ROOT, "profiles", "gemm_tc_kernel_decode_batch64_llama3_8b_shape.md")
+
+
+def gemm_traffic_bytes_per_step():
+    """DRAM bytes (read + write) of the projection launches of one 32-layer headline step, as the ncu
+    capture summarised in the profile file measured them. The summary carries the figures on two lines,
+    `dram_bytes_per_layer: <n>` (the four projections of one layer) and `dram_bytes_lm_head: <n>` (the
+    head's launches), next to the commit the capture was taken at; nothing is typed in here, so a
+    stale capture shows in that file and not as a silent constant. None when the file lacks them."""
+    import re
+    try:
+        text = open(GEMM_PROFILE).read()
+    except OSError:
+        return None
+    layer = re.search(r"^dram_bytes_per_layer:\s*(\d+)", text, re.M)
+    head = re.search(r"^dram_bytes_lm_head:\s*(\d+)", text, re.M)
+    if not layer or not head:
+        return None
+    return LLAMA3_8B["num_layers"] * int(layer.group(1)) + int(head.group(1))
 
 
 def measured_peaks():
@@ -177,6 +191,17 @@ def cpu_tokens_per_s(t_layer, t_head, sample_batch):
     return sample_batch / step
 
 
+def headline_config(world, layers, workload=WORKLOAD, nbatch=BATCH, context=CONTEXT, full_layers=32, wbytes=None, kbytes=None):
+    """The `config` object of the JSON line; both arms print the same keys for the same workload."""
+    m = LLAMA3_8B
+    if wbytes is None:
+        wbytes, kbytes = weight_bytes_per_step(m, world), kv_bytes_per_step(m, [CONTEXT] * BATCH, world)
+    return {"workload": workload if layers == full_layers else f"{workload}_first{layers}layers",
+            "batch": nbatch, "context": context, "block_size": BLOCK, "layers": layers, "parallelism": f"tp{world}",
+            "l2": f"inputs exceed L2: {wbytes / 1e9:.1f} GB of weights + {kbytes / 1e9:.1f} GB of KV read "
+                  f"per step and rank"}
+
+
 def run_reference(args):
     """--impl reference: the reference's CPU path (restated; the Rust reference cannot be built
     where this runs) on the host cores, all threads, bounded sample per step."""
@@ -190,18 +215,19 @@ def run_reference(args):
     threads = min(cores, 64)
     sample_batch = 8
     rng = np.random.default_rng(0)
-    for _ in range(max(0, min(args.warmup, 1))):
-        cpu_sample_step(oracle, threads, 2, rng)
-    times = [cpu_sample_step(oracle, threads, sample_batch, rng) for _ in range(max(1, min(args.steps, 3)))]
+    # one sampled step costs ~0.15 s of wall clock on 16 threads: K steps and W warm-ups as asked
+    for _ in range(max(0, args.warmup)):
+        cpu_sample_step(oracle, threads, sample_batch, rng)
+    times = [cpu_sample_step(oracle, threads, sample_batch, rng) for _ in range(max(1, args.steps))]
     t_layer = float(np.mean([t[0] for t in times]))
     t_head = float(np.mean([t[1] for t in times]))
     value = cpu_tokens_per_s(t_layer, t_head, sample_batch)
     sample = (f"1 of 32 layers at {sample_batch} decode tokens (ctx {CONTEXT}) + 1/16 of the LM head rows per step, "
               f"extrapolated to 32 layers + full head; {threads} threads over output elements (bit-identical to 1)")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": 1000.0 * (t_layer + t_head),
+            "steps": len(times), "warmup": max(0, args.warmup), "ms_per_step": 1000.0 * (t_layer + t_head),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch": BATCH, "context": CONTEXT, "block_size": BLOCK},
+            "config": headline_config(max(1, args.gpus), LLAMA3_8B["num_layers"]),
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -318,6 +344,134 @@ def run_serving(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------
+# Tensor-parallel parity, checked before anything is timed at N > 1
+# ---------------------------------------------------------------------------------------------
+
+# A small Llama/Qwen2-shaped model with EIGHT kv heads (so that 2, 4 and 8 ranks all get whole heads),
+# QKV bias, head_dim 128 and 16-token blocks: every rank runs the tuned kernels of the headline step.
+TP_CHECK = dict(hidden_size=1024, num_layers=2, num_attention_heads=16, num_kv_heads=8, head_dim=128,
+                vocab_size=2048, ffn_dim=2048, max_position_embeddings=64, rope_theta=10000.0, rms_norm_eps=1e-5,
+                has_qkv_bias=True, tied_lm_head=False)
+TP_CHECK_BLOCKS = 384
+
+
+def round_bf16(a):
+    """Nearest-even rounding of f32 to bf16 precision, kept as f32 (what the device does at load)."""
+    bits = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    return (((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
+
+
+def tp_check_weights(m=None, seed=23):
+    """Seeded host checkpoint of the check model (every rank draws the same values and slices its own)."""
+    m, rng = m or TP_CHECK, np.random.default_rng(seed)
+    H, V, F, hd = m["hidden_size"], m["vocab_size"], m["ffn_dim"], m["head_dim"]
+    qd, kvd = m["num_attention_heads"] * hd, m["num_kv_heads"] * hd
+
+    def mat(r, c, std):
+        return round_bf16((rng.standard_normal((r, c)) * std).astype(np.float32))
+
+    def gain():
+        return (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+
+    t = {"model.embed_tokens.weight": mat(V, H, 1.0), "model.norm.weight": gain(), "lm_head.weight": mat(V, H, 0.05)}
+    for i in range(m["num_layers"]):
+        p = f"model.layers.{i}"
+        t[f"{p}.input_layernorm.weight"], t[f"{p}.post_attention_layernorm.weight"] = gain(), gain()
+        t[f"{p}.self_attn.q_proj.weight"], t[f"{p}.self_attn.k_proj.weight"] = mat(qd, H, 0.04), mat(kvd, H, 0.04)
+        t[f"{p}.self_attn.v_proj.weight"], t[f"{p}.self_attn.o_proj.weight"] = mat(kvd, H, 0.04), mat(H, qd, 0.03)
+        for n, d in (("q", qd), ("k", kvd), ("v", kvd)):
+            t[f"{p}.self_attn.{n}_proj.bias"] = (rng.standard_normal(d) * 0.1).astype(np.float32)
+        t[f"{p}.mlp.gate_proj.weight"], t[f"{p}.mlp.up_proj.weight"] = mat(F, H, 0.04), mat(F, H, 0.04)
+        t[f"{p}.mlp.down_proj.weight"] = mat(H, F, 0.03)
+    return t
+
+
+def tp_check_batches(pkg, seed=29):
+    """Four steps on 160 sequences (two blocks each, prompts of 2..20 tokens): a ragged prefill of the
+    first 48; a mixed batch (those 48 decode one token, the other 112 prefill); a decode batch of 48
+    rows (the small token tiles and, at 2 ranks, the one-shot hand-over); a decode batch of all 160
+    rows (the 256-token tile and more than 128 rows through the hand-over)."""
+    rng = np.random.default_rng(seed)
+    n, first, V = 160, 48, TP_CHECK["vocab_size"]
+    lens = rng.integers(2, 21, n)
+    perm = rng.permutation(TP_CHECK_BLOCKS)[:2 * n].reshape(n, 2)
+    tables = [row.tolist() for row in perm]
+    ids = list(range(1, n + 1))
+    done = np.zeros(n, np.int64)  # tokens each sequence has in the cache so far
+    steps = []
+
+    def step(feed):  # feed: list of (sequence index, number of tokens)
+        toks, pos, cnt, ctx, tbl, sid = [], [], [], [], [], []
+        for s, k in feed:
+            toks += rng.integers(0, V, k).tolist()
+            pos += list(range(int(done[s]), int(done[s]) + k))
+            done[s] += k
+            cnt.append(k), ctx.append(int(done[s])), tbl.append(tables[s]), sid.append(ids[s])
+        steps.append(pkg.ForwardBatch(toks, pos, sid, cnt, ctx, tbl, has_prefill=any(k > 1 for _, k in feed)))
+
+    step([(s, int(lens[s])) for s in range(first)])
+    step([(s, 1) for s in range(first)] + [(s, int(lens[s])) for s in range(first, n)])
+    step([(s, 1) for s in range(first)])
+    step([(s, 1) for s in range(n)])
+    return steps
+
+
+def tp_parity(pkg, backend, dist, rank, world, dtype_name="BF16", model=None, num_blocks=TP_CHECK_BLOCKS, batches=None):
+    """Runs the check model at tp_world = `world` and compares rank 0's logits and every rank's KV arena
+    with the CPU oracle's unsharded forward (the oracle is the checker here, nothing of it is timed).
+    Bars: bf16 build 2e-2 max-abs after softmax and logits within 3e-2 of their range; f32 build 1e-3."""
+    import torch
+
+    m = model or TP_CHECK
+    weights = tp_check_weights(m)
+    box = [pkg.NcclCollectiveId.create() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    dtype = getattr(pkg.DType, dtype_name)
+    meta = pkg.ModelMetadata(architecture="qwen2", name="tp-check", dtype=dtype, **m)
+    batches = batches or tp_check_batches(pkg)
+    max_tokens = max(len(b.tokens) for b in batches)
+    max_seqs = max(len(b.slot_token_counts) for b in batches)
+    dev = pkg.CudaTransformerModel.new(meta, weights, num_blocks, BLOCK, backend, compute_dtype=dtype,
+                                       max_batch_tokens=max_tokens, max_batch_sequences=max_seqs, tp_rank=rank,
+                                       tp_world=world, nccl_unique_id=box[0])
+    got = [dev.forward(b).logits for b in batches]
+    kv_dev = dev.read_kv()
+    del dev
+    lkv = m["num_kv_heads"] // world
+    kv_shape = (m["num_layers"], num_blocks, 2, BLOCK, m["num_kv_heads"], m["head_dim"])
+    kv_ref = torch.zeros(kv_shape, dtype=torch.float32)
+    report = {"ranks": world, "dtype": dtype_name.lower(),
+              "model": f"{m['num_layers']} layers, hidden {m['hidden_size']}, {m['num_attention_heads']}/"
+                       f"{m['num_kv_heads']} heads, head_dim {m['head_dim']}, ffn {m['ffn_dim']}, QKV bias",
+              "steps": [f"{len(b.slot_token_counts)} sequences / {len(b.tokens)} rows" for b in batches]}
+    if rank == 0:
+        from oracle import binding as oracle
+
+        oracle.build()
+        oracle.set_threads(min(os.cpu_count() or 1, 64))
+        ref = oracle.Model(num_blocks=num_blocks, block_size=BLOCK, **m).load(weights)
+        rel = soft = 0.0
+        for b, g in zip(batches, got):
+            exp = ref.forward(oracle.Batch(b.tokens, b.positions, b.slot_token_counts, b.context_lens, b.block_tables))
+            rel = max(rel, float(np.max(np.abs(g - exp)) / np.max(np.abs(exp))))
+            pe, pg = (np.exp(x - x.max(axis=1, keepdims=True)) for x in (exp.astype(np.float64), g.astype(np.float64)))
+            soft = max(soft, float(np.max(np.abs(pe / pe.sum(1, keepdims=True) - pg / pg.sum(1, keepdims=True)))))
+        kv_ref.copy_(torch.from_numpy(np.ascontiguousarray(ref.kv().array()).reshape(kv_shape)))
+        report.update(max_rel_err=rel, softmax_max_abs=soft)
+    dist.broadcast(kv_ref, src=0)
+    mine = kv_ref.numpy()[..., rank * lkv:(rank + 1) * lkv, :]
+    tol = 3e-2 if dtype_name == "BF16" else 1e-4
+    kv_ok = bool(np.array_equal(kv_dev != 0, mine != 0) and np.allclose(kv_dev, mine, atol=tol, rtol=tol))
+    flags = [None] * world
+    dist.all_gather_object(flags, kv_ok)
+    if rank == 0:
+        report["kv_slots_equal"] = all(flags)
+        bars = (2e-2, 3e-2) if dtype_name == "BF16" else (1e-3, 1e-3)
+        report["ok"] = bool(report["softmax_max_abs"] <= bars[0] and report["max_rel_err"] <= bars[1] and all(flags))
+    return report
+
+
 def run_ours(args):
     if args.workload in ("serving", "prefix"):
         return run_serving(args)
@@ -342,6 +496,7 @@ def run_ours(args):
         dist.broadcast_object_list(box, src=0)
         nccl_id = box[0]
     backend = pkg.CudaBackend(local_rank)
+    parity = tp_parity(pkg, backend, dist, rank, world) if world > 1 and not args.no_tp_parity else None
     if args.no_pdl:
         pkg._ffi.lib().orion_cuda_set_programmatic_launch(0)
     if args.attn_stages or args.attn_ctas:
@@ -429,6 +584,23 @@ def run_ours(args):
     gemm_chain_ms = max_over_ranks(model.replay_categories(args.steps, "gemm"))
     attn_chain_ms = max_over_ranks(model.replay_categories(args.steps, "attention"))
     barrier()
+    # (5) the same step at small batches (the projections in their GEMV regime, 16- and 32-token tiles):
+    # device-resident step time and the two kernel families run back to back, 20 steps each
+    small = []
+    if world == 1 and args.shape == "llama3-8b" and args.batch == BATCH and not args.no_small_batch:
+        peak_gbs = measured_peaks()[0]
+        for b in (1, 8, 16):
+            sb = make_decode_batch(pkg, np.random.default_rng(40 + b), num_blocks, contexts[:b], m["vocab_size"])
+            for _ in range(3):
+                model.forward(sb, out=logits)
+            n = 20
+            step_ms = model.replay(n) / n
+            g_ms, a_ms = model.replay_categories(n, "gemm") / n, model.replay_categories(n, "attention") / n
+            wb, kb = weight_bytes_per_step(m), kv_bytes_per_step(m, contexts[:b])
+            small.append({"batch": b, "ms_per_step": step_ms, "tokens_per_s": b / (step_ms / 1000.0),
+                          "gemm_ms": g_ms, "gemm_frac": wb / (g_ms / 1000.0) / 1e9 / peak_gbs,
+                          "attn_ms": a_ms, "attn_frac": kb / (a_ms / 1000.0) / 1e9 / peak_gbs,
+                          "step_frac": (wb + kb) / (step_ms / 1000.0) / 1e9 / peak_gbs})
     model.forward(batch, out=logits)  # leave the buffers holding a real step again
     if rank != 0:
         return 0
@@ -450,11 +622,8 @@ def run_ours(args):
         "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": workload if layers == full_layers else f"{workload}_first{layers}layers",
-                   "batch": nbatch, "context": CONTEXT if args.shape == "llama3-8b" else "U[1024,4096]",
-                   "block_size": BLOCK, "layers": layers, "parallelism": f"tp{world}",
-                   "l2": f"inputs exceed L2: {wbytes / 1e9:.1f} GB of weights + {kbytes / 1e9:.1f} GB of KV read "
-                         f"per step and rank"},
+        "config": headline_config(world, layers, workload, nbatch, CONTEXT if args.shape == "llama3-8b" else "U[1024,4096]",
+                                  full_layers, wbytes, kbytes),
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes,
                 "d2h_bytes_per_step": nbatch * m["vocab_size"] * 4},
         "e2e_greedy": {"value": nbatch * args.steps / greedy_s, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes,
@@ -464,7 +633,7 @@ def run_ours(args):
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel (projection weights streamed once per step)",
                      "achieved": gemm_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                     "frac": gemm_gbs / peak, "traffic": GEMM_TRAFFIC_BYTES_PER_STEP
+                     "frac": gemm_gbs / peak, "traffic": gemm_traffic_bytes_per_step()
                      if world == 1 and args.layers == 32 and args.shape == "llama3-8b" and args.batch == BATCH else None,
                      "algorithmic_bytes_per_step": wbytes, "launches_per_step": gemm_n // max(args.steps, 1),
                      "ms_per_step": gemm_chain_ms / args.steps,
@@ -488,6 +657,10 @@ def run_ours(args):
         "step_breakdown_note": "event pair around every launch in a separate pass: serialises the launches, so "
                                "the parts add up to more than ms_per_step",
     }
+    if small:
+        line["small_batch"] = small
+    if parity is not None:
+        line["tp_parity"] = parity
     if world == 1 and not args.no_attention_sweep:
         line["attention_microbench"] = attention_sweep(pkg, backend, peak)
     if world == 1 and not args.no_cpu_baseline and args.shape == "llama3-8b" and args.batch == BATCH:
@@ -502,6 +675,9 @@ def run_ours(args):
     print(json.dumps(line), file=json_out, flush=True)
     if dist is not None:
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        print(f"tensor-parallel parity failed: {parity}", file=sys.stderr)
+        return 1
     return 0
 
 
@@ -527,8 +703,13 @@ def main():
     ap.add_argument("--layers", type=int, default=32,
                     help="layers of the Llama-3-8B shape to build; fewer than 32 gives a small case with the "
                          "same per-launch kernel shapes, for profiler captures (not a benchmark number)")
+    ap.add_argument("--no-small-batch", action="store_true",
+                    help="skip the batch 1 / 8 / 16 steps that are appended at N=1")
     ap.add_argument("--no-attention-sweep", action="store_true",
                     help="skip the paged-attention microbenchmark sweep that is appended at N=1")
+    ap.add_argument("--no-tp-parity", action="store_true",
+                    help="N > 1: skip the parity check of the tensor-parallel path against the CPU oracle that "
+                         "precedes the timed region (tuning runs)")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (tuning A/B)")
     ap.add_argument("--gemm-ctas", type=int, default=0, help="split-K CTA target (tuning A/B)")
     ap.add_argument("--l2-prefetch-mb", type=int, default=-1, help="L2 weight prefetch per hand-over (tuning A/B)")

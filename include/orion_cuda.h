@@ -253,6 +253,18 @@ int orion_cuda_tp_layout(uint32_t num_attention_heads, uint32_t num_kv_heads, ui
                          uint64_t kv_heads[2], uint64_t ffn[2]);
 /* ncclGetUniqueId for the Collective backing (docs/distributed.md:112-120). */
 int orion_cuda_tp_unique_id(uint8_t id[ORION_NCCL_ID_BYTES]);
+/* Failure handling of the NCCL leg, exercised on the host against a stand-in NCCL (no GPU and no
+ * NCCL library are touched; no reference counterpart: the reference's engine loop only states that
+ * a failed step is logged and the loop goes on, orion-runtime/src/engine.rs:529-535). The library
+ * opens its communicator non-blocking, polls ncclCommGetAsyncError under a host time limit and
+ * calls ncclCommAbort when a rank never arrives, a peer dies or a step does not end; the failing
+ * call returns ORION_ERR_BACKEND and the communicator refuses further work. Scenarios: 0 healthy
+ * group (returns ORION_OK), 1 a rank never joins the rendezvous, 2 a remote error appears while a
+ * step is running, 3 a step never ends. `limit_ms` is the time limit used for both waits;
+ * *aborted reports whether ncclCommAbort ran, *polls how often the state was polled. The real
+ * limits are ORION_TP_INIT_TIMEOUT_S (default 300) and ORION_TP_STEP_TIMEOUT_S (default 60). */
+int orion_cuda_tp_selftest_failure_handling(int scenario, uint64_t limit_ms, uint32_t *aborted,
+                                            uint64_t *polls);
 
 /* ---- op-level entry points (host buffers in, host buffers out) ----
  * The functions of crates/orion-models/src/tensor.rs and attention.rs run

@@ -84,6 +84,7 @@ SIGNATURES = {
     "orion_cuda_attention_set_tuning": (_int, [_int, _u32]),
     "orion_cuda_tp_layout": (_int, [_u32, _u32, _u32, _u32, _u32, _u64p, _u64p, _u64p]),
     "orion_cuda_tp_unique_id": (_int, [_u8p]),
+    "orion_cuda_tp_selftest_failure_handling": (_int, [_int, _u64, C.POINTER(C.c_uint32), _u64p]),
     "orion_cuda_linear": (_int, [_vp, _int, _f32p, _u64, _u64, _f32p, _u64, _u64, _f32p, _u64, _f32p]),
     "orion_cuda_linear_bench": (_int, [_vp, _u64, _u64, _u64, _int, _int, _f32p, C.POINTER(_u32)]),
     "orion_cuda_rms_norm": (_int, [_vp, _int, _f32p, _u64, _u64, _f32p, _u64, C.c_float]),

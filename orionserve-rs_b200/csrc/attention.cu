@@ -14,7 +14,9 @@
 //    merged in shared memory; context splits are merged by decode_combine_kernel.
 #include "kernels.h"
 
+#include <algorithm>
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 namespace orion {
@@ -515,6 +517,8 @@ template int launch_paged_attention_generic<bf16>(const bf16 *, const bf16 *, Kv
 namespace {
 int g_decode_stages = 3;                 // ring depth per warp (2, 3 or 4)
 uint32_t g_decode_cta_target = 2 * 148;  // CTAs the context split aims for (two per SM are resident)
+// Fewest 16-token blocks a context split may hold (tuning A/B: ORION_DECODE_MIN_BLOCKS, 16 = the earlier rule).
+uint32_t g_decode_min_blocks = std::getenv("ORION_DECODE_MIN_BLOCKS") ? (uint32_t)std::max(1, std::atoi(std::getenv("ORION_DECODE_MIN_BLOCKS"))) : 4;
 }  // namespace
 
 bool decode_attention_supported(KvLayout kv, uint32_t q_heads) {
@@ -529,13 +533,14 @@ size_t decode_scratch_floats(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
 
 uint32_t decode_choose_splits(uint32_t rows, uint32_t kv_heads, uint32_t max_position,
                               uint32_t block_size, uint32_t max_splits) {
-  // Aim for about four CTAs per SM so the block scheduler can even out ragged
-  // contexts, but keep at least 16 blocks (4 per warp) in every split.
+  // Aim for two CTAs per SM. A split keeps at least one block per warp (4): at small batches the
+  // kernel is bound by latency, not bandwidth, and the 28 MB that 296 CTAs keep in flight cover a
+  // whole 8k context, so many short splits beat few long ones (batch 1 went from 72 to 256 CTAs).
   const uint32_t ctas = rows * kv_heads;
   if (ctas == 0) return 1;
   uint32_t want = (g_decode_cta_target + ctas - 1) / ctas;
   const uint32_t nblocks = max_position / block_size + 1;
-  const uint32_t cap = nblocks / 16 > 0 ? nblocks / 16 : 1;
+  const uint32_t cap = nblocks / g_decode_min_blocks > 0 ? nblocks / g_decode_min_blocks : 1;
   if (want > cap) want = cap;
   if (want > max_splits) want = max_splits;
   return want < 1 ? 1 : want;

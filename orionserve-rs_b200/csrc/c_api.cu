@@ -399,6 +399,11 @@ int orion_cuda_selftest_bounded_wait(OrionBackend *backend, uint64_t limit_us, u
   return selftest_bounded_wait(limit_us, timed_out, waited_us);
 }
 
+int orion_cuda_tp_selftest_failure_handling(int scenario, uint64_t limit_ms, uint32_t *aborted, uint64_t *polls) {
+  orion::clear_error();
+  return orion::nccl_failure_selftest(scenario, limit_ms, aborted, polls);
+}
+
 int orion_cuda_poll_wait_timeouts(OrionBackend *backend, uint32_t *mask) {
   orion::clear_error();
   ORION_TRY(orion::check_backend(backend));

@@ -147,6 +147,13 @@ class Model final : public ModelBase {
   int upload_slice(T *dst_t, float *dst_f, const void *src, int dtype, uint64_t C, uint64_t r0,
                    uint64_t r1, uint64_t c0, uint64_t c1);
   int run_step(bool want_argmax);
+  // Waits for a stream of this model. Under tensor parallelism the wait watches the communicator
+  // and is bounded in time, so a peer that died cannot hold the host inside a blocking synchronise.
+  int wait_for(cudaStream_t s, const char *stage) {
+    if (nccl_) return nccl_->wait_stream(s, stage);
+    ORION_CUDA_CHECK(stage, cudaStreamSynchronize(s));
+    return ORION_OK;
+  }
   int tp_reduce(uint32_t *splits, size_t slab);
   int setup_peer_handover();
   // Row-parallel projection -> residual + norm. Single GPU: the fused residual/norm kernel.
@@ -371,7 +378,7 @@ int Model<T>::setup_peer_handover() {
   ORION_TRY(alloc(&d_recv, (size_t)kFloatsPerHandle * world));
   ORION_CUDA_CHECK("ipc exchange", cudaMemcpy(d_send, &mine, sizeof mine, cudaMemcpyHostToDevice));
   ORION_TRY(nccl_->all_gather(d_send, d_recv, kFloatsPerHandle, stream_));
-  ORION_CUDA_CHECK("ipc exchange", cudaStreamSynchronize(stream_));
+  ORION_TRY(nccl_->wait_stream(stream_, "ipc exchange"));
   std::vector<cudaIpcMemHandle_t> all((size_t)world);
   ORION_CUDA_CHECK("ipc exchange", cudaMemcpy(all.data(), d_recv, all.size() * sizeof(cudaIpcMemHandle_t),
                                                cudaMemcpyDeviceToHost));
@@ -951,12 +958,12 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
   ORION_TRY(run_step(token_ids_out != nullptr));
   last_launches_ = g_launch_count;
   if (mt.zero_count) {
-    cudaStreamSynchronize(stream_);
+    ORION_TRY(wait_for(stream_, "forward"));
     // transformer.rs:413-417: detected after the layers ran, so KV slots were written.
     return set_error(ORION_ERR_INTERNAL, "a scheduled sequence contributed zero tokens");
   }
   if (d.tp_world > 1 && d.tp_rank != 0) {  // only the leader returns logits (Rank::is_leader)
-    ORION_CUDA_CHECK("forward", cudaStreamSynchronize(stream_));
+    ORION_TRY(wait_for(stream_, "forward"));
   } else {
     if (logits_out && head_chunks_ > 0) {
       const size_t pitch = (size_t)d.vocab_size * sizeof(float);
@@ -966,7 +973,7 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
                                                               (size_t)head_cols_[c] * sizeof(float), S, cudaMemcpyDeviceToHost,
                                                               copy_stream_));
       }
-      ORION_CUDA_CHECK("download logits", cudaStreamSynchronize(copy_stream_));
+      ORION_TRY(wait_for(copy_stream_, "download logits"));
     } else if (logits_out) {
       ORION_CUDA_CHECK("download logits", cudaMemcpyAsync(logits_out, logits_, S * (size_t)d.vocab_size * sizeof(float),
                                                           cudaMemcpyDeviceToHost, stream_));
@@ -974,7 +981,7 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
     if (token_ids_out)
       ORION_CUDA_CHECK("download tokens", cudaMemcpyAsync(token_ids_out, argmax_, S * sizeof(uint32_t),
                                                           cudaMemcpyDeviceToHost, stream_));
-    ORION_CUDA_CHECK("forward", cudaStreamSynchronize(stream_));
+    ORION_TRY(wait_for(stream_, "forward"));
   }
   uint32_t code = 0;
   if (tp_fused_) {
@@ -1011,6 +1018,7 @@ int Model<T>::replay(int iterations, uint32_t category_mask, float *elapsed_ms) 
   }
   only_mask_ = 0;
   ORION_CUDA_CHECK("replay", cudaEventRecord(ev1_, stream_));
+  ORION_TRY(wait_for(stream_, "replay"));
   ORION_CUDA_CHECK("replay", cudaEventSynchronize(ev1_));
   float ms = 0.f;
   ORION_CUDA_CHECK("replay", cudaEventElapsedTime(&ms, ev0_, ev1_));

@@ -2,9 +2,10 @@
 
 Tolerances: integer / index results are bit-exact; the f32 build must match logits
 within 1e-3 relative error; the bf16 build within 2e-2 max-abs after softmax with
-identical greedy tokens, except where the oracle's own top-2 logit gap is below the bf16 logit
-noise (BF16_TIE_MARGIN): there a token may differ, the oracle's token is fed back, and at least
-98 % of all tokens must still be identical. The f32 build is identical on every token.
+identical greedy tokens, except where the oracle's own top-2 logit gap is below what bf16
+storage of the KV cache alone can move two logits by (BF16_TIE_MARGIN, see
+test_bf16_noise_budget.py): there a token may differ, the oracle's token is fed back, and at
+least 98 % of all tokens must still be identical. The f32 build is identical on every token.
 """
 import numpy as np
 import pytest
@@ -16,7 +17,10 @@ pytestmark = pytest.mark.gpu
 
 F32_REL = 1e-3      # f32 build: logits relative error
 BF16_SOFTMAX = 2e-2  # bf16 build: max-abs after softmax
-BF16_TIE_MARGIN = 1e-2  # bf16 build: a greedy token may differ only below this oracle top-2 logit gap
+# bf16 build: a greedy token may differ only below this oracle top-2 logit gap. bf16 rounding of the stored
+# keys and values alone moves a logit of the config-1 model by up to 2.5e-3 (test_bf16_noise_budget.py),
+# so two logits closer than twice that can swap whatever the kernels do.
+BF16_TIE_MARGIN = 5e-3
 
 
 @pytest.fixture(scope="module")
@@ -361,14 +365,16 @@ def test_missing_and_misshapen_tensors_are_model_errors(pkg, backend):
 
 # ---- config 1: tiny Llama, 8 sequences, 32 greedy steps ---------------------------
 
-@pytest.mark.parametrize("dtype_name", ["F32", "BF16"])
-def test_config1_greedy_decode_matches_the_oracle(pkg, backend, oracle, dtype_name):
+@pytest.mark.parametrize("head_dim", [64, 128])  # 64 = configuration 1 as defined (generic attention kernel in both
+@pytest.mark.parametrize("dtype_name", ["F32", "BF16"])  # builds); 128 = the same model on the tuned bf16 kernels
+def test_config1_greedy_decode_matches_the_oracle(pkg, backend, oracle, dtype_name, head_dim):
     dtype = getattr(pkg.DType, dtype_name)
-    weights = c1_tensors(seed=1234, bf16_round=oracle.round_to_bf16 if dtype == pkg.DType.BF16 else None)
-    meta = pkg.ModelMetadata(architecture="llama", name="c1", **C1_META)
+    c1 = dict(C1_META, head_dim=head_dim)
+    weights = c1_tensors(seed=1234, meta=c1, bf16_round=oracle.round_to_bf16 if dtype == pkg.DType.BF16 else None)
+    meta = pkg.ModelMetadata(architecture="llama", name="c1", **c1)
     dev = pkg.CudaTransformerModel.new(meta, weights, 160, 16, backend, compute_dtype=dtype,
                                        max_batch_tokens=1024, max_batch_sequences=8)
-    ref = oracle.Model(num_blocks=160, block_size=16, **C1_META).load(weights)
+    ref = oracle.Model(num_blocks=160, block_size=16, **c1).load(weights)
     oracle.set_threads(8)
     drv = GreedyDriver(num_blocks=160, block_size=16, seed=7, num_sequences=8, prompt_range=(32, 128),
                        vocab=C1_META["vocab_size"])
@@ -597,6 +603,46 @@ def test_qwen2_shape_with_qkv_bias(pkg, backend, oracle):
         b = pkg.ForwardBatch(toks, np.arange(40), [1], [40], [40], [[9, 2, 7]])
         exp = ref.forward(oracle.Batch(toks, np.arange(40), [40], [40], [[9, 2, 7]]))
         assert check(dev.forward(b).logits, exp)
+
+
+def test_qwen2_7b_head_layout_with_qkv_bias_on_the_tuned_bf16_path(pkg, backend, oracle):
+    """28 query / 4 kv heads of 128 with QKV bias (the Qwen2-7B layout), bf16 build: a ragged prefill through
+    the RoPE / KV-write kernel and the prefill attention kernel, then decode steps where the decode attention
+    kernel folds the QKV partial sums, adds the bias, rotates and writes the KV slot itself."""
+    meta_d = dict(hidden_size=512, num_layers=2, num_attention_heads=28, num_kv_heads=4, head_dim=128, vocab_size=1024,
+                  ffn_dim=1024, max_position_embeddings=256, rope_theta=1000000.0, rms_norm_eps=1e-6, has_qkv_bias=True,
+                  tied_lm_head=False, num_blocks=64, block_size=16)
+    t = random_tensors(np.random.default_rng(13), meta_d, std=0.05)
+    t = {k: oracle.round_to_bf16(v) if v.ndim == 2 else v for k, v in t.items()}
+    ref = oracle.Model(**meta_d).load(t)
+    meta = pkg.ModelMetadata(architecture="qwen2", name="q7",
+                             **{k: v for k, v in meta_d.items() if k not in ("num_blocks", "block_size")})
+    dev = pkg.CudaTransformerModel.new(meta, t, 64, 16, backend, compute_dtype=pkg.DType.BF16, max_batch_tokens=256,
+                                       max_batch_sequences=8)
+    oracle.set_threads(8)
+    rng = np.random.default_rng(4)
+    lens = [33, 16, 47, 5, 64, 21]
+    perm = rng.permutation(64).tolist()
+    tables = [[perm.pop() for _ in range(6)] for _ in lens]
+    ids = list(range(1, len(lens) + 1))
+    toks = rng.integers(0, 1024, sum(lens)).tolist()
+    pos = [p for n in lens for p in range(n)]
+    exp = ref.forward(oracle.Batch(toks, pos, lens, lens, tables))
+    got = dev.forward(pkg.ForwardBatch(toks, pos, ids, lens, lens, tables, has_prefill=True)).logits
+    assert float(np.max(np.abs(softmax_rows(got) - softmax_rows(exp)))) < BF16_SOFTMAX and rel_err(got, exp) < 3e-2
+    last = [int(oracle.argmax(r)) for r in exp]
+    for step in range(4):
+        pos = [n + step for n in lens]
+        ctx = [p + 1 for p in pos]
+        exp = ref.forward(oracle.Batch(last, pos, [1] * len(lens), ctx, tables))
+        got = dev.forward(pkg.ForwardBatch(last, pos, ids, [1] * len(lens), ctx, tables, has_prefill=False)).logits
+        assert float(np.max(np.abs(softmax_rows(got) - softmax_rows(exp)))) < BF16_SOFTMAX, f"decode step {step}"
+        assert rel_err(got, exp) < 3e-2, f"decode step {step}"
+        last = [int(oracle.argmax(r)) for r in exp]
+    oracle.set_threads(1)
+    kv_dev, kv_ref = dev.read_kv(), ref.kv().array()
+    assert np.array_equal(kv_dev != 0, kv_ref != 0), "exactly the same slots were written"
+    assert np.allclose(kv_dev, kv_ref, atol=3e-2, rtol=3e-2)
 
 
 def test_cluster_split_k_variant_matches_the_oracle(pkg, backend):

@@ -183,3 +183,27 @@ def test_greedy_driver_is_deterministic_and_consistent():
     assert d.positions == [len(p) for p in a.prompts]
     for s in range(4):
         assert len(d.block_tables[s]) * 16 >= d.context_lens[s]
+
+
+def test_nccl_failures_abort_the_communicator_and_surface_as_backend_errors(pkg):
+    """The failure handling of the NCCL leg, on the host against a stand-in NCCL (no GPU, no library):
+    a rank that never joins, a peer that dies during a step and a step that never ends must each end
+    in ncclCommAbort and EngineError::Backend within the time limit; a healthy group must not."""
+    import time
+
+    lib = pkg._ffi.lib()
+    aborted, polls = ctypes.c_uint32(7), ctypes.c_uint64(0)
+    assert lib.orion_cuda_tp_selftest_failure_handling(0, 200, ctypes.byref(aborted), ctypes.byref(polls)) == 0, \
+        pkg._ffi.last_error()
+    assert aborted.value == 0 and polls.value >= 4  # the rendezvous was polled until every rank had joined
+    for scenario, text in ((1, "did not answer within the time limit"), (2, "remote process exited"),
+                           (3, "did not end within the time limit")):
+        t0 = time.monotonic()
+        rc = lib.orion_cuda_tp_selftest_failure_handling(scenario, 150, ctypes.byref(aborted), ctypes.byref(polls))
+        took = time.monotonic() - t0
+        assert rc == pkg._ffi.ERR_BACKEND, (scenario, rc, pkg._ffi.last_error())
+        msg = pkg._ffi.last_error()
+        assert text in msg and "communicator aborted" in msg and msg.startswith("backend cuda failed at "), msg
+        assert aborted.value == 1 and polls.value > 0
+        assert took < 5.0, f"scenario {scenario} took {took:.2f} s with a 150 ms limit"
+    assert lib.orion_cuda_tp_selftest_failure_handling(9, 10, None, None) == pkg._ffi.ERR_INVALID_REQUEST

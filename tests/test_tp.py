@@ -59,3 +59,26 @@ def test_four_gpu_ranks_match_the_oracle(pkg, dtype, handover):
         pytest.skip("needs four GPUs on the box")
     r = _run_ranks(4, "--mode", "gpu", "--dtype", dtype, handover=handover)
     assert r.returncode == 0, r.stdout[-3000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("handover", ["fused", "nccl"])
+@pytest.mark.parametrize("dtype", ["F32", "BF16"])
+def test_ranks_match_the_oracle_on_the_eight_kv_head_model(pkg, dtype, handover, world):
+    """The benchmark's own parity model (8 kv heads: whole heads at 2, 4 and 8 ranks): a ragged prefill, a
+    mixed batch, a 48-row and a 160-row decode batch; logits of rank 0 and the arena of every rank."""
+    if pkg.device_count() < world:
+        pytest.skip(f"needs {world} GPUs on the box")
+    r = _run_ranks(world, "--mode", "gpu", "--dtype", dtype, "--model", "kv8", handover=handover)
+    assert r.returncode == 0, r.stdout[-3000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("handover", ["fused", "twoshot"])
+def test_two_gpu_ranks_at_one_mi_elements_per_handover(pkg, handover):
+    """256 rows x hidden 4096: the size from which the bf16 build hands over in two shots at 2 ranks."""
+    if pkg.device_count() < 2:
+        pytest.skip("needs two GPUs on the box")
+    r = _run_ranks(2, "--mode", "gpu", "--dtype", "BF16", "--model", "wide", handover=handover)
+    assert r.returncode == 0, r.stdout[-3000:]

@@ -49,10 +49,35 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--mode", choices=("cpu", "gpu"), required=True)
     ap.add_argument("--dtype", choices=("F32", "BF16"), default="F32")
+    ap.add_argument("--model", choices=("small", "kv8", "wide"), default="small",
+                    help="gpu mode: small = 4 kv heads, 3 sequences; kv8 = the benchmark's own check model (8 kv heads, "
+                         "up to 8 ranks, 160-row decode and a mixed batch of 1274 rows); wide = hidden 4096 at 256 rows, "
+                         "1 Mi elements per hand-over")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("gloo", rank=rank, world_size=world)
     pkg = ge.load_package()
+    if args.mode == "gpu" and args.model != "small":
+        import bench
+
+        backend = pkg.CudaBackend(int(os.environ.get("LOCAL_RANK", rank)))
+        if args.model == "kv8":
+            report = bench.tp_parity(pkg, backend, dist, rank, world, args.dtype)
+        else:
+            # 256 one-token sequences at hidden 4096: rows x hidden = 1 Mi elements, where the bf16 build moves
+            # from the one-shot to the two-shot hand-over at 2 ranks; 256 rows is also the largest fused batch
+            wide = dict(bench.TP_CHECK, hidden_size=4096, num_layers=1, num_attention_heads=8, ffn_dim=1024, vocab_size=512)
+            rng = np.random.default_rng(31)
+            n = 256
+            b = pkg.ForwardBatch(rng.integers(0, 512, n).tolist(), [0] * n, list(range(1, n + 1)), [1] * n, [1] * n,
+                                 [[int(x)] for x in rng.permutation(300)[:n]], has_prefill=False)
+            report = bench.tp_parity(pkg, backend, dist, rank, world, args.dtype, model=wide, num_blocks=300, batches=[b])
+        ok = [report.get("ok", True)]
+        dist.broadcast_object_list(ok, src=0)
+        if rank == 0:
+            print(report, file=sys.stderr)
+        dist.destroy_process_group()
+        return 0 if ok[0] else 1
     weights = random_tensors(np.random.default_rng(17), META, std=0.06)
     if args.dtype == "BF16":
         weights = {k: oracle.round_to_bf16(v) if v.ndim == 2 else v for k, v in weights.items()}
