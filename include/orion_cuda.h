@@ -356,16 +356,18 @@ void orion_cuda_attn_bench_destroy(OrionAttnBench *bench);
  * context is cut into (0 = chosen like the allocating path does).
  *
  * The per-split partial results live in a fixed 16 MiB array inside the
- * library (held by every GPU that loads it until the process exits). A call
- * needing more — rows * num_query_heads * splits * 130 floats > 4 Mi floats —
- * is rejected with ORION_ERR_INVALID_REQUEST; splits == 1 needs none.
+ * library (held by every GPU that loads it until the process exits): 16 Ki
+ * arrival counters followed by the partials. A call needing more —
+ * 16384 + rows * num_query_heads * splits * 130 floats > 4 Mi floats — is
+ * rejected with ORION_ERR_INVALID_REQUEST; splits == 1 needs none.
  * The first call on a device looks the array's address up and opts the kernel
  * in to its shared-memory size on that device; make that first call before
  * starting any stream capture. Every call on a device shares the one array:
  * calls whose kernels can overlap on the GPU (different streams without
  * ordering between them) race on it and must be serialised by the caller. The
- * array needs no clearing between calls: each call overwrites every slot it
- * later reads.
+ * array needs no clearing between calls: each call overwrites every partial
+ * slot it later reads, and the counters start at zero when the library is
+ * loaded and are put back to zero by the launch that used them.
  *
  * `device` is made current for the duration of the call and the caller's
  * current device is put back before returning. Nothing the pointers refer to is

@@ -266,11 +266,7 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
       const uint32_t head = hh < group ? kvh * group + hh
                                        : (hh == group ? q_heads + kvh : q_heads + kv.num_kv_heads + kvh);
       const float *p = fq.partial + ((size_t)row * total_heads + head) * kHd;
-      float4 x0 = ld4(p + i), x1 = ld4(p + i + half);
-      for (uint32_t s = 1; s < fq.slabs; ++s) {
-        x0 = add4(x0, ld4(p + s * fq.slab_stride + i));
-        x1 = add4(x1, ld4(p + s * fq.slab_stride + i + half));
-      }
+      float4 x0 = sum_slabs4(p + i, fq.slabs, fq.slab_stride), x1 = sum_slabs4(p + i + half, fq.slabs, fq.slab_stride);
       if (fq.bias) {
         x0 = add4(x0, ld4(fq.bias + (size_t)head * kHd + i));
         x1 = add4(x1, ld4(fq.bias + (size_t)head * kHd + i + half));
@@ -466,6 +462,56 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
       }
     }
   }
+  if (splits > 1 && scratch.counters != nullptr) {
+    // The CTA that arrives last at its (row, kv head) merges the splits of the group's heads: its
+    // partials and everybody else's are visible (fence before the arrival, fence after it), and it
+    // puts the counter back to zero for the next launch.
+    __shared__ uint32_t arrived_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t *counter = scratch.counters + (size_t)row * kv.num_kv_heads + kvh;
+      const uint32_t before = atomicAdd(counter, 1u);
+      arrived_last = before == splits - 1 ? 1u : 0u;
+      if (arrived_last) *counter = 0u;
+    }
+    __syncthreads();
+    if (arrived_last) {
+      __threadfence();
+      // One warp per query head of the group: lane s holds the running max and sum of split s
+      // (at most 32 splits), lane l the four output dims 4l .. 4l + 3 of every split.
+      for (uint32_t g = warp; g < group; g += kWarps) {
+        const uint32_t head = kvh * group + g;
+        const size_t base = ((size_t)row * q_heads + head) * scratch.max_splits;
+        float ms = -INFINITY, ls = 0.f;
+        if (lane < splits) {
+          const float2 ml = __ldcg(reinterpret_cast<const float2 *>(scratch.partial_ml + (base + lane) * 2));
+          ms = ml.x;
+          ls = ml.y;
+        }
+        const float mall = warp_max(ms);
+        const float wgt = (ms == -INFINITY) ? 0.f : fast_exp2(ms - mall);
+        const float L = warp_sum(wgt * ls);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t s0 = 0; s0 < splits; s0 += 8) {
+          float4 x[8];
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j)  // eight independent loads in flight
+            x[j] = s0 + j < splits ? __ldcg(reinterpret_cast<const float4 *>(scratch.partial_out + (base + s0 + j) * kHd) + lane)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j) {
+            const float w = __shfl_sync(0xffffffffu, wgt, (s0 + j) & 31u);
+            if (s0 + j < splits) {
+              acc.x += w * x[j].x; acc.y += w * x[j].y; acc.z += w * x[j].z; acc.w += w * x[j].w;
+            }
+          }
+        }
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        st4<bf16>(out + ((size_t)row * q_heads + head) * kHd + 4 * lane, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
+      }
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kHd)
@@ -517,6 +563,9 @@ template int launch_paged_attention_generic<bf16>(const bf16 *, const bf16 *, Kv
 namespace {
 int g_decode_stages = 3;                 // ring depth per warp (2, 3 or 4)
 uint32_t g_decode_cta_target = 2 * 148;  // CTAs the context split aims for (two per SM are resident)
+// Merge of the context splits by the last CTA to arrive (default) or by a separate kernel
+// (ORION_DECODE_FUSED_COMBINE=0, tuning A/B).
+bool g_decode_fused_combine = std::getenv("ORION_DECODE_FUSED_COMBINE") ? std::atoi(std::getenv("ORION_DECODE_FUSED_COMBINE")) != 0 : true;
 // Fewest 16-token blocks a context split may hold (tuning A/B: ORION_DECODE_MIN_BLOCKS, 16 = the earlier rule).
 uint32_t g_decode_min_blocks = std::getenv("ORION_DECODE_MIN_BLOCKS") ? (uint32_t)std::max(1, std::atoi(std::getenv("ORION_DECODE_MIN_BLOCKS"))) : 4;
 }  // namespace
@@ -528,7 +577,21 @@ bool decode_attention_supported(KvLayout kv, uint32_t q_heads) {
 
 size_t decode_scratch_floats(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
                              uint32_t max_splits) {
-  return (size_t)rows * q_heads * max_splits * (head_dim + 2);
+  return kDecodeCounterWords + (size_t)rows * q_heads * max_splits * (head_dim + 2);
+}
+
+DecodeScratch decode_scratch_at(float *base, uint32_t rows, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
+                                uint32_t splits) {
+  DecodeScratch sc;
+  float *partials = base + kDecodeCounterWords;
+  sc.partial_out = partials;
+  sc.partial_ml = partials + (size_t)rows * q_heads * splits * head_dim;
+  sc.max_splits = splits;
+  // the in-kernel merge keeps one split per lane
+  sc.counters = (g_decode_fused_combine && splits <= 32 && (size_t)rows * kv_heads <= kDecodeCounterWords)
+                    ? reinterpret_cast<uint32_t *>(base)
+                    : nullptr;
+  return sc;
 }
 
 uint32_t decode_choose_splits(uint32_t rows, uint32_t kv_heads, uint32_t max_position,
@@ -584,7 +647,7 @@ int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv,
     default: ORION_TRY(launch_decode_stages<3>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, next, fq, stream)); break;
   }
   ORION_TRY(after_launch("paged_decode"));
-  if (splits > 1) {
+  if (splits > 1 && scratch.counters == nullptr) {
     ORION_CUDA_CHECK("decode_combine", launch_pdl(decode_combine_kernel, dim3(batch.rows, q_heads), dim3(kHd), 0,
                                                   stream, scratch, splits, q_heads, out));
     ORION_TRY(after_launch("decode_combine"));
@@ -657,7 +720,7 @@ int noalloc_decode_attention(int device, const bf16 *q, const bf16 *arena, uint3
                      "heads per kv head");
   if (rows == 0) return ORION_OK;
   if (splits == 0) splits = decode_choose_splits(rows, num_kv_heads, max_position, kBlk, 32);
-  const size_t need = decode_scratch_floats(rows, num_query_heads, kHd, splits);
+  const size_t need = decode_scratch_floats(rows, num_query_heads, kHd, splits);  // counter words included
   if (splits > 1 && need > kNoAllocScratchFloats)
     return set_error(ORION_ERR_INVALID_REQUEST,
                      "allocation-free decode attention: %u rows x %u heads x %u splits needs %zu scratch "
@@ -674,9 +737,10 @@ int noalloc_decode_attention(int device, const bf16 *q, const bf16 *arena, uint3
     base = static_cast<float *>(p);
     g_noalloc_ptr[device].store(base, std::memory_order_release);
   }
-  // Every (row, head, split) slot is written by the decode kernel before the
-  // combine kernel reads it, so nothing has to be cleared between calls.
-  DecodeScratch sc{base, base + (size_t)rows * num_query_heads * splits * kHd, splits};
+  // Every (row, head, split) slot is written before the merge reads it, and the arrival
+  // counters at the head of the array are put back to zero by the launch that used them (the
+  // array starts zeroed when the module is loaded), so nothing has to be cleared between calls.
+  DecodeScratch sc = decode_scratch_at(base, rows, num_query_heads, num_kv_heads, kHd, splits);
   AttnBatch ab{query_positions, seq_of_row, tables_flat, table_offsets, rows, max_position};
   return launch_paged_attention_decode(q, arena, kv, 0, ab, num_query_heads, splits, sc, out, stream);
 }

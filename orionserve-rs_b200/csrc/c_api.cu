@@ -185,8 +185,10 @@ int op_attention(const float *kv, uint64_t num_blocks, uint64_t block_size, uint
     if (decode && decode_attention_supported(lay, (uint32_t)qh)) {
       const uint32_t splits = decode_choose_splits((uint32_t)rows, (uint32_t)kvh, max_pos, (uint32_t)block_size, 32);
       Dev<float> scratch;
-      ORION_TRY(scratch.alloc(decode_scratch_floats((uint32_t)rows, (uint32_t)qh, (uint32_t)hd, splits)));
-      DecodeScratch sc{scratch.p, scratch.p + rows * qh * splits * hd, splits};
+      const size_t scratch_floats = decode_scratch_floats((uint32_t)rows, (uint32_t)qh, (uint32_t)hd, splits);
+      ORION_TRY(scratch.alloc(scratch_floats));
+      ORION_CUDA_CHECK("clear attention scratch", cudaMemset(scratch.p, 0, scratch_floats * sizeof(float)));
+      DecodeScratch sc = decode_scratch_at(scratch.p, (uint32_t)rows, (uint32_t)qh, (uint32_t)kvh, (uint32_t)hd, splits);
       ORION_TRY(launch_paged_attention_decode(qt.p, arena.p, lay, 0, ab, (uint32_t)qh, splits, sc, ot.p, 0));
       ORION_CUDA_CHECK("paged_attention", cudaDeviceSynchronize());
       uint32_t code = 0;
@@ -708,8 +710,9 @@ int orion_cuda_attn_bench_create(OrionBackend *backend, uint32_t num_query_heads
   ORION_CUDA_CHECK("allocate", cudaMalloc(reinterpret_cast<void **>(&b->meta), meta.size() * sizeof(uint32_t)));
   ORION_CUDA_CHECK("upload", cudaMemcpy(b->meta, meta.data(), meta.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
   b->splits = decode_choose_splits(batch, num_kv_heads, b->max_position, block_size, 32);
-  ORION_CUDA_CHECK("allocate", cudaMalloc(reinterpret_cast<void **>(&b->scratch),
-                                          decode_scratch_floats(batch, num_query_heads, head_dim, b->splits) * sizeof(float)));
+  const size_t scratch_bytes = decode_scratch_floats(batch, num_query_heads, head_dim, b->splits) * sizeof(float);
+  ORION_CUDA_CHECK("allocate", cudaMalloc(reinterpret_cast<void **>(&b->scratch), scratch_bytes));
+  ORION_CUDA_CHECK("clear attention scratch", cudaMemset(b->scratch, 0, scratch_bytes));
   // K and V once per kv head and context token, q in and out once, one table entry per block.
   b->algorithmic_bytes = total_tokens * num_kv_heads * head_dim * 2 * 2 + (uint64_t)qn * 2 * 2 + total_entries * 4;
   ORION_CUDA_CHECK("create event", cudaEventCreate(&b->ev0));
@@ -722,7 +725,7 @@ int orion_cuda_attn_bench_create(OrionBackend *backend, uint32_t num_query_heads
 static int attn_bench_launch(OrionAttnBench *b) {
   const uint32_t n = b->batch;
   AttnBatch ab{b->meta, b->meta + n, b->meta + 2 * n + (n + 1), b->meta + 2 * n, n, b->max_position};
-  DecodeScratch sc{b->scratch, b->scratch + (size_t)n * b->q_heads * b->splits * b->lay.head_dim, b->splits};
+  DecodeScratch sc = decode_scratch_at(b->scratch, n, b->q_heads, b->lay.num_kv_heads, b->lay.head_dim, b->splits);
   return launch_paged_attention_decode(b->q, b->arena, b->lay, 0, ab, b->q_heads, b->splits, sc, b->out, 0);
 }
 

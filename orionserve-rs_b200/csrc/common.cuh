@@ -130,6 +130,30 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Sum of `n` f32 slabs at `p` (slab stride `stride` floats), in slab order, four floats per call.
+// The loads of a batch are unconditional (a slab index past the end re-reads the last slab and its
+// value is dropped), so they are independent straight-line code and a batch costs one memory round
+// trip rather than one per slab.
+constexpr int kSlabBatch = 8;
+__device__ __forceinline__ float4 sum_slabs4(const float *p, uint32_t n, size_t stride) {
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (uint32_t j0 = 0; j0 < n; j0 += kSlabBatch) {
+    float4 x[kSlabBatch];
+#pragma unroll
+    for (int j = 0; j < kSlabBatch; ++j) {
+      const uint32_t slab = j0 + j < n ? j0 + j : n - 1;
+      x[j] = *reinterpret_cast<const float4 *>(p + (size_t)slab * stride);
+    }
+#pragma unroll
+    for (int j = 0; j < kSlabBatch; ++j) {
+      if (j0 + j < n) {
+        acc.x += x[j].x; acc.y += x[j].y; acc.z += x[j].z; acc.w += x[j].w;
+      }
+    }
+  }
+  return acc;
+}
+
 // ---- PTX wrappers ------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {

@@ -4,6 +4,8 @@
 // conversion / layout helpers used at load time and by the parity tests.
 #include "kernels.h"
 
+#include <cstdlib>
+
 #include <cfloat>
 
 namespace orion {
@@ -151,9 +153,7 @@ residual_rmsnorm_vec_kernel(const float *__restrict__ partial, uint32_t splits, 
     if (idx < nvec) {
       v[c] = ld4(h + 4 * (size_t)idx);
       if (partial) {
-        const float *p = partial + (size_t)src_row * H + 4 * (size_t)idx;
-        float4 add = ld4(p);
-        for (uint32_t s = 1; s < splits; ++s) add = add4(add, ld4(p + s * split_stride));
+        const float4 add = sum_slabs4(partial + (size_t)src_row * H + 4 * (size_t)idx, splits, split_stride);
         v[c] = add4(v[c], add);  // hidden += proj, transformer.rs:330-332
         if (!row_map) *reinterpret_cast<float4 *>(h + 4 * (size_t)idx) = v[c];
       }
@@ -191,11 +191,7 @@ rope_kvwrite_vec_kernel(const float *__restrict__ partial, uint32_t splits, size
   if (head >= total_heads) return;
   const uint32_t i = (threadIdx.x % tph) * 4;
   const float *p = partial + ((size_t)row * total_heads + head) * hd;
-  float4 x0 = ld4(p + i), x1 = ld4(p + i + half);
-  for (uint32_t s = 1; s < splits; ++s) {
-    x0 = add4(x0, ld4(p + s * split_stride + i));
-    x1 = add4(x1, ld4(p + s * split_stride + i + half));
-  }
+  float4 x0 = sum_slabs4(p + i, splits, split_stride), x1 = sum_slabs4(p + i + half, splits, split_stride);
   if (bias) {  // acc + bias, tensor.rs:126
     x0 = add4(x0, ld4(bias + (size_t)head * hd + i));
     x1 = add4(x1, ld4(bias + (size_t)head * hd + i + half));

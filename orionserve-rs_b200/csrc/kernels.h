@@ -156,10 +156,20 @@ struct DecodeScratch {
   float *partial_out;  // [rows][q_heads][max_splits][head_dim]
   float *partial_ml;   // [rows][q_heads][max_splits][2]  (running max, running sum)
   uint32_t max_splits;
+  // [rows * kv_heads] arrival counters, zero between launches: the last CTA of a (row, kv head) to
+  // finish merges the splits itself, so no separate combine launch follows. Null = combine kernel.
+  uint32_t *counters;
 };
+// A scratch buffer starts with kDecodeCounterWords counter words (which must be zero when the buffer
+// is first used and are left zero by every launch), followed by the partial results.
+constexpr uint32_t kDecodeCounterWords = 16384;
 bool decode_attention_supported(KvLayout kv, uint32_t q_heads);
+// Floats a scratch buffer needs, counter words included.
 size_t decode_scratch_floats(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
                              uint32_t max_splits);
+// Lays the parts of a scratch buffer of at least decode_scratch_floats(...) floats out.
+DecodeScratch decode_scratch_at(float *base, uint32_t rows, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
+                                uint32_t splits);
 uint32_t decode_choose_splits(uint32_t rows, uint32_t kv_heads, uint32_t max_position,
                               uint32_t block_size, uint32_t max_splits);
 // With `partial` set the kernel takes the row's q, k and v straight from the QKV projection's

@@ -339,6 +339,7 @@ int Model<T>::init() {
       dscratch_floats_ = std::max(dscratch_floats_, decode_scratch_floats(r, lq_, d.head_dim, s));
     }
     ORION_TRY(alloc(&dscratch_, dscratch_floats_));
+    ORION_CUDA_CHECK("clear attention scratch", cudaMemsetAsync(dscratch_, 0, dscratch_floats_ * sizeof(float), stream_));
   }
 
   if (d.tp_world > 1) {
@@ -700,7 +701,7 @@ int Model<T>::run_step(bool want_argmax) {
                                        slot_slot, rope_cos_, rope_sin_, qbuf_, arena_, kv_, l, Tn, lq_, stream_); }));
     if (tuned_decode) {
       if constexpr (kBf16) {
-        DecodeScratch sc{dscratch_, dscratch_ + (size_t)Tn * lq_ * dsplits * hd, dsplits};
+        DecodeScratch sc = decode_scratch_at(dscratch_, Tn, lq_, lkv_, hd, dsplits);
         FusedQkv fq;
         if (fuse_qkv) {
           fq.partial = partial_;
@@ -721,7 +722,7 @@ int Model<T>::run_step(bool want_argmax) {
           const uint32_t r0 = meta_.dec_row0, n = meta_.dec_rows;
           AttnBatch sub{positions + r0, m + meta_.seq_of_row + r0, ab.tables_flat, ab.table_offsets, n, meta_.max_position};
           const uint32_t sp = fit_context_splits(n, decode_choose_splits(n, lkv_, meta_.max_position, d.block_size, 32));
-          DecodeScratch sc{dscratch_, dscratch_ + (size_t)n * lq_ * sp * hd, sp};
+          DecodeScratch sc = decode_scratch_at(dscratch_, n, lq_, lkv_, hd, sp);
           ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_decode(qbuf_ + (size_t)r0 * qd, arena_, kv_, l, sub, lq_, sp, sc,
                                                                                        attn_ + (size_t)r0 * qd, stream_); }));
         }

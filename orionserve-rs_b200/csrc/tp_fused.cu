@@ -122,24 +122,6 @@ __device__ __forceinline__ void st_row4<bf16>(bf16 *dst, float4 v) {
   *reinterpret_cast<uint2 *>(dst) = packed;
 }
 
-// Sum of `n` f32 slabs at `p` (stride `stride`), four floats per thread, loads issued in
-// independent batches of 8.
-__device__ __forceinline__ float4 sum_slabs_local(const float *p, uint32_t n, size_t stride) {
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (uint32_t j0 = 0; j0 < n; j0 += 8) {
-    float4 x[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      x[j] = (j0 + j < n) ? *reinterpret_cast<const float4 *>(p + (size_t)(j0 + j) * stride)
-                          : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      acc.x += x[j].x; acc.y += x[j].y; acc.z += x[j].z; acc.w += x[j].w;
-    }
-  }
-  return acc;
-}
-
 // One CTA per batch row.
 template <typename T, typename Acc>
 __global__ void __launch_bounds__(1024)
@@ -161,7 +143,7 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
     const uint32_t idx = threadIdx.x + c * blockDim.x;
     if (idx < nvec) {
       const size_t off = (size_t)row * H + 4 * (size_t)idx;
-      v[c] = sum_slabs_local(partial + off, splits, split_stride);
+      v[c] = sum_slabs4(partial + off, splits, split_stride);
       const size_t at = parity_base + (size_t)peers.rank * slot + off * 2;
       for (int r = 0; r < peers.world; ++r)
         if (r != peers.rank) {
@@ -251,7 +233,7 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
     const uint32_t idx = threadIdx.x + c * blockDim.x;
     if (idx < nvec) {
       const size_t off = (size_t)row * H + 4 * (size_t)idx;
-      v[c] = sum_slabs_local(partial + off, splits, split_stride);
+      v[c] = sum_slabs4(partial + off, splits, split_stride);
       const int owner = (int)(idx / per);
       if (owner != peers.rank)
         send_group<Packed>(peers.inbox[owner] + scatter + (size_t)peers.rank * slot, off, v[c], epoch);
