@@ -130,6 +130,14 @@ void orion_cuda_model_destroy(OrionModel *model);
 int orion_cuda_selftest_bounded_wait(OrionBackend *backend, uint64_t limit_us, uint32_t *timed_out,
                                      uint32_t *waited_us);
 
+/* The same self-test for the peer polls of the tensor-parallel hand-over (no reference counterpart):
+ * one thread polls inbox units that no peer ever writes, in both unit formats, with a limit of
+ * `limit_us` per poll (1 .. 1 000 000). Both polls must give up, *timed_out = 1 reports that the
+ * device's hand-over time-out word was set (it is cleared again), *waited_us the time both polls
+ * took together, and the device must stay usable. Needs one GPU only. */
+int orion_cuda_selftest_peer_wait(OrionBackend *backend, uint64_t limit_us, uint32_t *timed_out,
+                                  uint32_t *waited_us);
+
 /* Reads and clears the time-out words of the backend's device (no reference counterpart): bit 0 the
  * projection GEMM, bit 1 decode attention, bit 2 prefill attention, bit 3 the tensor-parallel
  * hand-over. A set bit means a bounded device-side wait of that kernel family gave up since the last
@@ -253,6 +261,27 @@ int orion_cuda_tp_layout(uint32_t num_attention_heads, uint32_t num_kv_heads, ui
                          uint64_t kv_heads[2], uint64_t ffn[2]);
 /* ncclGetUniqueId for the Collective backing (docs/distributed.md:112-120). */
 int orion_cuda_tp_unique_id(uint8_t id[ORION_NCCL_ID_BYTES]);
+/* Collective (orion-distributed/src/lib.rs:231-254) backed by NCCL over NVLink, one handle per rank
+ * and process, created on the backend's device from the id of orion_cuda_tp_unique_id. Buffers are
+ * HOST f32 slices like the trait's (the call uploads, runs the collective on the device and brings
+ * the result back); world 1 behaves like SingleRank (lib.rs:257-292): every operation is a copy.
+ * all_reduce_sum (lib.rs:243): in place. all_gather (lib.rs:247): out holds world * count_per_rank
+ * floats in rank order. reduce_scatter_sum (lib.rs:250): input holds world * count_per_rank floats,
+ * out receives this rank's count_per_rank summed floats. barrier (lib.rs:253). A peer that does not
+ * answer within the limits described at orion_cuda_tp_selftest_failure_handling ends the call with
+ * ORION_ERR_BACKEND. The model's own all-reduces run on device-resident data and do not go through
+ * these entry points. */
+typedef struct OrionCollective OrionCollective;
+int orion_cuda_collective_create(OrionBackend *backend, const uint8_t id[ORION_NCCL_ID_BYTES],
+                                 uint32_t rank, uint32_t world, OrionCollective **out);
+void orion_cuda_collective_destroy(OrionCollective *collective);
+int orion_cuda_collective_all_reduce_sum(OrionCollective *collective, float *buffer, uint64_t count);
+int orion_cuda_collective_all_gather(OrionCollective *collective, const float *local,
+                                     uint64_t count_per_rank, float *out);
+int orion_cuda_collective_reduce_scatter_sum(OrionCollective *collective, const float *input,
+                                             uint64_t count_per_rank, float *out);
+int orion_cuda_collective_barrier(OrionCollective *collective);
+
 /* Failure handling of the NCCL leg, exercised on the host against a stand-in NCCL (no GPU and no
  * NCCL library are touched; no reference counterpart: the reference's engine loop only states that
  * a failed step is logged and the loop goes on, orion-runtime/src/engine.rs:529-535). The library

@@ -15,7 +15,7 @@ from .types import DType, Device, ForwardBatch, ForwardOutput, ModelMetadata
 from .backend import CudaBackend, device_count, is_available
 from .model import CudaTransformerModel, HfConfig, read_safetensors, write_safetensors
 from .validate import Tolerance, ValidationReport, validate
-from .distributed import (Collective, CommunicationEstimate, NcclCollectiveId, ParallelLayout, Rank,
+from .distributed import (Collective, CommunicationEstimate, NcclCollective, NcclCollectiveId, ParallelLayout, Rank,
                           Shard, ShardStrategy, SingleRank, shard_dimension)
 from . import engine, errors, ops
 from .engine import Engine, KvCacheManager, SamplingParams, Scheduler, SchedulerConfig, hash_block
@@ -26,7 +26,7 @@ __all__ = [
     "DType", "Device", "ForwardBatch", "ForwardOutput", "ModelMetadata", "CudaBackend",
     "device_count", "is_available", "CudaTransformerModel", "HfConfig", "read_safetensors",
     "write_safetensors", "Tolerance", "ValidationReport", "validate", "Collective",
-    "CommunicationEstimate", "NcclCollectiveId", "ParallelLayout", "Rank", "Shard", "ShardStrategy",
+    "CommunicationEstimate", "NcclCollective", "NcclCollectiveId", "ParallelLayout", "Rank", "Shard", "ShardStrategy",
     "SingleRank", "shard_dimension", "ops", "PagedAttentionBench", "CacheExhausted", "ContextLengthExceeded",
     "QueueFull", "engine", "errors", "Engine", "KvCacheManager", "SamplingParams", "Scheduler", "SchedulerConfig",
     "hash_block",

@@ -68,6 +68,7 @@ SIGNATURES = {
     "orion_cuda_model_forward_greedy": (_int, [_vp, *_BATCH, _u32p, _vp, _u64]),
     "orion_cuda_model_load_checkpoint": (_int, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
     "orion_cuda_poll_wait_timeouts": (_int, [_vp, C.POINTER(C.c_uint32)]),
+    "orion_cuda_selftest_peer_wait": (_int, [_vp, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "orion_cuda_selftest_bounded_wait": (_int, [_vp, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "orion_cuda_model_replay": (_int, [_vp, _int, _f32p]),
     "orion_cuda_model_replay_categories": (_int, [_vp, _int, C.c_uint32, _f32p]),
@@ -84,6 +85,12 @@ SIGNATURES = {
     "orion_cuda_attention_set_tuning": (_int, [_int, _u32]),
     "orion_cuda_tp_layout": (_int, [_u32, _u32, _u32, _u32, _u32, _u64p, _u64p, _u64p]),
     "orion_cuda_tp_unique_id": (_int, [_u8p]),
+    "orion_cuda_collective_create": (_int, [_vp, _u8p, _u32, _u32, C.POINTER(_vp)]),
+    "orion_cuda_collective_destroy": (None, [_vp]),
+    "orion_cuda_collective_all_reduce_sum": (_int, [_vp, _f32p, _u64]),
+    "orion_cuda_collective_all_gather": (_int, [_vp, _f32p, _u64, _f32p]),
+    "orion_cuda_collective_reduce_scatter_sum": (_int, [_vp, _f32p, _u64, _f32p]),
+    "orion_cuda_collective_barrier": (_int, [_vp]),
     "orion_cuda_tp_selftest_failure_handling": (_int, [_int, _u64, C.POINTER(C.c_uint32), _u64p]),
     "orion_cuda_linear": (_int, [_vp, _int, _f32p, _u64, _u64, _f32p, _u64, _u64, _f32p, _u64, _f32p]),
     "orion_cuda_linear_bench": (_int, [_vp, _u64, _u64, _u64, _int, _int, _f32p, C.POINTER(_u32)]),

@@ -61,5 +61,12 @@ class CudaBackend:
         check(_ffi.lib().orion_cuda_selftest_bounded_wait(self._h, limit_us, C.byref(t), C.byref(w)))
         return bool(t.value), int(w.value)
 
+    def selftest_peer_wait(self, limit_us: int):
+        """The same for the peer polls of the tensor-parallel hand-over (inbox units that no peer
+        ever writes); returns ``(timed_out, waited_us)``."""
+        t, w = C.c_uint32(), C.c_uint32()
+        check(_ffi.lib().orion_cuda_selftest_peer_wait(self._h, limit_us, C.byref(t), C.byref(w)))
+        return bool(t.value), int(w.value)
+
     def supports_dtype(self, dtype: DType) -> bool:
         return bool(_ffi.lib().orion_cuda_backend_supports_dtype(self._h, int(dtype)))

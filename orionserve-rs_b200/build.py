@@ -18,6 +18,8 @@ FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std
          "-I", "/usr/include"]
 
 
+if os.environ.get("ORION_EXTRA_NVCC_FLAGS"):  # e.g. -DNAME for a compile-time A/B (rebuild with --force)
+    FLAGS.extend(os.environ["ORION_EXTRA_NVCC_FLAGS"].split())
 if os.environ.get("ORION_TRACE"):  # phase traces of the GEMM and the hand-over kernels (rebuild with --force)
     FLAGS.append("-DORION_TRACE")
 

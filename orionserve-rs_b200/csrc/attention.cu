@@ -206,7 +206,13 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
   const uint32_t *table = batch.tables_flat + batch.table_offsets[batch.seq_of_row[row]];
   const uint32_t nblocks = (ctx + kBlk - 1) / kBlk;
   // Context split: a contiguous range of blocks; warps interleave inside it.
-  const uint32_t per_split = (nblocks + splits - 1) / splits;
+  // Splits of this row: with a length-proportional plan a row is cut into pieces of about
+  // blocks_per_split blocks (a short context is not cut at all, a long one up to gridDim.z times), so
+  // the CTAs of a ragged batch carry similar amounts; CTAs beyond the row's count have nothing to do.
+  const uint32_t bps = scratch.blocks_per_split;
+  const uint32_t my_splits = bps ? min(max((nblocks + bps / 2) / bps, 1u), splits) : splits;
+  if (split >= my_splits) return;
+  const uint32_t per_split = (nblocks + my_splits - 1) / my_splits;
   const uint32_t b_begin = min(split * per_split, nblocks);
   const uint32_t b_end = min(b_begin + per_split, nblocks);
 
@@ -450,7 +456,7 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
         L += wgt * mml[(w * kMaxGroup + g) * 2 + 1];
       }
       const uint32_t head = kvh * group + g;
-      if (splits == 1) {
+      if (my_splits == 1) {
         out[((size_t)row * q_heads + head) * kHd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
       } else {
         const size_t pi = ((size_t)row * q_heads + head) * scratch.max_splits + split;
@@ -462,7 +468,7 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
       }
     }
   }
-  if (splits > 1 && scratch.counters != nullptr) {
+  if (my_splits > 1 && scratch.counters != nullptr) {
     // The CTA that arrives last at its (row, kv head) merges the splits of the group's heads: its
     // partials and everybody else's are visible (fence before the arrival, fence after it), and it
     // puts the counter back to zero for the next launch.
@@ -472,7 +478,7 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
     if (threadIdx.x == 0) {
       uint32_t *counter = scratch.counters + (size_t)row * kv.num_kv_heads + kvh;
       const uint32_t before = atomicAdd(counter, 1u);
-      arrived_last = before == splits - 1 ? 1u : 0u;
+      arrived_last = before == my_splits - 1 ? 1u : 0u;
       if (arrived_last) *counter = 0u;
     }
     __syncthreads();
@@ -484,7 +490,7 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
         const uint32_t head = kvh * group + g;
         const size_t base = ((size_t)row * q_heads + head) * scratch.max_splits;
         float ms = -INFINITY, ls = 0.f;
-        if (lane < splits) {
+        if (lane < my_splits) {
           const float2 ml = __ldcg(reinterpret_cast<const float2 *>(scratch.partial_ml + (base + lane) * 2));
           ms = ml.x;
           ls = ml.y;
@@ -493,16 +499,16 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
         const float wgt = (ms == -INFINITY) ? 0.f : fast_exp2(ms - mall);
         const float L = warp_sum(wgt * ls);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t s0 = 0; s0 < splits; s0 += 8) {
+        for (uint32_t s0 = 0; s0 < my_splits; s0 += 8) {
           float4 x[8];
 #pragma unroll
           for (uint32_t j = 0; j < 8; ++j)  // eight independent loads in flight
-            x[j] = s0 + j < splits ? __ldcg(reinterpret_cast<const float4 *>(scratch.partial_out + (base + s0 + j) * kHd) + lane)
+            x[j] = s0 + j < my_splits ? __ldcg(reinterpret_cast<const float4 *>(scratch.partial_out + (base + s0 + j) * kHd) + lane)
                                    : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
           for (uint32_t j = 0; j < 8; ++j) {
             const float w = __shfl_sync(0xffffffffu, wgt, (s0 + j) & 31u);
-            if (s0 + j < splits) {
+            if (s0 + j < my_splits) {
               acc.x += w * x[j].x; acc.y += w * x[j].y; acc.z += w * x[j].z; acc.w += w * x[j].w;
             }
           }
@@ -515,11 +521,16 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
 }
 
 __global__ void __launch_bounds__(kHd)
-decode_combine_kernel(DecodeScratch scratch, uint32_t splits, uint32_t q_heads,
+decode_combine_kernel(DecodeScratch scratch, uint32_t splits, uint32_t q_heads, const uint32_t *__restrict__ query_positions,
                       bf16 *__restrict__ out) {
   pdl_trigger();
   pdl_wait();
   const uint32_t row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+  if (scratch.blocks_per_split) {  // the row's own split count, as the decode kernel computed it
+    const uint32_t nblocks = query_positions[row] / kBlk + 1, bps = scratch.blocks_per_split;
+    splits = min(max((nblocks + bps / 2) / bps, 1u), splits);
+    if (splits == 1) return;  // written by the decode kernel itself
+  }
   const size_t base = ((size_t)row * q_heads + head) * scratch.max_splits;
   float mall = -INFINITY;
   for (uint32_t s = 0; s < splits; ++s) mall = fmaxf(mall, scratch.partial_ml[(base + s) * 2]);
@@ -581,8 +592,9 @@ size_t decode_scratch_floats(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
 }
 
 DecodeScratch decode_scratch_at(float *base, uint32_t rows, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
-                                uint32_t splits) {
+                                uint32_t splits, uint32_t blocks_per_split) {
   DecodeScratch sc;
+  sc.blocks_per_split = splits > 1 ? blocks_per_split : 0;
   float *partials = base + kDecodeCounterWords;
   sc.partial_out = partials;
   sc.partial_ml = partials + (size_t)rows * q_heads * splits * head_dim;
@@ -601,12 +613,43 @@ uint32_t decode_choose_splits(uint32_t rows, uint32_t kv_heads, uint32_t max_pos
   // whole 8k context, so many short splits beat few long ones (batch 1 went from 72 to 256 CTAs).
   const uint32_t ctas = rows * kv_heads;
   if (ctas == 0) return 1;
-  uint32_t want = (g_decode_cta_target + ctas - 1) / ctas;
+  // nearest count, not the next one up: 256 CTAs (64 rows x 4 kv heads) already reach every SM and
+  // run as one resident wave; cutting each context in two only added partial results to merge
+  uint32_t want = (g_decode_cta_target + ctas / 2) / ctas;
   const uint32_t nblocks = max_position / block_size + 1;
   const uint32_t cap = nblocks / g_decode_min_blocks > 0 ? nblocks / g_decode_min_blocks : 1;
   if (want > cap) want = cap;
   if (want > max_splits) want = max_splits;
   return want < 1 ? 1 : want;
+}
+
+DecodePlan decode_plan(uint32_t rows, uint32_t kv_heads, uint64_t total_blocks, uint32_t max_position,
+                       uint32_t block_size, uint32_t max_splits) {
+  DecodePlan p{1, 0};
+  const uint64_t ctas = (uint64_t)rows * kv_heads;
+  if (ctas == 0 || total_blocks == 0) return p;
+  // Fewer rows than SMs: every row is cut alike (measured better than pieces of equal length on
+  // 8 ragged rows, 0.73 vs 0.65 of the copy peak: the short rows' pieces end early and their
+  // merges overlap the long rows' streams).
+  if (ctas < 148) {
+    p.splits = decode_choose_splits(rows, kv_heads, max_position, block_size, max_splits);
+    return p;
+  }
+  // Blocks one piece should hold: what makes about g_decode_cta_target CTAs out of the batch's blocks
+  // (fills the machine when the batch is small), but never more than the mean row, so that in a
+  // ragged batch the long rows are cut down to the size of the others. Rows of equal length are cut
+  // only when there are too few of them to reach every SM.
+  uint64_t per = (total_blocks * kv_heads + g_decode_cta_target - 1) / g_decode_cta_target;
+  const uint64_t mean_row = (total_blocks + rows - 1) / rows;
+  if (per > mean_row) per = mean_row;
+  if (per < g_decode_min_blocks) per = g_decode_min_blocks;
+  const uint32_t nblocks = max_position / block_size + 1;  // the longest row
+  uint32_t most = (uint32_t)((nblocks + per / 2) / per);
+  if (most > max_splits) most = max_splits;
+  if (most <= 1) return p;
+  p.splits = most;
+  p.blocks_per_split = (uint32_t)per;
+  return p;
 }
 
 namespace {
@@ -649,7 +692,7 @@ int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv,
   ORION_TRY(after_launch("paged_decode"));
   if (splits > 1 && scratch.counters == nullptr) {
     ORION_CUDA_CHECK("decode_combine", launch_pdl(decode_combine_kernel, dim3(batch.rows, q_heads), dim3(kHd), 0,
-                                                  stream, scratch, splits, q_heads, out));
+                                                  stream, scratch, splits, q_heads, batch.query_positions, out));
     ORION_TRY(after_launch("decode_combine"));
   }
   return ORION_OK;

@@ -1,5 +1,6 @@
 // extern "C" entry points declared in include/orion_cuda.h.
 #include <cstring>
+#include <memory>
 #include <new>
 #include <vector>
 
@@ -183,12 +184,16 @@ int op_attention(const float *kv, uint64_t num_blocks, uint64_t block_size, uint
   bool done = false;
   if constexpr (sizeof(T) == 2) {
     if (decode && decode_attention_supported(lay, (uint32_t)qh)) {
-      const uint32_t splits = decode_choose_splits((uint32_t)rows, (uint32_t)kvh, max_pos, (uint32_t)block_size, 32);
+      uint64_t total_blocks = 0;
+      for (uint64_t r = 0; r < rows; ++r) total_blocks += qpos[r] / block_size + 1;
+      const DecodePlan plan = decode_plan((uint32_t)rows, (uint32_t)kvh, total_blocks, max_pos, (uint32_t)block_size, 32);
+      const uint32_t splits = plan.splits;
       Dev<float> scratch;
       const size_t scratch_floats = decode_scratch_floats((uint32_t)rows, (uint32_t)qh, (uint32_t)hd, splits);
       ORION_TRY(scratch.alloc(scratch_floats));
       ORION_CUDA_CHECK("clear attention scratch", cudaMemset(scratch.p, 0, scratch_floats * sizeof(float)));
-      DecodeScratch sc = decode_scratch_at(scratch.p, (uint32_t)rows, (uint32_t)qh, (uint32_t)kvh, (uint32_t)hd, splits);
+      DecodeScratch sc = decode_scratch_at(scratch.p, (uint32_t)rows, (uint32_t)qh, (uint32_t)kvh, (uint32_t)hd, splits,
+                                           plan.blocks_per_split);
       ORION_TRY(launch_paged_attention_decode(qt.p, arena.p, lay, 0, ab, (uint32_t)qh, splits, sc, ot.p, 0));
       ORION_CUDA_CHECK("paged_attention", cudaDeviceSynchronize());
       uint32_t code = 0;
@@ -239,7 +244,7 @@ using namespace orion;
 struct OrionAttnBench {
   OrionBackend *backend = nullptr;
   KvLayout lay{};
-  uint32_t q_heads = 0, batch = 0, splits = 1, max_position = 0;
+  uint32_t q_heads = 0, batch = 0, splits = 1, blocks_per_split = 0, max_position = 0;
   bf16 *arena = nullptr, *q = nullptr, *out = nullptr;
   uint32_t *meta = nullptr;  // positions | seq_of_row | offsets | tables
   float *scratch = nullptr;
@@ -252,6 +257,49 @@ struct OrionAttnBench {
     if (ev1) cudaEventDestroy(ev1);
   }
 };
+
+// ---- Collective over NCCL (orion-distributed/src/lib.rs:231-254), host buffers in and out ----
+
+struct OrionCollective {
+  int ordinal = 0;
+  cudaStream_t stream = nullptr;
+  orion::NcclCollective nccl;
+  float *dev = nullptr;
+  size_t cap = 0;
+  ~OrionCollective() {
+    cudaSetDevice(ordinal);
+    if (dev) cudaFree(dev);
+    if (stream) cudaStreamDestroy(stream);
+  }
+  int reserve(size_t floats) {
+    if (cap >= floats) return ORION_OK;
+    if (dev) cudaFree(dev);
+    dev = nullptr;
+    cap = 0;
+    ORION_CUDA_CHECK("allocate", cudaMalloc(reinterpret_cast<void **>(&dev), (floats ? floats : 1) * sizeof(float)));
+    cap = floats;
+    return ORION_OK;
+  }
+};
+
+namespace {
+// in: `in_count` floats from the host; the collective; out: `out_count` floats back to the host.
+template <typename F>
+int collective_round_trip(OrionCollective *c, const float *in, size_t in_count, float *out, size_t out_count,
+                          const char *stage, F &&run) {
+  orion::clear_error();
+  if (!c || (in_count && !in) || (out_count && !out)) return orion::set_error(ORION_ERR_INVALID_REQUEST, "null argument");
+  ORION_CUDA_CHECK("set device", cudaSetDevice(c->ordinal));
+  ORION_TRY(c->reserve(in_count + out_count));
+  float *d_in = c->dev, *d_out = c->dev + in_count;
+  if (in_count)
+    ORION_CUDA_CHECK(stage, cudaMemcpyAsync(d_in, in, in_count * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  ORION_TRY(run(d_in, d_out));
+  if (out_count)
+    ORION_CUDA_CHECK(stage, cudaMemcpyAsync(out, d_out, out_count * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+  return c->nccl.wait_stream(c->stream, stage);
+}
+}  // namespace
 
 extern "C" {
 
@@ -399,6 +447,60 @@ int orion_cuda_selftest_bounded_wait(OrionBackend *backend, uint64_t limit_us, u
   clear_error();
   ORION_TRY(check_backend(backend));
   return selftest_bounded_wait(limit_us, timed_out, waited_us);
+}
+
+int orion_cuda_collective_create(OrionBackend *backend, const uint8_t id[ORION_NCCL_ID_BYTES], uint32_t rank,
+                                 uint32_t world, OrionCollective **out) {
+  orion::clear_error();
+  ORION_TRY(orion::check_backend(backend));
+  if (!id || !out) return orion::set_error(ORION_ERR_INVALID_REQUEST, "null argument");
+  *out = nullptr;
+  if (world == 0) return orion::set_error(ORION_ERR_INVALID_REQUEST, "world_size must be at least 1");  // Rank::new
+  if (rank >= world)
+    return orion::set_error(ORION_ERR_INVALID_REQUEST, "rank %u is out of range for world size %u", rank, world);
+  std::unique_ptr<OrionCollective> c(new (std::nothrow) OrionCollective());
+  if (!c) return orion::set_error(ORION_ERR_INTERNAL, "out of host memory");
+  c->ordinal = backend->ordinal;
+  ORION_CUDA_CHECK("create stream", cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  if (world > 1) ORION_TRY(c->nccl.init(id, (int)rank, (int)world));
+  *out = c.release();
+  return ORION_OK;
+}
+
+void orion_cuda_collective_destroy(OrionCollective *c) { delete c; }
+
+int orion_cuda_collective_all_reduce_sum(OrionCollective *c, float *buffer, uint64_t count) {
+  return collective_round_trip(c, buffer, count, nullptr, 0, "all_reduce_sum", [&](float *d_in, float *) -> int {
+    ORION_TRY(c->nccl.all_reduce_sum(d_in, count, c->stream));
+    if (count)  // in place: the sum goes back into the caller's buffer
+      ORION_CUDA_CHECK("all_reduce_sum", cudaMemcpyAsync(buffer, d_in, count * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+    return ORION_OK;
+  });
+}
+
+int orion_cuda_collective_all_gather(OrionCollective *c, const float *local, uint64_t count_per_rank, float *out) {
+  const size_t world = c ? (size_t)c->nccl.world() : 1;
+  return collective_round_trip(c, local, count_per_rank, out, count_per_rank * world, "all_gather",
+                               [&](float *d_in, float *d_out) { return c->nccl.all_gather(d_in, d_out, count_per_rank, c->stream); });
+}
+
+int orion_cuda_collective_reduce_scatter_sum(OrionCollective *c, const float *input, uint64_t count_per_rank, float *out) {
+  const size_t world = c ? (size_t)c->nccl.world() : 1;
+  return collective_round_trip(c, input, count_per_rank * world, out, count_per_rank, "reduce_scatter_sum",
+                               [&](float *d_in, float *d_out) { return c->nccl.reduce_scatter_sum(d_in, d_out, count_per_rank, c->stream); });
+}
+
+int orion_cuda_collective_barrier(OrionCollective *c) {
+  orion::clear_error();
+  if (!c) return orion::set_error(ORION_ERR_INVALID_REQUEST, "null argument");
+  ORION_CUDA_CHECK("set device", cudaSetDevice(c->ordinal));
+  return c->nccl.barrier(c->stream);
+}
+
+int orion_cuda_selftest_peer_wait(OrionBackend *backend, uint64_t limit_us, uint32_t *timed_out, uint32_t *waited_us) {
+  orion::clear_error();
+  ORION_TRY(orion::check_backend(backend));
+  return orion::selftest_peer_wait(limit_us, timed_out, waited_us);
 }
 
 int orion_cuda_tp_selftest_failure_handling(int scenario, uint64_t limit_ms, uint32_t *aborted, uint64_t *polls) {
@@ -709,7 +811,11 @@ int orion_cuda_attn_bench_create(OrionBackend *backend, uint32_t num_query_heads
   meta.insert(meta.end(), b->tables.begin(), b->tables.end());
   ORION_CUDA_CHECK("allocate", cudaMalloc(reinterpret_cast<void **>(&b->meta), meta.size() * sizeof(uint32_t)));
   ORION_CUDA_CHECK("upload", cudaMemcpy(b->meta, meta.data(), meta.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
-  b->splits = decode_choose_splits(batch, num_kv_heads, b->max_position, block_size, 32);
+  {
+    const DecodePlan plan = decode_plan(batch, num_kv_heads, total_entries, b->max_position, block_size, 32);
+    b->splits = plan.splits;
+    b->blocks_per_split = plan.blocks_per_split;
+  }
   const size_t scratch_bytes = decode_scratch_floats(batch, num_query_heads, head_dim, b->splits) * sizeof(float);
   ORION_CUDA_CHECK("allocate", cudaMalloc(reinterpret_cast<void **>(&b->scratch), scratch_bytes));
   ORION_CUDA_CHECK("clear attention scratch", cudaMemset(b->scratch, 0, scratch_bytes));
@@ -725,7 +831,8 @@ int orion_cuda_attn_bench_create(OrionBackend *backend, uint32_t num_query_heads
 static int attn_bench_launch(OrionAttnBench *b) {
   const uint32_t n = b->batch;
   AttnBatch ab{b->meta, b->meta + n, b->meta + 2 * n + (n + 1), b->meta + 2 * n, n, b->max_position};
-  DecodeScratch sc = decode_scratch_at(b->scratch, n, b->q_heads, b->lay.num_kv_heads, b->lay.head_dim, b->splits);
+  DecodeScratch sc = decode_scratch_at(b->scratch, n, b->q_heads, b->lay.num_kv_heads, b->lay.head_dim, b->splits,
+                                       b->blocks_per_split);
   return launch_paged_attention_decode(b->q, b->arena, b->lay, 0, ab, b->q_heads, b->splits, sc, b->out, 0);
 }
 

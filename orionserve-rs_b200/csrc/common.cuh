@@ -131,9 +131,8 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // Sum of `n` f32 slabs at `p` (slab stride `stride` floats), in slab order, four floats per call.
-// The loads of a batch are unconditional (a slab index past the end re-reads the last slab and its
-// value is dropped), so they are independent straight-line code and a batch costs one memory round
-// trip rather than one per slab.
+// The loads of a batch of eight slabs are independent of one another, so a batch costs one memory
+// round trip rather than eight.
 constexpr int kSlabBatch = 8;
 __device__ __forceinline__ float4 sum_slabs4(const float *p, uint32_t n, size_t stride) {
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -141,14 +140,12 @@ __device__ __forceinline__ float4 sum_slabs4(const float *p, uint32_t n, size_t 
     float4 x[kSlabBatch];
 #pragma unroll
     for (int j = 0; j < kSlabBatch; ++j) {
-      const uint32_t slab = j0 + j < n ? j0 + j : n - 1;
-      x[j] = *reinterpret_cast<const float4 *>(p + (size_t)slab * stride);
+      x[j] = (j0 + j < n) ? *reinterpret_cast<const float4 *>(p + (size_t)(j0 + j) * stride)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
     for (int j = 0; j < kSlabBatch; ++j) {
-      if (j0 + j < n) {
-        acc.x += x[j].x; acc.y += x[j].y; acc.z += x[j].z; acc.w += x[j].w;
-      }
+      acc.x += x[j].x; acc.y += x[j].y; acc.z += x[j].z; acc.w += x[j].w;
     }
   }
   return acc;

@@ -159,6 +159,9 @@ struct DecodeScratch {
   // [rows * kv_heads] arrival counters, zero between launches: the last CTA of a (row, kv head) to
   // finish merges the splits itself, so no separate combine launch follows. Null = combine kernel.
   uint32_t *counters;
+  // 0: every row is cut into max_splits pieces; else a row of n blocks is cut into
+  // round(n / blocks_per_split) pieces (at least 1, at most max_splits).
+  uint32_t blocks_per_split;
 };
 // A scratch buffer starts with kDecodeCounterWords counter words (which must be zero when the buffer
 // is first used and are left zero by every launch), followed by the partial results.
@@ -169,7 +172,15 @@ size_t decode_scratch_floats(uint32_t rows, uint32_t q_heads, uint32_t head_dim,
                              uint32_t max_splits);
 // Lays the parts of a scratch buffer of at least decode_scratch_floats(...) floats out.
 DecodeScratch decode_scratch_at(float *base, uint32_t rows, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
-                                uint32_t splits);
+                                uint32_t splits, uint32_t blocks_per_split = 0);
+// Length-proportional context split for a ragged batch: `splits` = pieces of the longest row (the
+// grid's z extent), `blocks_per_split` = blocks a piece should hold. `total_blocks` = sum over the
+// rows of their block counts. splits == 1 means no row is cut.
+struct DecodePlan {
+  uint32_t splits, blocks_per_split;
+};
+DecodePlan decode_plan(uint32_t rows, uint32_t kv_heads, uint64_t total_blocks, uint32_t max_position,
+                       uint32_t block_size, uint32_t max_splits);
 uint32_t decode_choose_splits(uint32_t rows, uint32_t kv_heads, uint32_t max_position,
                               uint32_t block_size, uint32_t max_splits);
 // With `partial` set the kernel takes the row's q, k and v straight from the QKV projection's
@@ -208,6 +219,7 @@ struct TpPeers {
   uint32_t *inbox[kMaxTpWorld];
   int rank, world;
   uint32_t slot_floats;
+  uint64_t wait_limit_ns = 2000000000ull;  // how long a poll for a peer's unit may last before it gives up
 };
 // All-reduce of the partial sums over ranks and split-K slabs + residual add + RMSNorm for
 // `rows` batch rows; every rank ends up with the full residual stream in `hidden` and all
@@ -222,6 +234,10 @@ int tp_poll_error(uint32_t *code);
 // Launches a kernel whose only thread waits on a barrier that nothing arrives at, with the given
 // limit: the bounded wait must give up (timed_out = 1) and the kernel must end normally.
 int selftest_bounded_wait(uint64_t limit_us, uint32_t *timed_out, uint32_t *waited_us);
+// The same for the peer polls of the tensor-parallel hand-over: one thread polls inbox units that
+// nobody writes (both unit formats); each poll must give up after the limit, the device error word
+// must be set (and is cleared again), and the kernel must end normally.
+int selftest_peer_wait(uint64_t limit_us, uint32_t *timed_out, uint32_t *waited_us);
 
 // ---- GEMM ----------------------------------------------------------------------
 

@@ -228,6 +228,7 @@ class Model final : public ModelBase {
   size_t meta_cap_ = 0;
   struct Meta {
     uint32_t rows = 0, seqs = 0, max_position = 0;
+    uint64_t total_blocks = 0;  // sum over the rows of the blocks their contexts span
     bool decode = false, zero_count = false;
     size_t tokens = 0, positions = 0, slot_block = 0, slot_slot = 0, seq_of_row = 0, last_rows = 0,
            offsets = 0, tables = 0, tiles = 0, total = 0;
@@ -335,7 +336,9 @@ int Model<T>::init() {
   ORION_TRY(alloc(&partial_, partial_floats_));
   if (kBf16 && decode_attention_supported(kv_, lq_)) {
     for (uint32_t r = 1; r <= Sm; ++r) {
-      const uint32_t s = decode_choose_splits(r, lkv_, d.max_position_embeddings, d.block_size, 32);
+      // room for the uniform split of r equally long rows, and for up to eight pieces of the long
+      // rows of a ragged batch (a plan that wants more is cut back to what fits)
+      const uint32_t s = std::max(decode_choose_splits(r, lkv_, d.max_position_embeddings, d.block_size, 32), 8u);
       dscratch_floats_ = std::max(dscratch_floats_, decode_scratch_floats(r, lq_, d.head_dim, s));
     }
     ORION_TRY(alloc(&dscratch_, dscratch_floats_));
@@ -675,7 +678,9 @@ int Model<T>::run_step(bool want_argmax) {
     if (p.splits == 1) p.cluster_reduce = false, p.out_slabs = 1;
     return p;
   };
-  const uint32_t dsplits = tuned_decode ? fit_context_splits(Tn, decode_choose_splits(Tn, lkv_, meta_.max_position, d.block_size, 32)) : 1;
+  const DecodePlan dplan = tuned_decode ? decode_plan(Tn, lkv_, meta_.total_blocks, meta_.max_position, d.block_size, 32)
+                                        : DecodePlan{1, 0};
+  const uint32_t dsplits = fit_context_splits(Tn, dplan.splits);
   // L2 prefetch of the next projection's weights: only where the projections are bandwidth-bound
   // (decode-sized batches), and never more than a fraction of L2 per hand-over.
   const size_t budget = (kBf16 && Tn <= 256) ? g_prefetch_budget : 0;
@@ -701,7 +706,7 @@ int Model<T>::run_step(bool want_argmax) {
                                        slot_slot, rope_cos_, rope_sin_, qbuf_, arena_, kv_, l, Tn, lq_, stream_); }));
     if (tuned_decode) {
       if constexpr (kBf16) {
-        DecodeScratch sc = decode_scratch_at(dscratch_, Tn, lq_, lkv_, hd, dsplits);
+        DecodeScratch sc = decode_scratch_at(dscratch_, Tn, lq_, lkv_, hd, dsplits, dplan.blocks_per_split);
         FusedQkv fq;
         if (fuse_qkv) {
           fq.partial = partial_;
@@ -886,6 +891,7 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
     h[mt.slot_block + row] = b.block_tables_flat[t0 + logical];
     h[mt.slot_slot + row] = pos % B;
     mt.max_position = std::max(mt.max_position, pos);
+    mt.total_blocks += logical + 1;
   }
   for (uint64_t row = 0; row < Tn; ++row)  // embed, transformer.rs:211-217
     if (b.tokens[row] >= d.vocab_size)

@@ -51,7 +51,7 @@ __device__ __forceinline__ uint4 ld_unit2(const uint32_t *src) {
   return v;
 }
 // Polls two 16-byte slots (four self-validating units) until all carry `epoch`.
-__device__ __forceinline__ float4 receive4(const uint32_t *src, uint32_t epoch) {
+__device__ __forceinline__ float4 receive4(const uint32_t *src, uint32_t epoch, uint64_t limit_ns) {
   uint4 lo = ld_unit2(src), hi = ld_unit2(src + 4);
   if (lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch) {
     const uint64_t start = global_timer_ns();
@@ -59,7 +59,7 @@ __device__ __forceinline__ float4 receive4(const uint32_t *src, uint32_t epoch) 
     do {
       lo = ld_unit2(src);
       hi = ld_unit2(src + 4);
-      if ((++spins & 1023u) == 0 && global_timer_ns() - start > 2000000000ull) {
+      if ((++spins & 1023u) == 0 && global_timer_ns() - start > limit_ns) {
         atomicOr(&g_tp_error, 1u);
         break;
       }
@@ -90,8 +90,8 @@ __device__ __forceinline__ void send_group(uint32_t *base, size_t element, float
   }
 }
 template <bool Packed>
-__device__ __forceinline__ float4 receive_group(const uint32_t *base, size_t element, uint32_t epoch) {
-  if (!Packed) return receive4(base + element * 2, epoch);
+__device__ __forceinline__ float4 receive_group(const uint32_t *base, size_t element, uint32_t epoch, uint64_t limit_ns) {
+  if (!Packed) return receive4(base + element * 2, epoch, limit_ns);
   const uint32_t *src = base + element;
   uint4 u = ld_unit2(src);
   if (u.y != epoch || u.w != epoch) {
@@ -99,7 +99,7 @@ __device__ __forceinline__ float4 receive_group(const uint32_t *base, size_t ele
     uint32_t spins = 0;
     do {
       u = ld_unit2(src);
-      if ((++spins & 1023u) == 0 && global_timer_ns() - start > 2000000000ull) {
+      if ((++spins & 1023u) == 0 && global_timer_ns() - start > limit_ns) {
         atomicOr(&g_tp_error, 1u);
         break;
       }
@@ -122,8 +122,10 @@ __device__ __forceinline__ void st_row4<bf16>(bf16 *dst, float4 v) {
   *reinterpret_cast<uint2 *>(dst) = packed;
 }
 
-// One CTA per batch row.
-template <typename T, typename Acc>
+// One CTA per batch row. Packed: the sums travel as bf16 pairs (half the NVLink bytes); every rank
+// then adds the bf16-rounded sums of ALL ranks, its own included, so the residual streams stay
+// bit-identical across ranks.
+template <typename T, typename Acc, bool Packed>
 __global__ void __launch_bounds__(1024)
 tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ partial,
                                      uint32_t splits, size_t split_stride, float *__restrict__ hidden,
@@ -144,12 +146,12 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
     if (idx < nvec) {
       const size_t off = (size_t)row * H + 4 * (size_t)idx;
       v[c] = sum_slabs4(partial + off, splits, split_stride);
-      const size_t at = parity_base + (size_t)peers.rank * slot + off * 2;
       for (int r = 0; r < peers.world; ++r)
-        if (r != peers.rank) {
-          st_unit2(peers.inbox[r] + at, v[c].x, v[c].y, epoch);
-          st_unit2(peers.inbox[r] + at + 4, v[c].z, v[c].w, epoch);
-        }
+        if (r != peers.rank) send_group<Packed>(peers.inbox[r] + parity_base + (size_t)peers.rank * slot, off, v[c], epoch);
+      if (Packed) {  // what the peers receive is what this rank adds for itself
+        const float2 lo = unpack_bf16x2(pack_bf16x2(v[c].x, v[c].y)), hi = unpack_bf16x2(pack_bf16x2(v[c].z, v[c].w));
+        v[c] = make_float4(lo.x, lo.y, hi.x, hi.y);
+      }
     }
   }
   trace(1);
@@ -164,7 +166,8 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
       float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int r = 0; r < peers.world; ++r) {
         const float4 x = r == peers.rank ? v[c]
-                                         : receive4(peers.inbox[peers.rank] + parity_base + (size_t)r * slot + off * 2, epoch);
+                                         : receive_group<Packed>(peers.inbox[peers.rank] + parity_base + (size_t)r * slot, off, epoch,
+                                                                 peers.wait_limit_ns);
         add.x += x.x; add.y += x.y; add.z += x.z; add.w += x.w;
       }
       const float4 old = *reinterpret_cast<const float4 *>(h + 4 * (size_t)idx);
@@ -250,7 +253,7 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
       for (int r = 0; r < peers.world; ++r) {
         const float4 x = r == peers.rank
                              ? v[c]
-                             : receive_group<Packed>(peers.inbox[peers.rank] + scatter + (size_t)r * slot, off, epoch);
+                             : receive_group<Packed>(peers.inbox[peers.rank] + scatter + (size_t)r * slot, off, epoch, peers.wait_limit_ns);
         add.x += x.x; add.y += x.y; add.z += x.z; add.w += x.w;
       }
       if (Packed) {  // every rank must add exactly what the peers receive
@@ -273,7 +276,7 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
       const size_t off = (size_t)row * H + 4 * (size_t)idx;
       const float4 add = (int)(idx / per) == peers.rank
                              ? v[c]
-                             : receive_group<Packed>(peers.inbox[peers.rank] + gather, off, epoch);
+                             : receive_group<Packed>(peers.inbox[peers.rank] + gather, off, epoch, peers.wait_limit_ns);
       const float4 old = *reinterpret_cast<const float4 *>(h + 4 * (size_t)idx);
       v[c] = make_float4(old.x + add.x, old.y + add.y, old.z + add.z, old.w + add.w);
       *reinterpret_cast<float4 *>(h + 4 * (size_t)idx) = v[c];
@@ -316,7 +319,7 @@ int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, c
   uint32_t threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
   if (threads < 32) threads = 32;
   using Acc = typename std::conditional<sizeof(T) == 4, double, float>::type;
-  // What the two-shot kernel of the bf16 build sends: bf16 pairs (default; half the NVLink bytes, measured
+  // What the kernels of the bf16 build send: bf16 pairs (default; half the NVLink bytes, measured
   // 29.2 -> 27.6 ms per batch-128 step of the 70B shape at 2 ranks) or, with ORION_TP_PAYLOAD=f32, f32 values.
   // The f32 build always sends f32.
   static const bool packed = [] {
@@ -331,9 +334,13 @@ int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, c
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
                      launch_pdl(tp_twoshot_kernel<T, Acc, false>, dim3(rows), dim3(threads), 0, stream, peers, epoch,
                                 partial, splits, split_stride, hidden, norm_w, eps, out, rows, hidden_size));
+  else if (sizeof(T) == 2 && packed)
+    ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
+                     launch_pdl(tp_allreduce_residual_rmsnorm_kernel<T, Acc, true>, dim3(rows), dim3(threads), 0, stream, peers,
+                                epoch, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size));
   else
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
-                     launch_pdl(tp_allreduce_residual_rmsnorm_kernel<T, Acc>, dim3(rows), dim3(threads), 0, stream, peers,
+                     launch_pdl(tp_allreduce_residual_rmsnorm_kernel<T, Acc, false>, dim3(rows), dim3(threads), 0, stream, peers,
                                 epoch, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size));
   count_launch();
   ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm", cudaGetLastError());
@@ -345,6 +352,37 @@ template int launch_tp_allreduce_residual_rmsnorm<float>(const TpPeers &, uint32
 template int launch_tp_allreduce_residual_rmsnorm<bf16>(const TpPeers &, uint32_t, const float *, uint32_t, size_t,
                                                         float *, const float *, float, bf16 *, uint32_t, uint32_t,
                                                         bool, cudaStream_t);
+
+namespace {
+// One thread polls inbox units that nobody ever writes, in both unit formats, with the given limit.
+__global__ void tp_peer_wait_probe_kernel(const uint32_t *inbox, uint32_t epoch, uint64_t limit_ns, uint32_t *waited_us) {
+  if (threadIdx.x != 0) return;
+  const uint64_t t0 = global_timer_ns();
+  const float4 a = receive4(inbox, epoch, limit_ns);                     // f32 units
+  const float4 b = receive_group<true>(inbox + 64, 0, epoch, limit_ns);  // packed bf16 units
+  waited_us[0] = (uint32_t)((global_timer_ns() - t0) / 1000);
+  waited_us[1] = __float_as_uint(a.x + b.x);  // keeps both polls alive
+}
+}  // namespace
+
+int selftest_peer_wait(uint64_t limit_us, uint32_t *timed_out, uint32_t *waited_us) {
+  if (limit_us == 0 || limit_us > 1000000)
+    return set_error(ORION_ERR_INVALID_REQUEST, "the probe takes a limit between 1 us and 1 s");
+  uint32_t code = 0;
+  ORION_TRY(tp_poll_error(&code));  // start from a clear error word
+  uint32_t *d = nullptr;
+  ORION_CUDA_CHECK("allocate", cudaMalloc(reinterpret_cast<void **>(&d), 256 * sizeof(uint32_t)));
+  cudaMemset(d, 0, 256 * sizeof(uint32_t));  // epoch 0 is never sent, so no unit ever validates
+  tp_peer_wait_probe_kernel<<<1, 32>>>(d, 5u, limit_us * 1000, d + 128);
+  uint32_t h[2] = {0, 0};
+  cudaError_t e = cudaMemcpy(h, d + 128, sizeof h, cudaMemcpyDeviceToHost);
+  cudaFree(d);
+  ORION_CUDA_CHECK("peer wait probe", e);
+  ORION_TRY(tp_poll_error(&code));  // the word the host reads after a step (and clears)
+  if (timed_out) *timed_out = code ? 1u : 0u;
+  if (waited_us) *waited_us = h[0];
+  return ORION_OK;
+}
 
 int tp_poll_error(uint32_t *code) {
 #ifdef ORION_TRACE

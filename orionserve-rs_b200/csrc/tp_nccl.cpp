@@ -40,10 +40,17 @@ NcclApi &real_api() {
   static NcclApi a;
   static std::once_flag once;
   std::call_once(once, [] {
-    // A process that already holds NCCL (for instance through its tensor
-    // framework) gets that copy back; otherwise the system library is opened.
-    a.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-    if (!a.handle) a.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    // A process that already holds NCCL (for instance through its tensor framework) gets that copy
+    // back. Otherwise ORION_NCCL_LIBRARY names the file to open, else the loader's libnccl.so.2. The
+    // library is opened privately: a different NCCL that the process loads later under the same
+    // name must not find this one's symbols in its way.
+    a.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+    if (!a.handle) {
+      const char *path = std::getenv("ORION_NCCL_LIBRARY");
+      if (path && *path) a.handle = dlopen(path, RTLD_NOW | RTLD_LOCAL);
+    }
+    if (!a.handle) a.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+    if (!a.handle) a.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_LOCAL);
     if (!a.handle) return;
 #define ORION_NCCL_SYM(field, name)                                        \
   a.field = reinterpret_cast<decltype(a.field)>(dlsym(a.handle, name));   \
@@ -77,7 +84,7 @@ uint64_t ms_since(Clock::time_point t0) {
 
 }  // namespace
 
-NcclCollective::NcclCollective() : NcclCollective(&real_api()) {
+NcclCollective::NcclCollective() {  // the library is looked up by init(): a single rank never needs it
   init_limit_ms_ = env_seconds_ms("ORION_TP_INIT_TIMEOUT_S", 300);
   step_limit_ms_ = env_seconds_ms("ORION_TP_STEP_TIMEOUT_S", 60);
 }
@@ -130,7 +137,8 @@ int NcclCollective::unique_id(uint8_t id[128]) {
 }
 
 int NcclCollective::init(const uint8_t id[128], int rank, int world) {
-  if (!api_ || !api_->ok)
+  if (!api_) api_ = &real_api();
+  if (!api_->ok)
     return set_error(ORION_ERR_BACKEND, "backend cuda failed at nccl load: libnccl.so.2 not found");
   ncclUniqueId u;
   std::memcpy(&u, id, 128);

@@ -186,6 +186,53 @@ class TorchCollective(Collective):
         self._dist.barrier(group=self._group)
 
 
+class NcclCollective(Collective):
+    """The Collective trait over NCCL and NVLink (``orion_cuda_collective_*``): one handle per rank,
+    on the backend's device; host f32 arrays in and out like the trait's slices."""
+
+    def __init__(self, backend, unique_id: bytes, rank: Rank):
+        self._rank = rank
+        self._h = C.c_void_p()
+        idbuf = (C.c_uint8 * _ffi.NCCL_ID_BYTES)(*(unique_id or bytes(_ffi.NCCL_ID_BYTES)))
+        check(_ffi.lib().orion_cuda_collective_create(backend._h, idbuf, rank.index, rank.world_size,
+                                                      C.byref(self._h)))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            _ffi.lib().orion_cuda_collective_destroy(self._h)
+            self._h = None
+
+    def rank(self) -> Rank:
+        return self._rank
+
+    @staticmethod
+    def _f32(a: np.ndarray, writable: bool) -> np.ndarray:
+        if a.dtype != np.float32 or not a.flags.c_contiguous or (writable and not a.flags.writeable):
+            raise InternalError("collective buffers are contiguous f32 arrays")
+        return a
+
+    def all_reduce_sum(self, buffer: np.ndarray) -> None:
+        b = self._f32(buffer, True)
+        check(_ffi.lib().orion_cuda_collective_all_reduce_sum(self._h, b.ctypes.data_as(C.POINTER(C.c_float)), b.size))
+
+    def all_gather(self, local: np.ndarray, out: np.ndarray) -> None:
+        if out.size != local.size * self._rank.world_size:
+            raise InternalError("all_gather output must hold world_size slices")
+        a, o = self._f32(local, False), self._f32(out, True)
+        F = C.POINTER(C.c_float)
+        check(_ffi.lib().orion_cuda_collective_all_gather(self._h, a.ctypes.data_as(F), a.size, o.ctypes.data_as(F)))
+
+    def reduce_scatter_sum(self, inp: np.ndarray, out: np.ndarray) -> None:
+        if inp.size != out.size * self._rank.world_size:
+            raise InternalError("reduce_scatter input must hold world_size slices")
+        a, o = self._f32(inp, False), self._f32(out, True)
+        F = C.POINTER(C.c_float)
+        check(_ffi.lib().orion_cuda_collective_reduce_scatter_sum(self._h, a.ctypes.data_as(F), o.size, o.ctypes.data_as(F)))
+
+    def barrier(self) -> None:
+        check(_ffi.lib().orion_cuda_collective_barrier(self._h))
+
+
 class NcclCollectiveId:
     """The 128-byte ``ncclUniqueId`` rank 0 creates and every rank passes to its model."""
 

@@ -57,6 +57,18 @@ def test_a_device_wait_that_cannot_complete_gives_up_and_the_device_stays_usable
         backend.selftest_bounded_wait(0)
 
 
+def test_a_poll_for_a_peer_that_never_writes_gives_up_and_the_device_stays_usable(pkg, backend):
+    """The peer polls of the tensor-parallel hand-over (both unit formats) on an inbox nobody writes,
+    5 ms per poll: both give up, the hand-over's time-out word is set, and the device goes on working.
+    One GPU, no peer, no fault."""
+    timed_out, waited_us = backend.selftest_peer_wait(5_000)
+    assert timed_out and 10_000 <= waited_us < 200_000
+    backend.synchronize()
+    assert np.array_equal(pkg.ops.argmax(backend, np.array([[1.0, 3.0, 2.0]], np.float32)), [1])
+    again, _ = backend.selftest_peer_wait(1_000)
+    assert again, "the time-out word is cleared by the read and set again by the next time-out"
+
+
 # ---- op-level parity: tensor.rs ---------------------------------------------------
 
 def test_linear_f32_is_bit_exact(pkg, backend, oracle, kats):

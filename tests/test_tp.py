@@ -82,3 +82,31 @@ def test_two_gpu_ranks_at_one_mi_elements_per_handover(pkg, handover):
         pytest.skip("needs two GPUs on the box")
     r = _run_ranks(2, "--mode", "gpu", "--dtype", "BF16", "--model", "wide", handover=handover)
     assert r.returncode == 0, r.stdout[-3000:]
+
+
+@pytest.mark.gpu
+def test_collective_trait_over_nccl_on_two_gpus(pkg):
+    """all_reduce_sum / all_gather / reduce_scatter_sum / barrier of the Collective trait through the C boundary."""
+    if pkg.device_count() < 2:
+        pytest.skip("needs two GPUs on the box")
+    r = _run_ranks(2, "--mode", "gpu", "--model", "collective")
+    assert r.returncode == 0, r.stdout[-3000:]
+
+
+@pytest.mark.gpu
+def test_collective_of_one_rank_behaves_like_single_rank(pkg):
+    """world 1 at the C boundary = SingleRank (lib.rs:257-292): every operation is a copy, no NCCL involved."""
+    import numpy as np
+
+    coll = pkg.NcclCollective(pkg.CudaBackend(0), b"", pkg.Rank.single())
+    buf = np.arange(7, dtype=np.float32)
+    coll.all_reduce_sum(buf)
+    assert buf.tolist() == list(range(7))
+    out = np.zeros(4, np.float32)
+    coll.all_gather(np.array([1, 2, 3, 4], np.float32), out)
+    assert out.tolist() == [1, 2, 3, 4]
+    coll.reduce_scatter_sum(np.array([5, 6], np.float32), out[:2])
+    assert out[:2].tolist() == [5, 6]
+    coll.barrier()
+    with pytest.raises(pkg.InternalError):
+        coll.all_gather(np.zeros(3, np.float32), np.zeros(4, np.float32))

@@ -49,7 +49,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--mode", choices=("cpu", "gpu"), required=True)
     ap.add_argument("--dtype", choices=("F32", "BF16"), default="F32")
-    ap.add_argument("--model", choices=("small", "kv8", "wide"), default="small",
+    ap.add_argument("--model", choices=("small", "kv8", "wide", "collective"), default="small",
                     help="gpu mode: small = 4 kv heads, 3 sequences; kv8 = the benchmark's own check model (8 kv heads, "
                          "up to 8 ranks, 160-row decode and a mixed batch of 1274 rows); wide = hidden 4096 at 256 rows, "
                          "1 Mi elements per hand-over")
@@ -61,6 +61,33 @@ def main():
         import bench
 
         backend = pkg.CudaBackend(int(os.environ.get("LOCAL_RANK", rank)))
+        if args.model == "collective":
+            # the Collective trait over NCCL at the C boundary (lib.rs:243-253), same checks as over gloo
+            box = [pkg.NcclCollectiveId.create() if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            coll = pkg.NcclCollective(backend, box[0], pkg.Rank(rank, world))
+            good = coll.rank() == pkg.Rank(rank, world)
+            buf = np.full(5, rank + 1.0, np.float32)
+            coll.all_reduce_sum(buf)
+            good &= bool(np.all(buf == sum(range(1, world + 1))))
+            out = np.zeros(3 * world, np.float32)
+            coll.all_gather(np.full(3, float(rank), np.float32), out)
+            good &= out.tolist() == [float(r) for r in range(world) for _ in range(3)]
+            piece = np.zeros(2, np.float32)
+            coll.reduce_scatter_sum(np.arange(2 * world, dtype=np.float32), piece)
+            good &= piece.tolist() == [world * (2 * rank + i) for i in range(2)]
+            big = np.random.default_rng(rank).standard_normal(1 << 20).astype(np.float32)
+            total = big.astype(np.float64)
+            for r in range(world):
+                if r != rank:
+                    total = total + np.random.default_rng(r).standard_normal(1 << 20).astype(np.float32)
+            coll.all_reduce_sum(big)
+            good &= bool(np.allclose(big, total, atol=1e-5))
+            coll.barrier()
+            flags = [None] * world
+            dist.all_gather_object(flags, bool(good))
+            dist.destroy_process_group()
+            return 0 if all(flags) else 1
         if args.model == "kv8":
             report = bench.tp_parity(pkg, backend, dist, rank, world, args.dtype)
         else:
