@@ -62,10 +62,15 @@ __device__ __forceinline__ void gtrace(uint32_t slot, int k) {
 // possible); prefill batches are tensor-bound and limited by the shared-memory fill rate, so a
 // CTA there takes two weight tiles against one activation tile (MT = 2: 64 KiB of operands per
 // 2.1 MFLOP instead of 48 KiB per 1.05), with two accumulators in tensor memory.
-template <int TOKN, int WST, int XST, int MT = 1>
+// PAIR: two CTAs of a cluster work as one MMA unit (tcgen05 cta_group::2): each loads its own weight
+// tiles and HALF of the activation tile, the leader issues 256-row MMAs that read both CTAs' shared
+// memory and write both CTAs' tensor memory. Per CTA an activation stage is half as large, so a
+// prefill-sized projection moves 48 KiB of operands per 8.4 MFLOP instead of 64 KiB.
+template <int TOKN, int WST, int XST, int MT = 1, bool PAIR = false>
 struct TcConfig {
   static constexpr int kWBytes = MT * kTileN * kSlabK * 2;
-  static constexpr int kXBytes = TOKN * kSlabK * 2;
+  static constexpr int kXRows = PAIR ? TOKN / 2 : TOKN;  // activation rows this CTA loads per stage
+  static constexpr int kXBytes = kXRows * kSlabK * 2;
   static constexpr int kWStages = WST;
   static constexpr int kXStages = XST;
   static constexpr int kXRingOffset = WST * kWBytes;
@@ -100,6 +105,42 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// ---- cta_group::2 (a pair of CTAs as one MMA unit) ----
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *dst_smem, uint32_t ncols) {  // one warp in EACH CTA of the pair
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Arrives on the barrier at cluster shared-memory address `bar_cluster_addr` (this CTA's or the
+// peer's) once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 2-D tiled TMA load of one CTA of a pair: the data lands in THIS CTA's shared memory, the bytes are
+// counted on the barrier at cluster address `bar_cluster_addr` (the leader's). No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void *dst_smem, const void *tensor_map, int c0, int c1,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst_smem)),
+      "l"(tensor_map), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
       : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
@@ -154,18 +195,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
 
 // Instruction descriptor: f32 accumulate, bf16 x bf16, both operands K-major,
 // N = TOKN (>>3 at bit 17), M = 128 (>>4 at bit 24).
-template <int TOKN>
+template <int TOKN, int M = kTileN>
 __device__ __forceinline__ constexpr uint32_t instr_desc() {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TOKN >> 3) << 17) |
-         ((uint32_t)(kTileN >> 4) << 24);
+         ((uint32_t)(M >> 4) << 24);
 }
 
-template <int TOKN, int WST, int XST, int MT>
+template <int TOKN, int WST, int XST, int MT, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                float *__restrict__ partial, bf16 *__restrict__ act, uint32_t M, uint32_t N, uint32_t K,
                uint32_t splits, uint32_t cluster_reduce, uint32_t ldc, PrefetchHint next) {
-  using Cfg = TcConfig<TOKN, WST, XST, MT>;
+  using Cfg = TcConfig<TOKN, WST, XST, MT, PAIR>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                               ~uintptr_t(1023));
@@ -183,6 +224,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t kb_begin = (uint32_t)((uint64_t)split * nkb / splits);
   const uint32_t kb_end = (uint32_t)((uint64_t)(split + 1) * nkb / splits);
   const uint32_t my_kb = kb_end - kb_begin;
+  // Pair mode: the two CTAs of a cluster sit next to each other in x; the even one leads.
+  const uint32_t pair_rank = PAIR ? (blockIdx.x & 1u) : 0u;
+  const bool leader = pair_rank == 0;
 
   pdl_trigger();
 #ifdef ORION_TRACE
@@ -210,11 +254,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, Cfg::kTmemCols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, Cfg::kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) {  // the peer's barriers exist before anything of this CTA signals them
+    cluster_arrive_release();
+    cluster_wait_acquire();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 #ifdef ORION_TRACE
@@ -230,6 +283,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (uint32_t i = 0; i < my_kb; ++i) {
         const uint32_t s = i % WST, use = i / WST;
         if (!mbar_wait(&empty_w[s], (use & 1) ^ 1)) { ok = false; break; }
+        if (PAIR) {
+          // both CTAs' tiles are counted on the leader's barrier, which expects the bytes of both
+          if (leader) mbar_arrive_expect_tx(&full_w[s], 2 * Cfg::kWBytes);
+          const uint32_t bar = mapa_u32(smem_u32(&full_w[s]), 0);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            tma_load_2d_pair(w_ring + s * Cfg::kWBytes + mt * (kTileN * kSlabK * 2), &map_w, (int)((kb_begin + i) * kSlabK),
+                             (int)(n0 + mt * kTileN), bar);
+          continue;
+        }
         mbar_arrive_expect_tx(&full_w[s], Cfg::kWBytes);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)  // rows past the matrix read as zeros and still count their bytes
@@ -246,13 +309,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (uint32_t i = 0; i < my_kb; ++i) {
         const uint32_t s = i % XST, use = i / XST;
         if (!mbar_wait(&empty_x[s], (use & 1) ^ 1)) { ok = false; break; }
+        if (PAIR) {  // this CTA's half of the token tile; counted on the leader's barrier like the weights
+          if (leader) mbar_arrive_expect_tx(&full_x[s], 2 * Cfg::kXBytes);
+          tma_load_2d_pair(x_ring + s * Cfg::kXBytes, &map_x, (int)((kb_begin + i) * kSlabK),
+                           (int)(t0 + pair_rank * Cfg::kXRows), mapa_u32(smem_u32(&full_x[s]), 0));
+          continue;
+        }
         mbar_arrive_expect_tx(&full_x[s], Cfg::kXBytes);
         tma_load_2d(x_ring + s * Cfg::kXBytes, &map_x, (int)((kb_begin + i) * kSlabK), (int)t0, &full_x[s]);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc<TOKN>();
+    if (lane == 0 && leader) {  // in pair mode the leader issues for both CTAs
+      constexpr uint32_t idesc = PAIR ? instr_desc<TOKN, 2 * kTileN>() : instr_desc<TOKN>();
       for (uint32_t i = 0; i < my_kb; ++i) {
         const uint32_t sw = i % WST, sx = i % XST;
         if (!mbar_wait(&full_w[sw], (i / WST) & 1)) { ok = false; break; }
@@ -268,12 +337,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {  // one accumulator of TOKN columns per weight tile
             const uint64_t a = smem_desc_sw128(wt + mt * (kTileN * kSlabK * 2) + k * kUmmaK * 2);
-            umma_bf16(tmem_base + (uint32_t)(mt * TOKN), a, b, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            if (PAIR) umma_bf16_pair(tmem_base + (uint32_t)(mt * TOKN), a, b, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            else umma_bf16(tmem_base + (uint32_t)(mt * TOKN), a, b, idesc, (i > 0 || k > 0) ? 1u : 0u);
           }
+        }
+        if (PAIR) {  // the same stage of both CTAs is free once these MMAs have read it
+#pragma unroll
+          for (uint32_t r = 0; r < 2; ++r) {
+            umma_commit_pair(mapa_u32(smem_u32(&empty_w[sw]), r));
+            umma_commit_pair(mapa_u32(smem_u32(&empty_x[sx]), r));
+          }
+          continue;
         }
         umma_commit(&empty_w[sw]);  // both stages are free once these MMAs have read them
         umma_commit(&empty_x[sx]);
       }
+      if (PAIR) {
+        umma_commit_pair(mapa_u32(smem_u32(acc_ready), 0));
+        umma_commit_pair(mapa_u32(smem_u32(acc_ready), 1));
+      } else
       umma_commit(acc_ready);  // arrives when every MMA above has completed
       ORION_GTRACE(tslot, 4);
     }
@@ -374,6 +456,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (!ok) atomicOr(&g_gemm_error, 1u);
   tc_fence_before();
   __syncthreads();
+  if (PAIR) {
+    // Neither CTA leaves, nor frees the tensor memory the pair allocated together, while the other may
+    // still be read by an MMA or be reading its accumulator.
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    return;
+  }
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
@@ -441,33 +531,46 @@ int cached_map(const void *base, uint64_t rows, uint64_t k, uint64_t ld, uint32_
   return ORION_OK;
 }
 
-template <int TOKN, int WST, int XST, int MT = 1>
+template <int TOKN, int WST, int XST, int MT = 1, bool PAIR = false>
 int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial, bf16 *act,
               uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, bool cluster_reduce, uint32_t ldc,
               PrefetchHint next, cudaStream_t stream) {
   if (ldc == 0) ldc = n;
   if (ldc != n && (splits != 1 || act != nullptr))
     return set_error(ORION_ERR_INTERNAL, "a strided GEMM output needs one k split and f32 results");
-  using Cfg = TcConfig<TOKN, WST, XST, MT>;
+  using Cfg = TcConfig<TOKN, WST, XST, MT, PAIR>;
   static_assert(Cfg::kSmemBytes <= 232448, "ring exceeds the shared memory of an SM");
   if (MT > 1 && cluster_reduce) return set_error(ORION_ERR_INTERNAL, "cluster split-K is built for one weight tile per CTA");
   static bool attr_set[kMaxDeviceOrdinals] = {};
-  ORION_CUDA_CHECK("gemm_tc attr", ensure_dynamic_smem(gemm_tc_kernel<TOKN, WST, XST, MT>, Cfg::kSmemBytes, attr_set));
+  ORION_CUDA_CHECK("gemm_tc attr", ensure_dynamic_smem(gemm_tc_kernel<TOKN, WST, XST, MT, PAIR>, Cfg::kSmemBytes, attr_set));
   const CUtensorMap *mw, *mx;
   ORION_TRY(cached_map(w, n, k, ldw, kTileN, &mw));
-  ORION_TRY(cached_map(x, rows, k, ldx, TOKN, &mx));
+  ORION_TRY(cached_map(x, rows, k, ldx, Cfg::kXRows, &mx));
   dim3 grid((n + MT * kTileN - 1) / (MT * kTileN), (rows + TOKN - 1) / TOKN, splits);
-  if (cluster_reduce)
-    ORION_CUDA_CHECK("gemm_tc", launch_pdl_cluster(gemm_tc_kernel<TOKN, WST, XST, MT>, grid, dim3(kThreads), dim3(1, 1, splits),
+  if (PAIR) {
+    if (cluster_reduce || (grid.x & 1u))
+      return set_error(ORION_ERR_INTERNAL, "the paired GEMM needs an even number of weight tile groups and no cluster split-K");
+    ORION_CUDA_CHECK("gemm_tc", launch_pdl_cluster(gemm_tc_kernel<TOKN, WST, XST, MT, PAIR>, grid, dim3(kThreads), dim3(2, 1, 1),
+                                                   Cfg::kSmemBytes, stream, *mw, *mx, partial, act, rows, n, k, splits,
+                                                   0u, ldc, next));
+  } else if (cluster_reduce)
+    ORION_CUDA_CHECK("gemm_tc", launch_pdl_cluster(gemm_tc_kernel<TOKN, WST, XST, MT, PAIR>, grid, dim3(kThreads), dim3(1, 1, splits),
                                                    Cfg::kSmemBytes, stream, *mw, *mx, partial, act, rows, n, k, splits,
                                                    1u, ldc, next));
   else
-    ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, WST, XST, MT>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
+    ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, WST, XST, MT, PAIR>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
                                            *mw, *mx, partial, act, rows, n, k, splits, 0u, ldc, next));
   count_launch();
   ORION_CUDA_CHECK("gemm_tc", cudaGetLastError());
   return ORION_OK;
 }
+
+// 256-token tiles as CTA pairs (tcgen05 cta_group::2). Measured on the Llama-3-8B shape, projections of
+// a step of 512 / 2048 / 8192 tokens: 616 / 869 / 1034 TFLOP/s paired against 630 / 900 / 996 unpaired:
+// the pair pays off once a step has many token tiles. 1 (default) = pairs from 4096 rows on, 2 = wherever
+// the grid allows (the parity tests run this), 0 = never. ORION_GEMM_PAIR overrides.
+int g_gemm_pair = std::getenv("ORION_GEMM_PAIR") ? std::atoi(std::getenv("ORION_GEMM_PAIR")) : 1;
+constexpr uint32_t kPairMinRows = 4096;
 
 // Tuning A/B: ORION_GEMM_PREFILL_TILES=1 keeps one weight tile per CTA for prefill-sized batches
 // (two tiles measured 3 % faster on the continuous-batching workload, gate/up only: the other
@@ -541,10 +644,17 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
       return g_mid_tile == 0
                  ? launch_tc<128, 4, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
                  : launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
-    default:
-      if (!cluster_reduce && prefill_weight_tiles(rows, n) == 2)
-        return launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
-      return launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
+    default: {
+      const uint32_t mt = (!cluster_reduce && prefill_weight_tiles(rows, n) == 2) ? 2 : 1;
+      // CTA pairs: each CTA loads half of the activation tile, so the rings go a stage deeper
+      const bool pair = (g_gemm_pair >= 2 || (g_gemm_pair == 1 && rows >= kPairMinRows)) && !cluster_reduce &&
+                        (((n + mt * kTileN - 1) / (mt * kTileN)) & 1u) == 0;
+      if (mt == 2)
+        return pair ? launch_tc<256, 4, 4, 2, true>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
+                    : launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
+      return pair ? launch_tc<256, 6, 6, 1, true>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
+                  : launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
+    }
   }
 }
 

@@ -92,6 +92,12 @@ def test_linear_f32_is_bit_exact(pkg, backend, oracle, kats):
                                       (129, 640, 1024), (300, 1152, 2048), (8, 200, 72),
                                       # prefill-sized batches: two weight tiles per CTA, ragged last tile
                                       (512, 384, 512), (260, 128, 64), (700, 2176, 256),
+                                      # an even number of weight tile groups: CTA pairs (cta_group::2), one and two weight
+                                      # tiles per CTA, ragged last token tile (one CTA's half entirely past the end), ragged
+                                      # last weight tile
+                                      # (from 4096 rows on by default, everywhere the grid allows in the paired re-run below)
+                                      (300, 1024, 2048), (200, 1024, 512), (600, 1000, 1024), (300, 19456, 256),
+                                      (4100, 512, 256),
                                       # Llama-3-70B projections on one of 8 ranks: qkv, o, gate|up, down
                                       (16, 1280, 8192), (16, 8192, 1024), (16, 7168, 8192), (16, 8192, 3584)])
 def test_linear_bf16_tensor_core_matches_the_oracle(pkg, backend, oracle, rows, n, k):
@@ -655,6 +661,22 @@ def test_qwen2_7b_head_layout_with_qkv_bias_on_the_tuned_bf16_path(pkg, backend,
     kv_dev, kv_ref = dev.read_kv(), ref.kv().array()
     assert np.array_equal(kv_dev != 0, kv_ref != 0), "exactly the same slots were written"
     assert np.allclose(kv_dev, kv_ref, atol=3e-2, rtol=3e-2)
+
+
+def test_paired_gemm_variant_matches_the_oracle(pkg, backend):
+    """256-token GEMM tiles as CTA pairs (tcgen05 cta_group::2) are used from 4096 rows on by default; the
+    switch is read when the library loads, so the parity cases with 129 rows and more run once more in a
+    child process with pairs wherever the grid allows: plain and SwiGLU epilogues, one and two weight tiles."""
+    import os
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+    env = dict(os.environ, ORION_GEMM_PAIR="2")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_parity.py"), "-q", "-x",
+                        "-m", "gpu", "-k", "linear_bf16_tensor_core or chunked_prefill or mixed_batch"],
+                       cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:]
 
 
 def test_cluster_split_k_variant_matches_the_oracle(pkg, backend):
