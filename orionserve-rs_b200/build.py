@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "liborion_cuda.so")
-SOURCES = ["elementwise.cu", "attention.cu", "attention_prefill.cu", "gemm_simt.cu", "tp_fused.cu", "gemm_tc.cu", "model.cu", "c_api.cu",
+SOURCES = ["elementwise.cu", "attention.cu", "attention_prefill.cu", "attention_prefill_tc.cu", "gemm_simt.cu", "tp_fused.cu", "gemm_tc.cu", "model.cu", "c_api.cu",
            "tp_nccl.cpp", "driver.cpp", "driver_sched.cpp", "driver_api.cpp", "checkpoint.cpp", "selftest.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -227,6 +227,8 @@ int launch_paged_attention_prefill(const bf16 *q, const bf16 *arena, KvLayout kv
                                    const PrefillTile *tiles, uint32_t num_tiles, uint32_t q_heads, bf16 *out,
                                    cudaStream_t stream) {
   if (num_tiles == 0) return ORION_OK;
+  if (prefill_attention_tc_supported(kv, q_heads, arena))  // tcgen05 / tensor-memory kernel; this file's is the fallback
+    return launch_paged_attention_prefill_tc(q, arena, kv, layer, batch, tiles, num_tiles, q_heads, out, stream);
   if (!prefill_attention_supported(kv, q_heads))
     return set_error(ORION_ERR_INTERNAL, "prefill attention kernel does not cover this shape");
   static bool attr_set[kMaxDeviceOrdinals] = {};
@@ -239,12 +241,15 @@ int launch_paged_attention_prefill(const bf16 *q, const bf16 *arena, KvLayout kv
 }
 
 int prefill_poll_error(uint32_t *code) {
+  uint32_t tc = 0;
+  ORION_TRY(prefill_tc_poll_error(&tc));
   uint32_t v = 0;
   ORION_CUDA_CHECK("prefill error word", cudaMemcpyFromSymbol(&v, g_prefill_error, sizeof v));
   if (v) {
     uint32_t zero = 0;
     ORION_CUDA_CHECK("prefill error word", cudaMemcpyToSymbol(g_prefill_error, &zero, sizeof zero));
   }
+  v |= tc ? 2u : 0u;
   *code = v;
   return ORION_OK;
 }

@@ -148,6 +148,13 @@ int launch_paged_attention_prefill(const bf16 *q, const bf16 *arena, KvLayout kv
                                    AttnBatch batch, const PrefillTile *tiles, uint32_t num_tiles,
                                    uint32_t q_heads, bf16 *out, cudaStream_t stream);
 int prefill_poll_error(uint32_t *code);
+// The same computation on tcgen05 / tensor memory (S and O accumulators in tensor memory, K/V tiles by
+// tiled TMA straight out of the arena); same tiles, same arguments.
+bool prefill_attention_tc_supported(KvLayout kv, uint32_t q_heads, const void *arena);
+int launch_paged_attention_prefill_tc(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer,
+                                      AttnBatch batch, const PrefillTile *tiles, uint32_t num_tiles,
+                                      uint32_t q_heads, bf16 *out, cudaStream_t stream);
+int prefill_tc_poll_error(uint32_t *code);
 
 // Tuned decode path (bf16, head_dim 128, block 16, one query row per sequence):
 // one CTA per (sequence, kv head, context split); the query heads of a GQA group

@@ -679,6 +679,22 @@ def test_paired_gemm_variant_matches_the_oracle(pkg, backend):
     assert r.returncode == 0, r.stdout[-3000:]
 
 
+def test_prefill_attention_fallback_kernel_matches_the_oracle(pkg, backend):
+    """Chunked-prefill attention runs on tcgen05 / tensor memory by default; the mma.sync kernel behind it (arenas
+    too large for one tensor map, ORION_PREFILL_TC=0) is kept honest by running the prefill and mixed-batch
+    cases once more in a child process with the switch off."""
+    import os
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+    env = dict(os.environ, ORION_PREFILL_TC="0")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_parity.py"), "-q", "-x",
+                        "-m", "gpu", "-k", "chunked_prefill or mixed_batch or qwen2_7b_head_layout"],
+                       cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:]
+
+
 def test_cluster_split_k_variant_matches_the_oracle(pkg, backend):
     """The GEMM's split-K reduction inside a thread-block cluster is off by default (measured
     slower); the switch is read when the library loads, so the parity cases that reach split-K
