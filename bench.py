@@ -74,10 +74,18 @@ def layer_param_count(m, world=1):
     return H * (q + 2 * kv) * hd + q * hd * H + 3 * H * f
 
 
+def head_rows_per_rank(m, world=1):
+    """Rows of the LM head the busiest rank streams: all of them on one GPU; under tensor parallelism the head
+    is split by vocabulary in multiples of the 128-row weight tile (ORION_TP_VOCAB_PARALLEL=0: replicated)."""
+    if world == 1 or os.environ.get("ORION_TP_VOCAB_PARALLEL") == "0":
+        return m["vocab_size"]
+    return min(m["vocab_size"], ((m["vocab_size"] + world - 1) // world + 127) // 128 * 128)
+
+
 def weight_bytes_per_step(m, world=1):
     """Algorithmic bytes of the projection GEMMs of one decode step on one rank: every bf16
-    weight once (layers sharded under TP, LM head replicated)."""
-    return 2 * (m["num_layers"] * layer_param_count(m, world) + m["vocab_size"] * m["hidden_size"])
+    weight of the rank once (layers and LM head sharded under TP)."""
+    return 2 * (m["num_layers"] * layer_param_count(m, world) + head_rows_per_rank(m, world) * m["hidden_size"])
 
 
 def kv_bytes_per_step(m, contexts, world=1):

@@ -238,6 +238,12 @@ int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, c
                                          size_t split_stride, float *hidden, const float *norm_w, float eps, T *out,
                                          uint32_t rows, uint32_t hidden_size, bool two_shot, cudaStream_t stream);
 int tp_poll_error(uint32_t *code);
+// Vocabulary-parallel LM head: `launch_tp_signal` (ranks other than the leader) stores `epoch` into the
+// rank's flag in the leader's memory once the preceding kernel of the stream has completed;
+// `launch_tp_wait_flags` (leader) holds the stream until the flags of ranks 1 .. world-1 carry `epoch`
+// (bounded: after `limit_ns` the hand-over error word gets bit 1 and the stream goes on).
+int launch_tp_signal(uint32_t *flag, uint32_t epoch, cudaStream_t stream);
+int launch_tp_wait_flags(const uint32_t *flags, uint32_t epoch, int world, uint64_t limit_ns, cudaStream_t stream);
 // Launches a kernel whose only thread waits on a barrier that nothing arrives at, with the given
 // limit: the bounded wait must give up (timed_out = 1) and the kernel must end normally.
 int selftest_bounded_wait(uint64_t limit_us, uint32_t *timed_out, uint32_t *waited_us);

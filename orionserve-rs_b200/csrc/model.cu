@@ -160,6 +160,15 @@ class Model final : public ModelBase {
   // Tensor parallel: the fused peer-memory all-reduce + residual + norm kernel, or NCCL followed
   // by the single-GPU kernel. `out_rows`/`row_map` select gathered output rows (final norm).
   int handover(uint32_t splits, const float *norm_w, T *out, const uint32_t *row_map, uint32_t out_rows);
+  // Vocabulary-parallel LM head under tensor parallelism: this rank holds rows [head_v0_, head_v0_ + head_vn_)
+  // of the head, computes that column block of the logits and stores it straight into the leader's
+  // logits buffer (peer-mapped); flags in the leader's memory tell it when every block has landed.
+  bool head_parallel_ = false;
+  uint32_t head_v0_ = 0, head_vn_ = 0;
+  float *head_out_ = nullptr;       // the leader's logits buffer as seen from this rank
+  uint32_t *head_flags_ = nullptr;  // the leader's flag words as seen from this rank (own allocation on the leader)
+  uint32_t head_epoch_ = 1;
+  int setup_head_peers();
   TpPeers peers_{};
   uint32_t *tp_inbox_ = nullptr;  // where the peers push their partial sums (peer-mapped)
   uint32_t tp_epoch_ = 1;
@@ -292,7 +301,18 @@ int Model<T>::init() {
   }
   ORION_TRY(alloc(&embed_, V * H));
   ORION_TRY(alloc(&final_norm_, H));
-  if (!d.tied_lm_head) ORION_TRY(alloc(&lm_head_own_, V * H));
+  head_vn_ = d.vocab_size;
+  if (d.tp_world > 1 && DTypeOf<T>::is_bf16 && gemm_plan(true, 1, 128, d.hidden_size, d.hidden_size, d.hidden_size).tensor_core) {
+    const char *e = std::getenv("ORION_TP_VOCAB_PARALLEL");
+    if (!e || std::atoi(e) != 0) {
+      // column blocks in multiples of the 128-row weight tile; the last ranks may hold fewer (or no) rows
+      const uint32_t per = ((d.vocab_size + d.tp_world - 1) / d.tp_world + 127) / 128 * 128;
+      head_parallel_ = true;
+      head_v0_ = std::min(d.vocab_size, d.tp_rank * per);
+      head_vn_ = std::min(d.vocab_size, head_v0_ + per) - head_v0_;
+    }
+  }
+  if (!d.tied_lm_head) ORION_TRY(alloc(&lm_head_own_, (size_t)head_vn_ * H));
 
   // Zero-initialised arena for this rank's KV heads (attention.rs:53-56).
   kv_ = KvLayout{d.num_layers, d.num_blocks, lkv_, d.block_size, d.head_dim,
@@ -358,6 +378,7 @@ int Model<T>::init() {
     tp_two_shot_ = d.tp_world > 2 || (mode && !strcmp(mode, "twoshot"));
     if (want_fused && d.tp_world <= (uint32_t)kMaxTpWorld && H % 4 == 0 && H / 4 <= 4096)
       ORION_TRY(setup_peer_handover());
+    if (head_parallel_) ORION_TRY(setup_head_peers());
   }
   ORION_CUDA_CHECK("model init", cudaStreamSynchronize(stream_));
   return ORION_OK;
@@ -400,6 +421,40 @@ int Model<T>::setup_peer_handover() {
   ORION_TRY(nccl_->barrier(stream_));  // nobody starts a step before every mapping exists
   tp_fused_ = true;
   return ORION_OK;
+}
+
+// Maps the leader's logits buffer and flag words into every rank (CUDA IPC, handles over one NCCL
+// all-gather) for the vocabulary-parallel LM head.
+template <typename T>
+int Model<T>::setup_head_peers() {
+  const int world = (int)d_.tp_world, rank = (int)d_.tp_rank;
+  uint32_t *flags = nullptr;
+  ORION_TRY(alloc(&flags, 64));
+  ORION_CUDA_CHECK("clear flags", cudaMemset(flags, 0, 64 * sizeof(uint32_t)));  // epoch 0 is never signalled
+  constexpr int kFloatsPerHandle = sizeof(cudaIpcMemHandle_t) / sizeof(float);
+  cudaIpcMemHandle_t mine[2];
+  ORION_CUDA_CHECK("ipc export", cudaIpcGetMemHandle(&mine[0], logits_));
+  ORION_CUDA_CHECK("ipc export", cudaIpcGetMemHandle(&mine[1], flags));
+  float *d_send = nullptr, *d_recv = nullptr;
+  ORION_TRY(alloc(&d_send, 2 * kFloatsPerHandle));
+  ORION_TRY(alloc(&d_recv, (size_t)2 * kFloatsPerHandle * world));
+  ORION_CUDA_CHECK("ipc exchange", cudaMemcpy(d_send, mine, sizeof mine, cudaMemcpyHostToDevice));
+  ORION_TRY(nccl_->all_gather(d_send, d_recv, 2 * kFloatsPerHandle, stream_));
+  ORION_TRY(nccl_->wait_stream(stream_, "ipc exchange"));
+  cudaIpcMemHandle_t leader[2];
+  ORION_CUDA_CHECK("ipc exchange", cudaMemcpy(leader, d_recv, sizeof leader, cudaMemcpyDeviceToHost));  // rank 0's pair comes first
+  head_out_ = logits_;
+  head_flags_ = flags;
+  if (rank != 0) {
+    void *p = nullptr;
+    ORION_CUDA_CHECK("ipc import", cudaIpcOpenMemHandle(&p, leader[0], cudaIpcMemLazyEnablePeerAccess));
+    ipc_opened_.push_back(p);
+    head_out_ = static_cast<float *>(p);
+    ORION_CUDA_CHECK("ipc import", cudaIpcOpenMemHandle(&p, leader[1], cudaIpcMemLazyEnablePeerAccess));
+    ipc_opened_.push_back(p);
+    head_flags_ = static_cast<uint32_t *>(p);
+  }
+  return nccl_->barrier(stream_);  // nobody starts a step before every mapping exists
 }
 
 template <typename T>
@@ -486,7 +541,7 @@ int Model<T>::load_tensor(const char *name, int dtype, const uint64_t *shape, in
     if (d.tied_lm_head) return ORION_OK;  // transformer.rs:108-110
     ORION_TRY(expect(V, H));
     got_head_ = true;
-    return upload_slice(lm_head_own_, nullptr, data, dtype, C, 0, V, 0, H);
+    return upload_slice(lm_head_own_, nullptr, data, dtype, C, head_v0_, head_v0_ + head_vn_, 0, H);
   }
   unsigned li = 0;
   char rest[96];
@@ -581,7 +636,7 @@ int Model<T>::init_random(uint64_t seed, float std) {
     return ORION_OK;
   };
   ORION_TRY(fill(embed_, V * H));
-  if (lm_head_own_) ORION_TRY(fill(lm_head_own_, V * H));
+  if (lm_head_own_) ORION_TRY(fill(lm_head_own_, (size_t)head_vn_ * H));
   ORION_TRY(set_ones(final_norm_));
   for (Layer &L : layers_) {
     ORION_TRY(fill(L.w_qkv, (size_t)(lq_ + 2 * lkv_) * hd * H));
@@ -612,7 +667,7 @@ int Model<T>::finalize() {
       if (!(layers_[i].got & (1u << b)))
         return set_error(ORION_ERR_MODEL, "missing tensor `model.layers.%zu.%s`", i, names[b]);
   // transformer.rs:108-112: the head falls back to the embedding when tied or absent.
-  lm_head_ = (d_.tied_lm_head || !got_head_) ? embed_ : lm_head_own_;
+  lm_head_ = (d_.tied_lm_head || !got_head_) ? embed_ + (size_t)head_v0_ * d_.hidden_size : lm_head_own_;
   finalized_ = true;
   return ORION_OK;
 }
@@ -762,7 +817,7 @@ int Model<T>::run_step(bool want_argmax) {
     p = plan_for(Tn, H, lf_);
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(act_, lf_, L.w_down, lf_, partial_, Tn, H, lf_, p, stream_,
                                                               l + 1 < d.num_layers ? hint(layers_[l + 1].w_qkv, (size_t)nqkv * H)
-                                                                                   : hint(lm_head_, (size_t)d.vocab_size * H)); }));
+                                                                                   : hint(lm_head_, (size_t)head_vn_ * H)); }));
     if (l + 1 < d.num_layers) {
       ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, layers_[l + 1].in_norm, normed_, nullptr, Tn); }));
     } else if (!meta_.zero_count) {
@@ -775,6 +830,24 @@ int Model<T>::run_step(bool want_argmax) {
     }
   }
   if (meta_.zero_count) return ORION_OK;
+  if (head_parallel_) {
+    // This rank's column block of the logits goes straight into the leader's buffer (plain peer stores from
+    // the GEMM epilogue), then the rank raises its flag there; the leader waits for all flags.
+    if (head_vn_ > 0) {
+      GemmPlan hp = gemm_plan(kBf16, S, head_vn_, H, H, H);
+      hp.splits = hp.out_slabs = 1, hp.cluster_reduce = false;
+      hp.ldc = d.vocab_size;
+      ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(tail_, H, lm_head_, H, head_out_ + head_v0_, S, head_vn_, H, hp, stream_); }));
+    }
+    head_chunks_ = 0;
+    const uint32_t epoch = head_epoch_;
+    head_epoch_ = head_epoch_ == 0xFFFFFFFEu ? 1u : head_epoch_ + 1;
+    if (d.tp_rank != 0)
+      return timed(kProfCollective, [&] { return launch_tp_signal(head_flags_ + d.tp_rank, epoch, stream_); });
+    ORION_TRY(timed(kProfCollective, [&] { return launch_tp_wait_flags(head_flags_, epoch, (int)d.tp_world, 2000000000ull, stream_); }));
+    if (want_argmax) ORION_TRY(timed(kProfElementwise, [&] { return launch_argmax(logits_, S, d.vocab_size, argmax_, stream_); }));
+    return ORION_OK;
+  }
   GemmPlan hp = gemm_plan(kBf16, S, d.vocab_size, H, H, H);
   hp.splits = hp.out_slabs = 1, hp.cluster_reduce = false;  // logits are written in place, row-major [S][V]
   head_chunks_ = 0;
@@ -991,7 +1064,7 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
     ORION_TRY(wait_for(stream_, "forward"));
   }
   uint32_t code = 0;
-  if (tp_fused_) {
+  if (nccl_) {
     ORION_TRY(tp_poll_error(&code));
     if (code) return set_error(ORION_ERR_BACKEND, "backend cuda failed at all_reduce: a peer did not arrive within the wait limit (code %u)", code);
   }

@@ -354,6 +354,49 @@ template int launch_tp_allreduce_residual_rmsnorm<bf16>(const TpPeers &, uint32_
                                                         bool, cudaStream_t);
 
 namespace {
+// Vocabulary-parallel LM head: a rank that has stored its column block of the logits into the
+// leader's memory raises its flag there; the leader waits for every flag before it touches the logits.
+__global__ void tp_signal_kernel(uint32_t *flag, uint32_t epoch) {
+  pdl_trigger();
+  pdl_wait();                // the projection that wrote the block has completed
+  __threadfence_system();    // its peer stores are ordered before the flag at system scope
+  if (threadIdx.x == 0) {
+    asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+  }
+}
+__global__ void tp_wait_flags_kernel(const uint32_t *flags, uint32_t epoch, int world, uint64_t limit_ns) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = (int)threadIdx.x + 1;  // flag of rank r; the leader has none
+  if (r < world) {
+    const volatile uint32_t *f = flags + r;
+    if (*f != epoch) {
+      const uint64_t start = global_timer_ns();
+      uint32_t spins = 0;
+      while (*f != epoch) {
+        if ((++spins & 255u) == 0 && global_timer_ns() - start > limit_ns) {
+          atomicOr(&g_tp_error, 2u);
+          break;
+        }
+      }
+    }
+  }
+  __threadfence_system();
+}
+}  // namespace
+
+int launch_tp_signal(uint32_t *flag, uint32_t epoch, cudaStream_t stream) {
+  ORION_CUDA_CHECK("tp_signal", launch_pdl(tp_signal_kernel, dim3(1), dim3(32), 0, stream, flag, epoch));
+  count_launch();
+  return ORION_OK;
+}
+int launch_tp_wait_flags(const uint32_t *flags, uint32_t epoch, int world, uint64_t limit_ns, cudaStream_t stream) {
+  ORION_CUDA_CHECK("tp_wait_flags", launch_pdl(tp_wait_flags_kernel, dim3(1), dim3(32), 0, stream, flags, epoch, world, limit_ns));
+  count_launch();
+  return ORION_OK;
+}
+
+namespace {
 // One thread polls inbox units that nobody ever writes, in both unit formats, with the given limit.
 __global__ void tp_peer_wait_probe_kernel(const uint32_t *inbox, uint32_t epoch, uint64_t limit_ns, uint32_t *waited_us) {
   if (threadIdx.x != 0) return;

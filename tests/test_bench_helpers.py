@@ -16,12 +16,15 @@ def test_algorithmic_bytes_of_the_headline_step():
     assert abs(kv / 1e9 - 8.62) < 0.01
 
 
-def test_tensor_parallel_ranks_share_the_layers_and_replicate_the_head():
+def test_tensor_parallel_ranks_share_the_layers_and_the_head():
     for m in (bench.LLAMA3_8B, bench.LLAMA3_70B):
         whole = bench.weight_bytes_per_step(m)
         head = 2 * m["vocab_size"] * m["hidden_size"]
         for world in (2, 4, 8):
-            assert bench.weight_bytes_per_step(m, world) == (whole - head) // world + head
+            # the head is split by vocabulary in multiples of 128 rows; the busiest rank holds the rounded-up share
+            rows = -(-(-(-m["vocab_size"] // world)) // 128) * 128
+            assert bench.head_rows_per_rank(m, world) == rows and rows * world >= m["vocab_size"] > rows * (world - 1)
+            assert bench.weight_bytes_per_step(m, world) == (whole - head) // world + 2 * rows * m["hidden_size"]
             ctx = [1024, 4096, 2000]
             tables = m["num_layers"] * sum((c + 15) // 16 for c in ctx) * 4  # every rank reads the whole table
             assert bench.kv_bytes_per_step(m, ctx, world) * world - bench.kv_bytes_per_step(m, ctx) == tables * (world - 1)
