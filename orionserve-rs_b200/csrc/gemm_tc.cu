@@ -660,7 +660,8 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
 
 int gemm_tc_poll_error(uint32_t *code) {
 #ifdef ORION_TRACE
-  static const bool tracing = std::getenv("ORION_GEMM_TRACE") != nullptr;
+  static const bool tracing = std::getenv("ORION_GEMM_TRACE") != nullptr &&
+                              (std::getenv("LOCAL_RANK") == nullptr || std::atoi(std::getenv("LOCAL_RANK")) == 0);  // one rank prints
   if (tracing) {
     static unsigned long long t[kTraceLaunches][kTraceStamps];
     uint32_t next = 0, on = 1;
@@ -669,10 +670,10 @@ int gemm_tc_poll_error(uint32_t *code) {
     cudaMemcpyToSymbol(g_gemm_trace_on, &on, sizeof on);
     if (next >= (uint32_t)kTraceLaunches) {
       unsigned long long prev_end = 0;
-      fprintf(stderr, "gemm trace of CTA 0 (us): grid.x splits slabs | gap-from-prev-end setup first-W pdl-wait last-mma acc-ready epilogue total\n");
+      fprintf(stderr, "gemm trace of CTA 0 (us): entry(abs mod 1e5) grid.x splits slabs | gap-from-prev-end setup first-W pdl-wait last-mma acc-ready epilogue total\n");
       for (int i = 0; i < kTraceLaunches; ++i) {
         const unsigned long long *r = t[(next + i) % kTraceLaunches];
-        fprintf(stderr, "  %4u %2u %3u | %7.2f %6.2f %6.2f %6.2f %6.2f %6.2f %6.2f %6.2f\n", (unsigned)(r[7] >> 32),
+        fprintf(stderr, "  gemm %10.2f %4u %2u %3u | %7.2f %6.2f %6.2f %6.2f %6.2f %6.2f %6.2f %6.2f\n", (double)(r[0] % 100000000ull) / 1e3, (unsigned)(r[7] >> 32),
                 (unsigned)((r[7] >> 16) & 0xFFFF), (unsigned)(r[7] & 0xFFFF), prev_end ? ((double)r[0] - (double)prev_end) / 1e3 : 0.0,
                 (r[1] - r[0]) / 1e3, (r[2] - r[0]) / 1e3, (r[3] - r[0]) / 1e3, (r[4] - r[0]) / 1e3, (r[5] - r[0]) / 1e3,
                 (r[6] - r[0]) / 1e3, (r[6] - r[0]) / 1e3);

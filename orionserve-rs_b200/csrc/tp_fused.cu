@@ -29,12 +29,23 @@ namespace {
 
 __device__ uint32_t g_tp_error = 0;
 #ifdef ORION_TRACE
-// Phase trace, compiled in with -DORION_TRACE only and switched on by ORION_TP_TRACE=1:
-// %globaltimer at the phase boundaries of CTA 0 of the last launch.
-__device__ unsigned long long g_tp_trace[4];
-__device__ uint32_t g_tp_trace_on = 0;
+// Phase trace, compiled in with -DORION_TRACE only and switched on by ORION_TP_TRACE=1: %globaltimer at
+// the phase boundaries of CTA 0 of the most recent launches. Stamps: 0 entry, 1 dependency wait over,
+// 2 slabs folded and sent, 3 owned groups reduced and published (one-shot: sums received), 4 end,
+// 5 the latest end over all CTAs of the launch.
+constexpr int kTpTraceLaunches = 80;
+__device__ unsigned long long g_tp_trace[kTpTraceLaunches][8];
+__device__ uint32_t g_tp_trace_on = 0, g_tp_trace_next = 0, g_tp_trace_slot = 0;
 __device__ __forceinline__ void trace(int k) {
-  if (g_tp_trace_on && blockIdx.x == 0 && threadIdx.x == 0) g_tp_trace[k] = global_timer_ns();
+  if (g_tp_trace_on && blockIdx.x == 0 && threadIdx.x == 0) {
+    if (k == 0) {
+      g_tp_trace_slot = g_tp_trace_next++ % kTpTraceLaunches;
+      g_tp_trace[g_tp_trace_slot][5] = 0;
+    }
+    g_tp_trace[g_tp_trace_slot][k] = global_timer_ns();
+  }
+  // CTA 0 has chosen the slot long before any CTA ends
+  if (g_tp_trace_on && k == 4 && threadIdx.x == 0) atomicMax(&g_tp_trace[g_tp_trace_slot][5], global_timer_ns());
 }
 #else
 __device__ __forceinline__ void trace(int) {}
@@ -132,8 +143,9 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
                                      const float *__restrict__ w, float eps, T *__restrict__ out, uint32_t H) {
   __shared__ Acc red[32];
   pdl_trigger();
-  pdl_wait();  // this rank's projection has finished
   trace(0);
+  pdl_wait();  // this rank's projection has finished
+  trace(1);
   const uint32_t nvec = H / 4, row = blockIdx.x;
   const size_t slot = (size_t)peers.slot_floats * 2;  // u32 words per (parity, sender) slot
   const size_t parity_base = (size_t)(epoch & 1u) * peers.world * slot;
@@ -154,7 +166,7 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
       }
     }
   }
-  trace(1);
+  trace(2);
   // ---- receive: add the ranks' sums in rank order, update the residual ----
   Acc ss = Acc(0);
   float *h = hidden + (size_t)row * H;
@@ -177,7 +189,7 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
             (Acc)v[c].w * (Acc)v[c].w;
     }
   }
-  trace(2);
+  trace(3);
   // ---- RMSNorm of the row (tensor.rs:143-163) ----
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -196,7 +208,7 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
                              __fmul_rn(__fmul_rn(v[c].z, scale), g.z), __fmul_rn(__fmul_rn(v[c].w, scale), g.w)));
     }
   }
-  trace(3);
+  trace(4);
 }
 
 // Two-shot variant for more than two ranks. One CTA per row on every rank; inside a row the
@@ -221,8 +233,9 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
                   T *__restrict__ out, uint32_t rows, uint32_t H) {
   __shared__ Acc red[32];
   pdl_trigger();
-  pdl_wait();  // this rank's projection has finished
   trace(0);
+  pdl_wait();  // this rank's projection has finished
+  trace(1);
   (void)rows;
   const uint32_t nvec = H / 4, row = blockIdx.x;
   const uint32_t per = (nvec + peers.world - 1) / peers.world;  // groups per owner
@@ -242,7 +255,7 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
         send_group<Packed>(peers.inbox[owner] + scatter + (size_t)peers.rank * slot, off, v[c], epoch);
     }
   }
-  trace(1);
+  trace(2);
   // ---- own groups: collect, add in rank order, publish the totals ----
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -265,7 +278,7 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
         if (r != peers.rank) send_group<Packed>(peers.inbox[r] + gather, off, add, epoch);
     }
   }
-  trace(2);
+  trace(3);
   // ---- the other groups: receive the totals; residual update on every rank ----
   Acc ss = Acc(0);
   float *h = hidden + (size_t)row * H;
@@ -302,7 +315,7 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
                              __fmul_rn(__fmul_rn(v[c].z, scale), g.z), __fmul_rn(__fmul_rn(v[c].w, scale), g.w)));
     }
   }
-  trace(3);
+  trace(4);
 }
 
 }  // namespace
@@ -429,14 +442,25 @@ int selftest_peer_wait(uint64_t limit_us, uint32_t *timed_out, uint32_t *waited_
 
 int tp_poll_error(uint32_t *code) {
 #ifdef ORION_TRACE
-  static const bool tracing = std::getenv("ORION_TP_TRACE") != nullptr;
+  static const bool tracing = std::getenv("ORION_TP_TRACE") != nullptr &&
+                              (std::getenv("LOCAL_RANK") == nullptr || std::atoi(std::getenv("LOCAL_RANK")) == 0);  // one rank prints
   if (tracing) {
-    uint32_t on = 1;
-    unsigned long long t[4];
+    uint32_t on = 1, next = 0;
+    static unsigned long long t[kTpTraceLaunches][8];
     cudaMemcpyFromSymbol(t, g_tp_trace, sizeof t);
+    cudaMemcpyFromSymbol(&next, g_tp_trace_next, sizeof next);
     cudaMemcpyToSymbol(g_tp_trace_on, &on, sizeof on);
-    fprintf(stderr, "tp trace of CTA 0 (us): fold+send %.2f receive %.2f norm %.2f total %.2f\n", (t[1] - t[0]) / 1e3,
-            (t[2] - t[1]) / 1e3, (t[3] - t[2]) / 1e3, (t[3] - t[0]) / 1e3);
+    if (next >= (uint32_t)kTpTraceLaunches) {
+      fprintf(stderr, "tp trace of CTA 0 (us): entry(abs mod 1e5) | gap-from-prev-end wait fold+send reduce+publish rest total-after-wait last-CTA-end-after-CTA-0\n");
+      unsigned long long prev_end = 0;
+      for (int i = 0; i < kTpTraceLaunches; ++i) {
+        const unsigned long long *r = t[(next + i) % kTpTraceLaunches];
+        fprintf(stderr, "  tp %10.2f | %7.2f %6.2f %6.2f %6.2f %6.2f %6.2f %6.2f\n", (double)(r[0] % 100000000ull) / 1e3,
+                prev_end ? ((double)r[0] - (double)prev_end) / 1e3 : 0.0, (r[1] - r[0]) / 1e3, (r[2] - r[1]) / 1e3, (r[3] - r[2]) / 1e3,
+                (r[4] - r[3]) / 1e3, (r[4] - r[1]) / 1e3, ((double)r[5] - (double)r[4]) / 1e3);
+        prev_end = r[4];
+      }
+    }
   }
 #endif
   uint32_t v = 0;
