@@ -256,6 +256,34 @@ __device__ __forceinline__ void prefetch_slice(PrefetchHint h) {
   for (size_t o = 0; o < len; o += 16384) l2_prefetch(base + o, (uint32_t)(len - o < 16384 ? len - o : 16384));
 }
 
+// A dependency between two kernels of a step carried by a counter in device memory instead of by the
+// completion of the earlier kernel. Every CTA of the producer adds 1 when its results are written
+// (signal_ready, after a CTA-wide barrier); the consumer, already resident through its programmatic
+// launch, polls until the counter has reached `target` and never executes griddepcontrol.wait. The
+// counter only grows (the host keeps the running total), compared modulo 2^32. The wait is bounded.
+struct ReadyWait {
+  const uint32_t *counter = nullptr;  // nullptr: wait for the preceding kernel as usual
+  uint32_t target = 0;
+};
+__device__ __forceinline__ void signal_ready(uint32_t *counter) {
+  __threadfence();
+  atomicAdd(counter, 1u);
+}
+__device__ __forceinline__ bool wait_ready(ReadyWait r, uint64_t limit_ns = 2000000000ull) {
+  uint64_t start = 0;
+  for (uint32_t i = 0;; ++i) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(r.counter) : "memory");
+    if ((int32_t)(v - r.target) >= 0) return true;
+    if ((i & 63u) == 0u) {
+      if (start == 0) start = global_timer_ns();
+      else if (global_timer_ns() - start > limit_ns) return false;
+    }
+  }
+}
+// Orders this thread's generic-proxy accesses (the acquire above) before its later async-proxy ones (TMA loads).
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -130,7 +130,8 @@ template <typename T, int CHUNKS>
 __global__ void __launch_bounds__(1024)
 residual_rmsnorm_vec_kernel(const float *__restrict__ partial, uint32_t splits, size_t split_stride,
                             float *__restrict__ hidden, const float *__restrict__ w, float eps,
-                            T *__restrict__ out, const uint32_t *__restrict__ row_map, uint32_t H) {
+                            T *__restrict__ out, const uint32_t *__restrict__ row_map, uint32_t H,
+                            uint32_t *__restrict__ ready) {
   using Acc = typename NormAcc<T>::type;
   __shared__ Acc red[32];
   pdl_trigger();
@@ -170,6 +171,10 @@ residual_rmsnorm_vec_kernel(const float *__restrict__ partial, uint32_t splits, 
       st4<T>(o + 4 * (size_t)idx,
              make_float4(__fmul_rn(__fmul_rn(v[c].x, scale), wv[c].x), __fmul_rn(__fmul_rn(v[c].y, scale), wv[c].y),
                          __fmul_rn(__fmul_rn(v[c].z, scale), wv[c].z), __fmul_rn(__fmul_rn(v[c].w, scale), wv[c].w)));
+  }
+  if (ready) {  // the consumer polls this count instead of waiting for the kernel to complete
+    __syncthreads();
+    if (threadIdx.x == 0) signal_ready(ready);
   }
 }
 
@@ -530,10 +535,10 @@ namespace {
 template <typename T, int CHUNKS>
 int launch_residual_vec(const float *partial, uint32_t splits, size_t split_stride, float *hidden,
                         const float *norm_w, float eps, T *out, const uint32_t *row_map,
-                        uint32_t out_rows, uint32_t H, uint32_t threads, cudaStream_t stream) {
+                        uint32_t out_rows, uint32_t H, uint32_t threads, cudaStream_t stream, uint32_t *ready) {
   ORION_CUDA_CHECK("residual_rmsnorm",
                    launch_pdl(residual_rmsnorm_vec_kernel<T, CHUNKS>, dim3(out_rows), dim3(threads), 0, stream,
-                              partial, splits, split_stride, hidden, norm_w, eps, out, row_map, H));
+                              partial, splits, split_stride, hidden, norm_w, eps, out, row_map, H, ready));
   return after_launch("residual_rmsnorm");
 }
 }  // namespace
@@ -542,7 +547,7 @@ template <typename T>
 int launch_residual_rmsnorm(const float *partial, uint32_t splits, size_t split_stride,
                             float *hidden, const float *norm_w, float eps, T *out,
                             const uint32_t *row_map, uint32_t out_rows, uint32_t hidden_size,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, uint32_t *ready) {
   if (out_rows == 0) return ORION_OK;
   if (hidden_size % 4 == 0 && hidden_size / 4 <= 4096 && split_stride % 4 == 0) {
     const uint32_t nvec = hidden_size / 4;
@@ -550,13 +555,14 @@ int launch_residual_rmsnorm(const float *partial, uint32_t splits, size_t split_
     const uint32_t chunks = (nvec + threads - 1) / threads;
     if (chunks == 1)
       return launch_residual_vec<T, 1>(partial, splits, split_stride, hidden, norm_w, eps, out, row_map,
-                                       out_rows, hidden_size, threads, stream);
+                                       out_rows, hidden_size, threads, stream, ready);
     if (chunks == 2)
       return launch_residual_vec<T, 2>(partial, splits, split_stride, hidden, norm_w, eps, out, row_map,
-                                       out_rows, hidden_size, threads, stream);
+                                       out_rows, hidden_size, threads, stream, ready);
     return launch_residual_vec<T, 4>(partial, splits, split_stride, hidden, norm_w, eps, out, row_map,
-                                     out_rows, hidden_size, threads, stream);
+                                     out_rows, hidden_size, threads, stream, ready);
   }
+  if (ready) return set_error(ORION_ERR_INTERNAL, "the scalar norm kernel counts no finished rows");
   const size_t smem = (size_t)hidden_size * sizeof(float);
   if (smem > 200 * 1024)
     return set_error(ORION_ERR_INTERNAL, "hidden size %u too large for the fused norm kernel",
@@ -575,7 +581,7 @@ template <typename T>
 int launch_rmsnorm_rows(const float *x, const float *norm_w, float eps, T *out, uint32_t rows,
                         uint32_t cols, cudaStream_t stream) {
   return launch_residual_rmsnorm<T>(nullptr, 0, 0, const_cast<float *>(x), norm_w, eps, out,
-                                    nullptr, rows, cols, stream);
+                                    nullptr, rows, cols, stream, nullptr);
 }
 
 template <typename T>
@@ -739,7 +745,7 @@ int launch_fill_normal(T *dst, size_t n, uint64_t seed, cudaStream_t stream) {
                                        T *, uint32_t, uint32_t, cudaStream_t);                    \
   template int launch_residual_rmsnorm<T>(const float *, uint32_t, size_t, float *, const float *, \
                                           float, T *, const uint32_t *, uint32_t, uint32_t,       \
-                                          cudaStream_t);                                          \
+                                          cudaStream_t, uint32_t *);                              \
   template int launch_rmsnorm_rows<T>(const float *, const float *, float, T *, uint32_t,         \
                                       uint32_t, cudaStream_t);                                    \
   template int launch_rope_kvwrite<T>(const float *, uint32_t, size_t, const float *,             \

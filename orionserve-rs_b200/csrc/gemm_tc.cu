@@ -205,7 +205,7 @@ template <int TOKN, int WST, int XST, int MT, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                float *__restrict__ partial, bf16 *__restrict__ act, uint32_t M, uint32_t N, uint32_t K,
-               uint32_t splits, uint32_t cluster_reduce, uint32_t ldc, PrefetchHint next) {
+               uint32_t splits, uint32_t cluster_reduce, uint32_t ldc, PrefetchHint next, ReadyWait ready) {
   using Cfg = TcConfig<TOKN, WST, XST, MT, PAIR>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
@@ -304,7 +304,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else if (warp == 2) {
     // Activation producer: waits for the preceding kernel, then keeps the short x ring full.
     if (lane == 0) {
-      pdl_wait();
+      if (ready.counter) {  // the activations' producer counts its finished CTAs: no wait for its completion
+        if (!wait_ready(ready)) atomicOr(&g_gemm_error, 2u);
+        fence_proxy_async_all();
+      } else {
+        pdl_wait();
+      }
       ORION_GTRACE(tslot, 3);
       for (uint32_t i = 0; i < my_kb; ++i) {
         const uint32_t s = i % XST, use = i / XST;
@@ -363,8 +368,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // Epilogue warps: warp w may touch tensor-memory lanes 32*(w%4) .. +31.
     const uint32_t lq = warp & 3;
     // The partial buffer may still be read by the kernel before the producer of x: wait for the
-    // predecessor here, while the main loop runs, rather than after the accumulator is ready.
-    pdl_wait();
+    // predecessor here, while the main loop runs, rather than after the accumulator is ready. (With a
+    // ready counter the producer has read the buffer before it counted, and the accumulator follows the count.)
+    if (!ready.counter) pdl_wait();
     if (my_kb > 0) {
       if (!mbar_wait(acc_ready, 0)) ok = false;
     }
@@ -534,7 +540,7 @@ int cached_map(const void *base, uint64_t rows, uint64_t k, uint64_t ld, uint32_
 template <int TOKN, int WST, int XST, int MT = 1, bool PAIR = false>
 int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial, bf16 *act,
               uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, bool cluster_reduce, uint32_t ldc,
-              PrefetchHint next, cudaStream_t stream) {
+              PrefetchHint next, cudaStream_t stream, ReadyWait ready = {}) {
   if (ldc == 0) ldc = n;
   if (ldc != n && (splits != 1 || act != nullptr))
     return set_error(ORION_ERR_INTERNAL, "a strided GEMM output needs one k split and f32 results");
@@ -552,14 +558,14 @@ int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *p
       return set_error(ORION_ERR_INTERNAL, "the paired GEMM needs an even number of weight tile groups and no cluster split-K");
     ORION_CUDA_CHECK("gemm_tc", launch_pdl_cluster(gemm_tc_kernel<TOKN, WST, XST, MT, PAIR>, grid, dim3(kThreads), dim3(2, 1, 1),
                                                    Cfg::kSmemBytes, stream, *mw, *mx, partial, act, rows, n, k, splits,
-                                                   0u, ldc, next));
+                                                   0u, ldc, next, ready));
   } else if (cluster_reduce)
     ORION_CUDA_CHECK("gemm_tc", launch_pdl_cluster(gemm_tc_kernel<TOKN, WST, XST, MT, PAIR>, grid, dim3(kThreads), dim3(1, 1, splits),
                                                    Cfg::kSmemBytes, stream, *mw, *mx, partial, act, rows, n, k, splits,
-                                                   1u, ldc, next));
+                                                   1u, ldc, next, ready));
   else
     ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, WST, XST, MT, PAIR>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
-                                           *mw, *mx, partial, act, rows, n, k, splits, 0u, ldc, next));
+                                           *mw, *mx, partial, act, rows, n, k, splits, 0u, ldc, next, ready));
   count_launch();
   ORION_CUDA_CHECK("gemm_tc", cudaGetLastError());
   return ORION_OK;
@@ -618,7 +624,7 @@ bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint
 
 int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
                    uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream,
-                   PrefetchHint next, bf16 *act, bool cluster_reduce, uint32_t ldc) {
+                   PrefetchHint next, bf16 *act, bool cluster_reduce, uint32_t ldc, ReadyWait ready) {
   const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
   if (cluster_reduce && (splits < 2 || splits > 8 || act != nullptr))
     return set_error(ORION_ERR_INTERNAL, "cluster split-K needs 2..8 splits and f32 output");
@@ -632,28 +638,28 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
   if (rows > 256 && g_prefill_fill == 1 && ((n + kTileN - 1) / kTileN) * ((rows + 255) / 256) < 148) tt = 128;
   switch (tt) {
     case 16:
-      return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
-                  : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
+      return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
+                  : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
     case 32:
-      return deep ? launch_tc<32, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
-                  : launch_tc<32, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
+      return deep ? launch_tc<32, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
+                  : launch_tc<32, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
     case 64:
-      return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
-                  : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
+      return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
+                  : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
     case 128:
       return g_mid_tile == 0
-                 ? launch_tc<128, 4, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
-                 : launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
+                 ? launch_tc<128, 4, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
+                 : launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
     default: {
       const uint32_t mt = (!cluster_reduce && prefill_weight_tiles(rows, n) == 2) ? 2 : 1;
       // CTA pairs: each CTA loads half of the activation tile, so the rings go a stage deeper
       const bool pair = (g_gemm_pair >= 2 || (g_gemm_pair == 1 && rows >= kPairMinRows)) && !cluster_reduce &&
                         (((n + mt * kTileN - 1) / (mt * kTileN)) & 1u) == 0;
       if (mt == 2)
-        return pair ? launch_tc<256, 4, 4, 2, true>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
-                    : launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
-      return pair ? launch_tc<256, 6, 6, 1, true>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream)
-                  : launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream);
+        return pair ? launch_tc<256, 4, 4, 2, true>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
+                    : launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
+      return pair ? launch_tc<256, 6, 6, 1, true>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
+                  : launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
     }
   }
 }
@@ -760,27 +766,27 @@ size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t
 }
 
 int launch_gemm_swiglu(const bf16 *x, uint32_t ldx, const bf16 *w_interleaved, uint32_t ldw, bf16 *act, uint32_t rows,
-                       uint32_t ffn, uint32_t k, cudaStream_t stream, PrefetchHint next) {
+                       uint32_t ffn, uint32_t k, cudaStream_t stream, PrefetchHint next, ReadyWait ready) {
   if (!gemm_tc_supported(rows, 2 * ffn, k, ldx, ldw, x, w_interleaved))
     return set_error(ORION_ERR_INTERNAL, "tensor-core GEMM planned for an unaligned operand");
-  return launch_gemm_tc(x, ldx, w_interleaved, ldw, nullptr, rows, 2 * ffn, k, 1, stream, next, act, false);
+  return launch_gemm_tc(x, ldx, w_interleaved, ldw, nullptr, rows, 2 * ffn, k, 1, stream, next, act, false, 0, ready);
 }
 
 template <>
 int launch_gemm<float>(const float *x, uint32_t ldx, const float *w, uint32_t ldw, float *partial,
-                       uint32_t rows, uint32_t n, uint32_t k, GemmPlan, cudaStream_t stream, PrefetchHint) {
+                       uint32_t rows, uint32_t n, uint32_t k, GemmPlan, cudaStream_t stream, PrefetchHint, ReadyWait) {
   return launch_gemm_simt<float>(x, ldx, w, ldw, partial, rows, n, k, stream);
 }
 
 template <>
 int launch_gemm<bf16>(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
                       uint32_t rows, uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream,
-                      PrefetchHint next) {
+                      PrefetchHint next, ReadyWait ready) {
   if (plan.tensor_core) {
     if (!gemm_tc_supported(rows, n, k, ldx, ldw, x, w))
       return set_error(ORION_ERR_INTERNAL, "tensor-core GEMM planned for an unaligned operand");
     return launch_gemm_tc(x, ldx, w, ldw, partial, rows, n, k, plan.splits, stream, next, nullptr, plan.cluster_reduce,
-                          plan.ldc);
+                          plan.ldc, ready);
   }
   if (plan.ldc != 0 && plan.ldc != n) return set_error(ORION_ERR_INTERNAL, "a strided GEMM output needs the tensor-core path");
   return launch_gemm_simt<bf16>(x, ldx, w, ldw, partial, rows, n, k, stream);

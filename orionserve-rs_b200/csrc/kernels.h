@@ -50,7 +50,7 @@ template <typename T>
 int launch_residual_rmsnorm(const float *partial, uint32_t splits, size_t split_stride,
                             float *hidden, const float *norm_w, float eps, T *out,
                             const uint32_t *row_map, uint32_t out_rows, uint32_t hidden_size,
-                            cudaStream_t stream);
+                            cudaStream_t stream, uint32_t *ready = nullptr);  // ready: every CTA (one per output row) adds 1 when done
 
 // Plain rms_norm of f32 rows into T (tensor.rs:143-163) for the op-level API.
 template <typename T>
@@ -236,7 +236,8 @@ struct TpPeers {
 template <typename T>
 int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, const float *partial, uint32_t splits,
                                          size_t split_stride, float *hidden, const float *norm_w, float eps, T *out,
-                                         uint32_t rows, uint32_t hidden_size, bool two_shot, cudaStream_t stream);
+                                         uint32_t rows, uint32_t hidden_size, bool two_shot, cudaStream_t stream,
+                                         uint32_t *ready = nullptr);  // ready: every CTA (one per row) adds 1 when done
 int tp_poll_error(uint32_t *code);
 // Vocabulary-parallel LM head: `launch_tp_signal` (ranks other than the leader) stores `epoch` into the
 // rank's flag in the leader's memory once the preceding kernel of the stream has completed;
@@ -267,7 +268,8 @@ struct GemmPlan {
 GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint32_t ldw);
 template <typename T>
 int launch_gemm(const T *x, uint32_t ldx, const T *w, uint32_t ldw, float *partial, uint32_t rows,
-                uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream, PrefetchHint next = {});
+                uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream, PrefetchHint next = {},
+                ReadyWait ready = {});  // `ready`: honoured by the tensor-core path only (GemmPlan::tensor_core)
 size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t k);
 // Number of CTAs split-K aims for on small batches (default 296, two per SM).
 void gemm_set_target_ctas(uint32_t ctas);
@@ -283,12 +285,13 @@ bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint
                        const void *x, const void *w);
 int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
                    uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream,
-                   PrefetchHint next = {}, bf16 *act = nullptr, bool cluster_reduce = false, uint32_t ldc = 0);
+                   PrefetchHint next = {}, bf16 *act = nullptr, bool cluster_reduce = false, uint32_t ldc = 0,
+                   ReadyWait ready = {});
 // Gate/up projection with SwiGLU in the epilogue: `w_interleaved` is [2 * ffn][k] with gate row f
 // at 2f and up row f at 2f + 1; writes act[r][f] = silu(x.gate_f) * (x.up_f) and no partials.
 // One k split only (gemm_plan(...).splits == 1 and .tensor_core).
 int launch_gemm_swiglu(const bf16 *x, uint32_t ldx, const bf16 *w_interleaved, uint32_t ldw, bf16 *act, uint32_t rows,
-                       uint32_t ffn, uint32_t k, cudaStream_t stream, PrefetchHint next = {});
+                       uint32_t ffn, uint32_t k, cudaStream_t stream, PrefetchHint next = {}, ReadyWait ready = {});
 // Device error word set by kernels whose bounded waits ran out (0 = none).
 int gemm_tc_poll_error(uint32_t *code);
 

@@ -51,6 +51,9 @@ bool g_fuse_qkv = std::getenv("ORION_FUSE_QKV") ? std::atoi(std::getenv("ORION_F
 // Tuning A/B: ORION_FUSE_SWIGLU=0 keeps the separate SwiGLU kernel after the gate/up projection.
 bool g_fuse_swiglu = std::getenv("ORION_FUSE_SWIGLU") ? std::atoi(std::getenv("ORION_FUSE_SWIGLU")) != 0 : true;
 void model_set_prefetch_budget(size_t bytes) { g_prefetch_budget = bytes; }
+// Tuning A/B: ORION_READY_COUNTERS=0 makes the projection after a tensor-parallel hand-over wait for that
+// kernel's completion again instead of polling its count of finished rows.
+bool g_ready_counters = std::getenv("ORION_READY_COUNTERS") ? std::atoi(std::getenv("ORION_READY_COUNTERS")) != 0 : true;
 
 namespace {
 
@@ -146,7 +149,12 @@ class Model final : public ModelBase {
   // converting once at load like the reference's loader (loader.rs:74-96).
   int upload_slice(T *dst_t, float *dst_f, const void *src, int dtype, uint64_t C, uint64_t r0,
                    uint64_t r1, uint64_t c0, uint64_t c1);
-  int run_step(bool want_argmax);
+  int run_step_body(bool want_argmax);
+  int run_step(bool want_argmax) {
+    const int rc = run_step_body(want_argmax);
+    if (rc != ORION_OK) ready_resync_ = true;  // a counting kernel may have run without its consumer, or the other way round
+    return rc;
+  }
   // Waits for a stream of this model. Under tensor parallelism the wait watches the communicator
   // and is bounded in time, so a peer that died cannot hold the host inside a blocking synchronise.
   int wait_for(cudaStream_t s, const char *stage) {
@@ -159,7 +167,11 @@ class Model final : public ModelBase {
   // Row-parallel projection -> residual + norm. Single GPU: the fused residual/norm kernel.
   // Tensor parallel: the fused peer-memory all-reduce + residual + norm kernel, or NCCL followed
   // by the single-GPU kernel. `out_rows`/`row_map` select gathered output rows (final norm).
-  int handover(uint32_t splits, const float *norm_w, T *out, const uint32_t *row_map, uint32_t out_rows);
+  int handover(uint32_t splits, const float *norm_w, T *out, const uint32_t *row_map, uint32_t out_rows, bool count_ready = false);
+  // The running total of finished hand-over CTAs the next projection has to see (ReadyWait in common.cuh).
+  uint32_t *ready_ = nullptr;
+  uint32_t ready_total_ = 0;
+  bool ready_resync_ = false;  // a step failed between a counting kernel and its consumer: reread the counter
   // Vocabulary-parallel LM head under tensor parallelism: this rank holds rows [head_v0_, head_v0_ + head_vn_)
   // of the head, computes that column block of the logits and stores it straight into the leader's
   // logits buffer (peer-mapped); flags in the leader's memory tell it when every block has landed.
@@ -354,6 +366,8 @@ int Model<T>::init() {
   partial_floats_ = std::max(partial_floats_, gemm_partial_floats(kBf16, (uint32_t)Tm, 2 * lf_, (uint32_t)H));
   partial_floats_ = std::max(partial_floats_, gemm_partial_floats(kBf16, (uint32_t)Tm, (uint32_t)H, lf_));
   ORION_TRY(alloc(&partial_, partial_floats_));
+  ORION_TRY(alloc(&ready_, 1));
+  ORION_CUDA_CHECK("clear ready counter", cudaMemsetAsync(ready_, 0, sizeof(uint32_t), stream_));
   if (kBf16 && decode_attention_supported(kv_, lq_)) {
     for (uint32_t r = 1; r <= Sm; ++r) {
       // room for the uniform split of r equally long rows, and for up to eight pieces of the long
@@ -683,7 +697,7 @@ int Model<T>::tp_reduce(uint32_t *splits, size_t slab) {
 }
 
 template <typename T>
-int Model<T>::handover(uint32_t splits, const float *norm_w, T *out, const uint32_t *row_map, uint32_t out_rows) {
+int Model<T>::handover(uint32_t splits, const float *norm_w, T *out, const uint32_t *row_map, uint32_t out_rows, bool count_ready) {
   const uint32_t Tn = meta_.rows, H = d_.hidden_size;
   const size_t slab = (size_t)Tn * H;
   if (nccl_ && tp_fused_ && Tn <= kTpFusedMaxRows) {
@@ -694,19 +708,22 @@ int Model<T>::handover(uint32_t splits, const float *norm_w, T *out, const uint3
                                                       // 1 Mi elements on (128 rows x 8192) the two-shot kernel with its bf16
                                                       // units moves a quarter of the bytes and measured 6 % faster per step
                                                       tp_two_shot_ || (sizeof(T) == 2 && (size_t)Tn * H >= ((size_t)1 << 20)),
-                                                      stream_));
+                                                      stream_, count_ready && !row_map ? ready_ : nullptr));
+    if (count_ready && !row_map) ready_total_ += Tn;
     tp_epoch_ = tp_epoch_ == 0xFFFFFFFEu ? 1u : tp_epoch_ + 1;
     if (row_map) return launch_gather_rows<T>(normed_, row_map, out, out_rows, H, stream_);
     if (out != normed_) return set_error(ORION_ERR_INTERNAL, "fused hand-over writes the activation buffer only");
     return ORION_OK;
   }
   ORION_TRY(tp_reduce(&splits, slab));
-  return launch_residual_rmsnorm<T>(partial_, splits, slab, hidden_, norm_w, d_.rms_norm_eps, out, row_map, out_rows, H,
-                                    stream_);
+  ORION_TRY(launch_residual_rmsnorm<T>(partial_, splits, slab, hidden_, norm_w, d_.rms_norm_eps, out, row_map, out_rows, H,
+                                       stream_, count_ready ? ready_ : nullptr));
+  if (count_ready) ready_total_ += out_rows;
+  return ORION_OK;
 }
 
 template <typename T>
-int Model<T>::run_step(bool want_argmax) {
+int Model<T>::run_step_body(bool want_argmax) {
   const OrionModelDesc &d = d_;
   constexpr bool kBf16 = DTypeOf<T>::is_bf16;
   const uint32_t Tn = meta_.rows, S = meta_.seqs, H = d.hidden_size, hd = d.head_dim;
@@ -739,6 +756,22 @@ int Model<T>::run_step(bool want_argmax) {
   // L2 prefetch of the next projection's weights: only where the projections are bandwidth-bound
   // (decode-sized batches), and never more than a fraction of L2 per hand-over.
   const size_t budget = (kBf16 && Tn <= 256) ? g_prefetch_budget : 0;
+  // Under tensor parallelism the projection that follows a fused hand-over polls that kernel's count of finished
+  // rows instead of waiting for its completion: a kernel that has stored to peer memory releases its dependents
+  // about 3 us later than one that has not (measured 4.5 against 1.5 us), and the count does not wait for that
+  // (3.33 -> 3.25 ms per step at 2 ranks). On one GPU the two are equally fast, so the counter is left out. Never
+  // in a timing replay that leaves kernel families out, where the counting kernel may be missing.
+  const bool count_ready = g_ready_counters && kBf16 && nccl_ && tp_fused_ && Tn <= kTpFusedMaxRows && only_mask_ == 0;
+  if (ready_resync_) {
+    ORION_CUDA_CHECK("ready counter", cudaStreamSynchronize(stream_));
+    ORION_CUDA_CHECK("ready counter", cudaMemcpy(&ready_total_, ready_, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    ready_resync_ = false;
+  }
+  auto ready_for = [&](const GemmPlan &gp) {
+    ReadyWait r;
+    if (count_ready && gp.tensor_core) r.counter = ready_, r.target = ready_total_;
+    return r;
+  };
   auto hint = [&](const T *w, size_t elems) {
     PrefetchHint h;
     if (budget) {
@@ -752,7 +785,9 @@ int Model<T>::run_step(bool want_argmax) {
   for (uint32_t l = 0; l < d.num_layers; ++l) {
     const Layer &L = layers_[l];
     GemmPlan p = plan_for(Tn, nqkv, H);
-    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_qkv, H, partial_, Tn, nqkv, H, p, stream_); }));
+    // layer 0 follows the embedding kernel, which counts nothing
+    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_qkv, H, partial_, Tn, nqkv, H, p, stream_, PrefetchHint{},
+                                                              l > 0 ? ready_for(p) : ReadyWait{}); }));
     // Pure decode batches on the tuned path: the attention kernel folds the QKV partials, applies
     // RoPE and writes the KV slot itself, so the separate kernel (and its launch hop) is left out.
     const bool fuse_qkv = tuned_decode && g_fuse_qkv;
@@ -798,19 +833,19 @@ int Model<T>::run_step(bool want_argmax) {
     ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(attn_, qd, L.w_o, qd, partial_, Tn, H, qd, p, stream_,
                                                               hint(L.w_gu, (size_t)2 * lf_ * H)); }));
     const int handover_cat = nccl_ ? kProfCollective : kProfElementwise;
-    ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, L.post_norm, normed_, nullptr, Tn); }));
+    ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, L.post_norm, normed_, nullptr, Tn, count_ready); }));
     p = plan_for(Tn, 2 * lf_, H);
     bool fused_swiglu = false;
     if constexpr (kBf16) {
       if (p.tensor_core && p.splits == 1 && g_fuse_swiglu) {  // SwiGLU in the GEMM epilogue: no partials, no extra launch
         fused_swiglu = true;
         ORION_TRY(timed(kProfGemm, [&] { return launch_gemm_swiglu(normed_, H, L.w_gu, H, act_, Tn, lf_, H, stream_,
-                                                                    hint(L.w_down, (size_t)H * lf_)); }));
+                                                                    hint(L.w_down, (size_t)H * lf_), ready_for(p)); }));
       }
     }
     if (!fused_swiglu) {
       ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_gu, H, partial_, Tn, 2 * lf_, H, p, stream_,
-                                                                hint(L.w_down, (size_t)H * lf_)); }));
+                                                                hint(L.w_down, (size_t)H * lf_), ready_for(p)); }));
       ORION_TRY(timed(kProfElementwise, [&] { return launch_swiglu<T>(partial_, p.out_slabs, (size_t)Tn * 2 * lf_, act_, Tn, lf_, stream_,
                                                                        kInterleaveGateUp); }));
     }
@@ -819,7 +854,7 @@ int Model<T>::run_step(bool want_argmax) {
                                                               l + 1 < d.num_layers ? hint(layers_[l + 1].w_qkv, (size_t)nqkv * H)
                                                                                    : hint(lm_head_, (size_t)head_vn_ * H)); }));
     if (l + 1 < d.num_layers) {
-      ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, layers_[l + 1].in_norm, normed_, nullptr, Tn); }));
+      ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, layers_[l + 1].in_norm, normed_, nullptr, Tn, count_ready); }));
     } else if (!meta_.zero_count) {
       // Final norm over the last row of every sequence (transformer.rs:401-428;
       // the norm is row-wise, so gathering first gives the same rows).

@@ -140,7 +140,8 @@ template <typename T, typename Acc, bool Packed>
 __global__ void __launch_bounds__(1024)
 tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ partial,
                                      uint32_t splits, size_t split_stride, float *__restrict__ hidden,
-                                     const float *__restrict__ w, float eps, T *__restrict__ out, uint32_t H) {
+                                     const float *__restrict__ w, float eps, T *__restrict__ out, uint32_t H,
+                                     uint32_t *__restrict__ ready) {
   __shared__ Acc red[32];
   pdl_trigger();
   trace(0);
@@ -209,6 +210,10 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
     }
   }
   trace(4);
+  if (ready) {  // the next projection polls this count instead of waiting for the kernel to complete
+    __syncthreads();
+    if (threadIdx.x == 0) signal_ready(ready);
+  }
 }
 
 // Two-shot variant for more than two ranks. One CTA per row on every rank; inside a row the
@@ -230,7 +235,7 @@ template <typename T, typename Acc, bool Packed>
 __global__ void __launch_bounds__(1024)
 tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ partial, uint32_t splits,
                   size_t split_stride, float *__restrict__ hidden, const float *__restrict__ w, float eps,
-                  T *__restrict__ out, uint32_t rows, uint32_t H) {
+                  T *__restrict__ out, uint32_t rows, uint32_t H, uint32_t *__restrict__ ready) {
   __shared__ Acc red[32];
   pdl_trigger();
   trace(0);
@@ -316,6 +321,10 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
     }
   }
   trace(4);
+  if (ready) {  // the next projection polls this count instead of waiting for the kernel to complete
+    __syncthreads();
+    if (threadIdx.x == 0) signal_ready(ready);
+  }
 }
 
 }  // namespace
@@ -323,7 +332,8 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
 template <typename T>
 int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, const float *partial, uint32_t splits,
                                          size_t split_stride, float *hidden, const float *norm_w, float eps, T *out,
-                                         uint32_t rows, uint32_t hidden_size, bool two_shot, cudaStream_t stream) {
+                                         uint32_t rows, uint32_t hidden_size, bool two_shot, cudaStream_t stream,
+                                         uint32_t *ready) {
   if (hidden_size % 4 != 0 || hidden_size / 4 > 4096 || split_stride % 4 != 0 ||
       (size_t)rows * hidden_size > peers.slot_floats || epoch == 0 || epoch == 0xFFFFFFFFu)
     return set_error(ORION_ERR_INTERNAL, "fused tensor-parallel hand-over: unsupported shape or epoch");
@@ -342,29 +352,29 @@ int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, c
   if (two_shot && sizeof(T) == 2 && packed)
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
                      launch_pdl(tp_twoshot_kernel<T, Acc, true>, dim3(rows), dim3(threads), 0, stream, peers, epoch,
-                                partial, splits, split_stride, hidden, norm_w, eps, out, rows, hidden_size));
+                                partial, splits, split_stride, hidden, norm_w, eps, out, rows, hidden_size, ready));
   else if (two_shot)
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
                      launch_pdl(tp_twoshot_kernel<T, Acc, false>, dim3(rows), dim3(threads), 0, stream, peers, epoch,
-                                partial, splits, split_stride, hidden, norm_w, eps, out, rows, hidden_size));
+                                partial, splits, split_stride, hidden, norm_w, eps, out, rows, hidden_size, ready));
   else if (sizeof(T) == 2 && packed)
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
                      launch_pdl(tp_allreduce_residual_rmsnorm_kernel<T, Acc, true>, dim3(rows), dim3(threads), 0, stream, peers,
-                                epoch, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size));
+                                epoch, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size, ready));
   else
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
                      launch_pdl(tp_allreduce_residual_rmsnorm_kernel<T, Acc, false>, dim3(rows), dim3(threads), 0, stream, peers,
-                                epoch, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size));
+                                epoch, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size, ready));
   count_launch();
   ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm", cudaGetLastError());
   return ORION_OK;
 }
 template int launch_tp_allreduce_residual_rmsnorm<float>(const TpPeers &, uint32_t, const float *, uint32_t, size_t,
                                                          float *, const float *, float, float *, uint32_t, uint32_t,
-                                                         bool, cudaStream_t);
+                                                         bool, cudaStream_t, uint32_t *);
 template int launch_tp_allreduce_residual_rmsnorm<bf16>(const TpPeers &, uint32_t, const float *, uint32_t, size_t,
                                                         float *, const float *, float, bf16 *, uint32_t, uint32_t,
-                                                        bool, cudaStream_t);
+                                                        bool, cudaStream_t, uint32_t *);
 
 namespace {
 // Vocabulary-parallel LM head: a rank that has stored its column block of the logits into the
