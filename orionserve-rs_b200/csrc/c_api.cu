@@ -603,22 +603,26 @@ void orion_cuda_host_free(void *p) { if (p) cudaFreeHost(p); }
 
 int orion_cuda_set_l2_prefetch_bytes(uint64_t bytes) {
   model_set_prefetch_budget((size_t)bytes);
+  ++g_tuning_generation;
   return ORION_OK;
 }
 
 int orion_cuda_set_programmatic_launch(int enabled) {
   g_pdl_enabled = enabled != 0;
+  ++g_tuning_generation;
   return ORION_OK;
 }
 
 int orion_cuda_attention_set_tuning(int stages, uint32_t cta_target) {
   decode_set_tuning(stages, cta_target);
+  ++g_tuning_generation;
   return ORION_OK;
 }
 
 int orion_cuda_gemm_set_tuning(uint32_t ctas, int small_batch_stages) {
   if (small_batch_stages) gemm_set_small_stages(small_batch_stages);
   gemm_set_target_ctas(ctas);
+  ++g_tuning_generation;
   return ORION_OK;
 }
 

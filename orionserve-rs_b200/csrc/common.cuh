@@ -43,6 +43,8 @@ inline void count_launch() { ++g_launch_count; }
 // Launches `kernel` with the programmatic-stream-serialization attribute (see
 // pdl_wait / pdl_trigger below). `enabled` false gives a plain launch.
 extern bool g_pdl_enabled;
+// Counts the calls that change a tuning value; a captured step graph belongs to the value it was captured under.
+extern uint32_t g_tuning_generation;
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                               cudaStream_t stream, Args... args) {

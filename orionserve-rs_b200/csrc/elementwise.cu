@@ -12,6 +12,7 @@ namespace orion {
 
 thread_local uint64_t g_launch_count = 0;
 bool g_pdl_enabled = true;
+uint32_t g_tuning_generation = 0;
 
 namespace {
 

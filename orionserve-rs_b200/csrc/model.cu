@@ -8,6 +8,8 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <tuple>
 
 namespace orion {
 
@@ -51,6 +53,12 @@ bool g_fuse_qkv = std::getenv("ORION_FUSE_QKV") ? std::atoi(std::getenv("ORION_F
 // Tuning A/B: ORION_FUSE_SWIGLU=0 keeps the separate SwiGLU kernel after the gate/up projection.
 bool g_fuse_swiglu = std::getenv("ORION_FUSE_SWIGLU") ? std::atoi(std::getenv("ORION_FUSE_SWIGLU")) != 0 : true;
 void model_set_prefetch_budget(size_t bytes) { g_prefetch_budget = bytes; }
+// Tuning A/B: ORION_STEP_GRAPH=0 launches every decode step kernel by kernel.
+bool g_step_graph = std::getenv("ORION_STEP_GRAPH") ? std::atoi(std::getenv("ORION_STEP_GRAPH")) != 0 : true;
+// Capture and instantiation take about 12 ms and save 0.09 ms per step: only a layout that stays is worth it.
+// ORION_STEP_GRAPH_AFTER overrides the number of repeats (the parity tests use 2).
+const uint32_t kGraphAfterSteps = std::getenv("ORION_STEP_GRAPH_AFTER") ? (uint32_t)std::max(1, std::atoi(std::getenv("ORION_STEP_GRAPH_AFTER"))) : 32u;
+constexpr size_t kMaxStepGraphs = 16;
 // Tuning A/B: ORION_READY_COUNTERS=0 makes the projection after a tensor-parallel hand-over wait for that
 // kernel's completion again instead of polling its count of finished rows.
 bool g_ready_counters = std::getenv("ORION_READY_COUNTERS") ? std::atoi(std::getenv("ORION_READY_COUNTERS")) != 0 : true;
@@ -87,6 +95,7 @@ class Model final : public ModelBase {
   ~Model() override {
     cudaSetDevice(ordinal_);
     if (stream_) cudaStreamSynchronize(stream_);
+    drop_graphs();
     for (void *p : ipc_opened_) cudaIpcCloseMemHandle(p);
     for (void *p : allocs_) cudaFree(p);
     if (h_meta_) cudaFreeHost(h_meta_);
@@ -149,11 +158,60 @@ class Model final : public ModelBase {
   // converting once at load like the reference's loader (loader.rs:74-96).
   int upload_slice(T *dst_t, float *dst_f, const void *src, int dtype, uint64_t C, uint64_t r0,
                    uint64_t r1, uint64_t c0, uint64_t c1);
-  int run_step_body(bool want_argmax);
+  // part 0: the whole step; 1: the embedding and the layers (what a step graph holds); 2: the LM head and what follows
+  int run_step_body(bool want_argmax, int part = 0);
+  int run_step_graphed(bool want_argmax);
   int run_step(bool want_argmax) {
-    const int rc = run_step_body(want_argmax);
+    const int rc = graph_eligible() ? run_step_graphed(want_argmax) : run_step_body(want_argmax);
     if (rc != ORION_OK) ready_resync_ = true;  // a counting kernel may have run without its consumer, or the other way round
     return rc;
+  }
+  // Pure decode steps on one GPU replay a CUDA graph of the embedding and the layers once the same batch layout has
+  // come 32 times in a row: every kernel argument of such a step is a pointer into buffers that do not move (the
+  // step's tokens, positions and block tables are uploaded into the metadata array before the launch), so the graph
+  // holds for as long as the layout (rows, sequences, offsets inside the metadata array, context splits) does.
+  struct GraphKey {
+    uint32_t rows, seqs, splits, blocks_per_split, generation;
+    size_t offsets[8];
+    bool operator<(const GraphKey &o) const {
+      return std::tie(rows, seqs, splits, blocks_per_split, generation, offsets[0], offsets[1], offsets[2], offsets[3], offsets[4],
+                      offsets[5], offsets[6], offsets[7]) <
+             std::tie(o.rows, o.seqs, o.splits, o.blocks_per_split, o.generation, o.offsets[0], o.offsets[1], o.offsets[2], o.offsets[3],
+                      o.offsets[4], o.offsets[5], o.offsets[6], o.offsets[7]);
+    }
+    bool operator==(const GraphKey &o) const { return !(*this < o) && !(o < *this); }
+  };
+  struct StepGraph {
+    cudaGraphExec_t exec = nullptr;
+    uint64_t launches = 0;
+  };
+  std::map<GraphKey, StepGraph> graphs_;
+  GraphKey last_key_{};
+  uint32_t key_streak_ = 0;
+  bool graph_eligible() const {
+    return g_step_graph && DTypeOf<T>::is_bf16 && meta_.decode && !meta_.zero_count && !nccl_ && !prof_on_ && only_mask_ == 0 &&
+           decode_attention_supported(kv_, lq_);
+  }
+  void step_decode_plan(uint32_t *splits, uint32_t *blocks_per_split) const {
+    const DecodePlan dp = decode_plan(meta_.rows, lkv_, meta_.total_blocks, meta_.max_position, d_.block_size, 32);
+    uint32_t want = dp.splits;
+    while (want > 1 && decode_scratch_floats(meta_.rows, lq_, d_.head_dim, want) > dscratch_floats_) --want;
+    *splits = want;
+    *blocks_per_split = dp.blocks_per_split;
+  }
+  GraphKey layout_key() const {
+    GraphKey key{};
+    key.rows = meta_.rows, key.seqs = meta_.seqs, key.generation = g_tuning_generation;
+    step_decode_plan(&key.splits, &key.blocks_per_split);
+    const size_t offs[8] = {meta_.tokens, meta_.positions, meta_.slot_block, meta_.slot_slot, meta_.seq_of_row, meta_.last_rows,
+                            meta_.offsets, meta_.tables};
+    for (int i = 0; i < 8; ++i) key.offsets[i] = offs[i];
+    return key;
+  }
+  void drop_graphs() {
+    for (auto &g : graphs_)
+      if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+    graphs_.clear();
   }
   // Waits for a stream of this model. Under tensor parallelism the wait watches the communicator
   // and is bounded in time, so a peer that died cannot hold the host inside a blocking synchronise.
@@ -723,7 +781,41 @@ int Model<T>::handover(uint32_t splits, const float *norm_w, T *out, const uint3
 }
 
 template <typename T>
-int Model<T>::run_step_body(bool want_argmax) {
+int Model<T>::run_step_graphed(bool want_argmax) {
+  const GraphKey key = layout_key();
+  key_streak_ = (key_streak_ > 0 && key == last_key_) ? key_streak_ + 1 : 1;
+  last_key_ = key;
+  auto it = graphs_.find(key);
+  if (it == graphs_.end() && key_streak_ >= kGraphAfterSteps) {
+    if (graphs_.size() >= kMaxStepGraphs) drop_graphs();
+    cudaGraph_t graph = nullptr;
+    StepGraph sg;  // stays without an executable graph if anything below fails: the layout is then launched kernel by kernel
+    const uint64_t before = g_launch_count;
+    if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+      const int rc = run_step_body(false, 1);
+      const cudaError_t ce = cudaStreamEndCapture(stream_, &graph);
+      sg.launches = g_launch_count - before;
+      if (rc != ORION_OK || ce != cudaSuccess || cudaGraphInstantiate(&sg.exec, graph, 0) != cudaSuccess) sg.exec = nullptr;
+      if (graph) cudaGraphDestroy(graph);
+    }
+    g_launch_count = before;
+    if (!sg.exec) {
+      cudaGetLastError();  // the failed capture's error is not the step's
+      clear_error();
+    }
+    it = graphs_.emplace(key, sg).first;
+  }
+  if (it != graphs_.end() && it->second.exec) {
+    ORION_CUDA_CHECK("step graph launch", cudaGraphLaunch(it->second.exec, stream_));
+    g_launch_count += it->second.launches;
+  } else {
+    ORION_TRY(run_step_body(want_argmax, 1));
+  }
+  return run_step_body(want_argmax, 2);
+}
+
+template <typename T>
+int Model<T>::run_step_body(bool want_argmax, int part) {
   const OrionModelDesc &d = d_;
   constexpr bool kBf16 = DTypeOf<T>::is_bf16;
   const uint32_t Tn = meta_.rows, S = meta_.seqs, H = d.hidden_size, hd = d.head_dim;
@@ -781,8 +873,9 @@ int Model<T>::run_step_body(bool want_argmax) {
     return h;
   };
 
-  ORION_TRY(timed(kProfElementwise, [&] { return launch_embed_rmsnorm<T>(embed_, tokens, layers_[0].in_norm, d.rms_norm_eps, hidden_, normed_, Tn, H, stream_); }));
-  for (uint32_t l = 0; l < d.num_layers; ++l) {
+  if (part != 2)
+    ORION_TRY(timed(kProfElementwise, [&] { return launch_embed_rmsnorm<T>(embed_, tokens, layers_[0].in_norm, d.rms_norm_eps, hidden_, normed_, Tn, H, stream_); }));
+  for (uint32_t l = 0; part != 2 && l < d.num_layers; ++l) {
     const Layer &L = layers_[l];
     GemmPlan p = plan_for(Tn, nqkv, H);
     // layer 0 follows the embedding kernel, which counts nothing
@@ -864,7 +957,7 @@ int Model<T>::run_step_body(bool want_argmax) {
       ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, final_norm_, normed_, nullptr, Tn); }));
     }
   }
-  if (meta_.zero_count) return ORION_OK;
+  if (part == 1 || meta_.zero_count) return ORION_OK;
   if (head_parallel_) {
     // This rank's column block of the logits goes straight into the leader's buffer (plain peer stores from
     // the GEMM epilogue), then the rank raises its flag there; the leader waits for all flags.
@@ -1120,8 +1213,16 @@ int Model<T>::replay(int iterations, uint32_t category_mask, float *elapsed_ms) 
     return set_error(ORION_ERR_INVALID_REQUEST, "replay needs a preceding successful forward");
   ORION_CUDA_CHECK("set device", cudaSetDevice(ordinal_));
   ORION_CUDA_CHECK("replay", cudaStreamSynchronize(stream_));
-  ORION_CUDA_CHECK("replay", cudaEventRecord(ev0_, stream_));
   only_mask_ = category_mask & ((1u << kProfCategories) - 1);
+  // a layout that will be replayed as a graph is brought there before the clock starts
+  for (uint32_t i = 0; i <= kGraphAfterSteps && graph_eligible() && graphs_.find(layout_key()) == graphs_.end(); ++i) {
+    const int rc = run_step(false);
+    if (rc != ORION_OK) {
+      only_mask_ = 0;
+      return rc;
+    }
+  }
+  ORION_CUDA_CHECK("replay", cudaEventRecord(ev0_, stream_));
   for (int i = 0; i < iterations; ++i) {
     g_launch_count = 0;
     const int rc = run_step(false);

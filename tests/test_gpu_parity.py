@@ -709,3 +709,21 @@ def test_cluster_split_k_variant_matches_the_oracle(pkg, backend):
                         "-m", "gpu", "-k", "linear_bf16_tensor_core or config1_greedy or chunked_prefill"],
                        cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:]
+
+
+def test_decode_steps_replayed_as_a_graph_match_the_oracle(pkg, backend):
+    """A decode batch whose layout repeats is replayed as a CUDA graph of the embedding and the layers (after 32
+    repeats by default; the count is read when the library loads). The greedy-decode comparison with the oracle, the
+    engine loop and the timing replays run once more in a child process that captures after two repeats, so that
+    nearly every decode step of those tests goes through a graph."""
+    import os
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+    env = dict(os.environ, ORION_STEP_GRAPH_AFTER="2")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_parity.py"),
+                        os.path.join(ROOT, "tests", "test_gpu_engine.py"), "-q", "-x", "-m", "gpu",
+                        "-k", "config1_greedy or timing_replays or engine or qwen2_7b_head_layout"],
+                       cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:]
