@@ -425,6 +425,9 @@ def tp_check_batches(pkg, seed=29):
     return steps
 
 
+GRAPH_REPEATS = 34  # two more than the repeats after which the library captures a decode step (32)
+
+
 def tp_parity(pkg, backend, dist, rank, world, dtype_name="BF16", model=None, num_blocks=TP_CHECK_BLOCKS, batches=None):
     """Runs the check model at tp_world = `world` and compares rank 0's logits and every rank's KV arena
     with the CPU oracle's unsharded forward (the oracle is the checker here, nothing of it is timed).
@@ -444,6 +447,15 @@ def tp_parity(pkg, backend, dist, rank, world, dtype_name="BF16", model=None, nu
                                        max_batch_tokens=max_tokens, max_batch_sequences=max_seqs, tp_rank=rank,
                                        tp_world=world, nccl_unique_id=box[0])
     got = [dev.forward(b).logits for b in batches]
+    # A decode batch whose layout repeats is replayed as a CUDA graph after GRAPH_REPEATS - 2 steps: the first decode
+    # batch of the check is run that often once more (the same tokens at the same positions rewrite the same KV
+    # slots with the same values), and the last result, produced by a graph, must be the first one bit for bit.
+    decode = next((i for i, b in enumerate(batches) if not b.has_prefill and len(b.tokens) <= 256), None)
+    graph_same = None
+    if decode is not None and dtype_name == "BF16":
+        for _ in range(GRAPH_REPEATS):
+            again = dev.forward(batches[decode]).logits
+        graph_same = bool(rank != 0 or np.array_equal(again, got[decode]))
     kv_dev = dev.read_kv()
     del dev
     lkv = m["num_kv_heads"] // world
@@ -473,10 +485,15 @@ def tp_parity(pkg, backend, dist, rank, world, dtype_name="BF16", model=None, nu
     kv_ok = bool(np.array_equal(kv_dev != 0, mine != 0) and np.allclose(kv_dev, mine, atol=tol, rtol=tol))
     flags = [None] * world
     dist.all_gather_object(flags, kv_ok)
+    if graph_same is not None:
+        same = [None] * world
+        dist.all_gather_object(same, graph_same)
+        report["graph_replay_identical"] = all(same)
     if rank == 0:
         report["kv_slots_equal"] = all(flags)
         bars = (2e-2, 3e-2) if dtype_name == "BF16" else (1e-3, 1e-3)
-        report["ok"] = bool(report["softmax_max_abs"] <= bars[0] and report["max_rel_err"] <= bars[1] and all(flags))
+        report["ok"] = bool(report["softmax_max_abs"] <= bars[0] and report["max_rel_err"] <= bars[1] and all(flags) and
+                            report.get("graph_replay_identical", True))
     return report
 
 

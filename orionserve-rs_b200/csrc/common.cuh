@@ -266,12 +266,18 @@ __device__ __forceinline__ void prefetch_slice(PrefetchHint h) {
 struct ReadyWait {
   const uint32_t *counter = nullptr;  // nullptr: wait for the preceding kernel as usual
   uint32_t target = 0;
+  const uint32_t *base = nullptr;     // if set, the target is *base + target (the step's starting count, device state)
 };
 __device__ __forceinline__ void signal_ready(uint32_t *counter) {
   __threadfence();
   atomicAdd(counter, 1u);
 }
 __device__ __forceinline__ bool wait_ready(ReadyWait r, uint64_t limit_ns = 2000000000ull) {
+  if (r.base) {
+    uint32_t b;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(b) : "l"(r.base) : "memory");
+    r.target += b;
+  }
   uint64_t start = 0;
   for (uint32_t i = 0;; ++i) {
     uint32_t v;

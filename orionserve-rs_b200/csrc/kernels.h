@@ -230,14 +230,19 @@ struct TpPeers {
 };
 // All-reduce of the partial sums over ranks and split-K slabs + residual add + RMSNorm for
 // `rows` batch rows; every rank ends up with the full residual stream in `hidden` and all
-// normalised rows in `out`. `epoch` cycles 1, 2, ..., 0xFFFFFFFE, 1, ...: one step per call.
+// normalised rows in `out`. The epoch of the call is *epoch_base + epoch_add (epoch_base may be null: epoch_add
+// alone); epochs cycle through 1 .. 0xFFFFFFFE, one step per call, and consecutive calls alternate in parity.
+// With the base in device memory (advanced by launch_tp_state_bump at the end of a step) a step's launches take
+// the same arguments every time, so the step can be replayed as a CUDA graph.
 // `two_shot`: reduce-scatter to the owner of each row + all-gather of the normalised rows (only
 // the owner of a row then holds its current residual); else every rank reduces every row.
 template <typename T>
-int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, const float *partial, uint32_t splits,
+int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, const uint32_t *epoch_base, uint32_t epoch_add, const float *partial, uint32_t splits,
                                          size_t split_stride, float *hidden, const float *norm_w, float eps, T *out,
                                          uint32_t rows, uint32_t hidden_size, bool two_shot, cudaStream_t stream,
                                          uint32_t *ready = nullptr);  // ready: every CTA (one per row) adds 1 when done
+// state[0] += epochs (wrapped as described above), state[1] += rows_counted, after the preceding kernel has completed.
+int launch_tp_state_bump(uint32_t *state, uint32_t epochs, uint32_t rows_counted, cudaStream_t stream);
 int tp_poll_error(uint32_t *code);
 // Vocabulary-parallel LM head: `launch_tp_signal` (ranks other than the leader) stores `epoch` into the
 // rank's flag in the leader's memory once the preceding kernel of the stream has completed;

@@ -163,7 +163,9 @@ class Model final : public ModelBase {
   int run_step_graphed(bool want_argmax);
   int run_step(bool want_argmax) {
     const int rc = graph_eligible() ? run_step_graphed(want_argmax) : run_step_body(want_argmax);
-    if (rc != ORION_OK) ready_resync_ = true;  // a counting kernel may have run without its consumer, or the other way round
+    // a fused hand-over sequence that stopped half way leaves the device-resident epoch behind the inboxes: the ranks
+    // cannot be brought back in step from here
+    if (rc != ORION_OK && nccl_ && tp_fused_) tp_broken_ = true;
     return rc;
   }
   // Pure decode steps on one GPU replay a CUDA graph of the embedding and the layers once the same batch layout has
@@ -189,8 +191,9 @@ class Model final : public ModelBase {
   GraphKey last_key_{};
   uint32_t key_streak_ = 0;
   bool graph_eligible() const {
-    return g_step_graph && DTypeOf<T>::is_bf16 && meta_.decode && !meta_.zero_count && !nccl_ && !prof_on_ && only_mask_ == 0 &&
-           decode_attention_supported(kv_, lq_);
+    // under tensor parallelism only steps that hand over through peer memory (no NCCL call inside the step)
+    return g_step_graph && DTypeOf<T>::is_bf16 && meta_.decode && !meta_.zero_count && !prof_on_ && only_mask_ == 0 &&
+           (!nccl_ || (tp_fused_ && meta_.rows <= kTpFusedMaxRows)) && decode_attention_supported(kv_, lq_);
   }
   void step_decode_plan(uint32_t *splits, uint32_t *blocks_per_split) const {
     const DecodePlan dp = decode_plan(meta_.rows, lkv_, meta_.total_blocks, meta_.max_position, d_.block_size, 32);
@@ -228,8 +231,12 @@ class Model final : public ModelBase {
   int handover(uint32_t splits, const float *norm_w, T *out, const uint32_t *row_map, uint32_t out_rows, bool count_ready = false);
   // The running total of finished hand-over CTAs the next projection has to see (ReadyWait in common.cuh).
   uint32_t *ready_ = nullptr;
-  uint32_t ready_total_ = 0;
-  bool ready_resync_ = false;  // a step failed between a counting kernel and its consumer: reread the counter
+  // Device state of the fused hand-overs: [0] the epoch of the step's first hand-over, [1] the count of finished
+  // hand-over rows at the start of the step; advanced on the device at the end of every step (launch_tp_state_bump), so
+  // that a step's launches take the same arguments every time. The host only counts within a step.
+  uint32_t *tp_state_ = nullptr;
+  uint32_t step_epochs_ = 0, step_rows_counted_ = 0;
+  bool tp_broken_ = false;
   // Vocabulary-parallel LM head under tensor parallelism: this rank holds rows [head_v0_, head_v0_ + head_vn_)
   // of the head, computes that column block of the logits and stores it straight into the leader's
   // logits buffer (peer-mapped); flags in the leader's memory tell it when every block has landed.
@@ -241,7 +248,6 @@ class Model final : public ModelBase {
   int setup_head_peers();
   TpPeers peers_{};
   uint32_t *tp_inbox_ = nullptr;  // where the peers push their partial sums (peer-mapped)
-  uint32_t tp_epoch_ = 1;
   bool tp_fused_ = false;
   bool tp_two_shot_ = false;
   std::vector<void *> ipc_opened_;
@@ -490,6 +496,9 @@ int Model<T>::setup_peer_handover() {
     }
     peers_.inbox[r] = static_cast<uint32_t *>(p);
   }
+  ORION_TRY(alloc(&tp_state_, 2));
+  const uint32_t first[2] = {1u, 0u};  // epoch 0 is never sent; the ready counter starts at zero
+  ORION_CUDA_CHECK("hand-over state", cudaMemcpy(tp_state_, first, sizeof first, cudaMemcpyHostToDevice));
   ORION_TRY(nccl_->barrier(stream_));  // nobody starts a step before every mapping exists
   tp_fused_ = true;
   return ORION_OK;
@@ -760,15 +769,15 @@ int Model<T>::handover(uint32_t splits, const float *norm_w, T *out, const uint3
   const size_t slab = (size_t)Tn * H;
   if (nccl_ && tp_fused_ && Tn <= kTpFusedMaxRows) {
     // every rank ends up with the whole residual stream and all Tn normalised rows
-    ORION_TRY(launch_tp_allreduce_residual_rmsnorm<T>(peers_, tp_epoch_, partial_, splits, slab, hidden_, norm_w,
+    ORION_TRY(launch_tp_allreduce_residual_rmsnorm<T>(peers_, tp_state_, step_epochs_, partial_, splits, slab, hidden_, norm_w,
                                                       d_.rms_norm_eps, normed_, Tn, H,
                                                       // at 2 ranks the one-shot kernel wins while the payload is small; from
                                                       // 1 Mi elements on (128 rows x 8192) the two-shot kernel with its bf16
                                                       // units moves a quarter of the bytes and measured 6 % faster per step
                                                       tp_two_shot_ || (sizeof(T) == 2 && (size_t)Tn * H >= ((size_t)1 << 20)),
                                                       stream_, count_ready && !row_map ? ready_ : nullptr));
-    if (count_ready && !row_map) ready_total_ += Tn;
-    tp_epoch_ = tp_epoch_ == 0xFFFFFFFEu ? 1u : tp_epoch_ + 1;
+    if (count_ready && !row_map) step_rows_counted_ += Tn;
+    ++step_epochs_;
     if (row_map) return launch_gather_rows<T>(normed_, row_map, out, out_rows, H, stream_);
     if (out != normed_) return set_error(ORION_ERR_INTERNAL, "fused hand-over writes the activation buffer only");
     return ORION_OK;
@@ -776,7 +785,7 @@ int Model<T>::handover(uint32_t splits, const float *norm_w, T *out, const uint3
   ORION_TRY(tp_reduce(&splits, slab));
   ORION_TRY(launch_residual_rmsnorm<T>(partial_, splits, slab, hidden_, norm_w, d_.rms_norm_eps, out, row_map, out_rows, H,
                                        stream_, count_ready ? ready_ : nullptr));
-  if (count_ready) ready_total_ += out_rows;
+  if (count_ready) step_rows_counted_ += out_rows;
   return ORION_OK;
 }
 
@@ -854,14 +863,12 @@ int Model<T>::run_step_body(bool want_argmax, int part) {
   // (3.33 -> 3.25 ms per step at 2 ranks). On one GPU the two are equally fast, so the counter is left out. Never
   // in a timing replay that leaves kernel families out, where the counting kernel may be missing.
   const bool count_ready = g_ready_counters && kBf16 && nccl_ && tp_fused_ && Tn <= kTpFusedMaxRows && only_mask_ == 0;
-  if (ready_resync_) {
-    ORION_CUDA_CHECK("ready counter", cudaStreamSynchronize(stream_));
-    ORION_CUDA_CHECK("ready counter", cudaMemcpy(&ready_total_, ready_, sizeof(uint32_t), cudaMemcpyDeviceToHost));
-    ready_resync_ = false;
-  }
+  if (tp_broken_)
+    return set_error(ORION_ERR_BACKEND, "backend cuda failed at forward: an earlier tensor-parallel step ended half way; the model cannot continue");
+  if (part != 2) step_epochs_ = step_rows_counted_ = 0;
   auto ready_for = [&](const GemmPlan &gp) {
     ReadyWait r;
-    if (count_ready && gp.tensor_core) r.counter = ready_, r.target = ready_total_;
+    if (count_ready && gp.tensor_core) r.counter = ready_, r.target = step_rows_counted_, r.base = tp_state_ + 1;
     return r;
   };
   auto hint = [&](const T *w, size_t elems) {
@@ -957,6 +964,8 @@ int Model<T>::run_step_body(bool want_argmax, int part) {
       ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, final_norm_, normed_, nullptr, Tn); }));
     }
   }
+  if (part != 2 && step_epochs_ > 0)  // the device state moves on to the next step
+    ORION_TRY(timed(kProfCollective, [&] { return launch_tp_state_bump(tp_state_, step_epochs_, step_rows_counted_, stream_); }));
   if (part == 1 || meta_.zero_count) return ORION_OK;
   if (head_parallel_) {
     // This rank's column block of the logits goes straight into the leader's buffer (plain peer stores from

@@ -51,6 +51,11 @@ __device__ __forceinline__ void trace(int k) {
 __device__ __forceinline__ void trace(int) {}
 #endif
 
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_unit2(uint32_t *dst, float a, float b, uint32_t epoch) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(__float_as_uint(a)), "r"(epoch),
                "r"(__float_as_uint(b)), "r"(epoch)
@@ -138,7 +143,7 @@ __device__ __forceinline__ void st_row4<bf16>(bf16 *dst, float4 v) {
 // bit-identical across ranks.
 template <typename T, typename Acc, bool Packed>
 __global__ void __launch_bounds__(1024)
-tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ partial,
+tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, const uint32_t *epoch_base, uint32_t epoch_add, const float *__restrict__ partial,
                                      uint32_t splits, size_t split_stride, float *__restrict__ hidden,
                                      const float *__restrict__ w, float eps, T *__restrict__ out, uint32_t H,
                                      uint32_t *__restrict__ ready) {
@@ -147,6 +152,8 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
   trace(0);
   pdl_wait();  // this rank's projection has finished
   trace(1);
+  // the epoch of this hand-over: the step's first epoch (device state, advanced once per step) + its place in the step
+  const uint32_t epoch = (epoch_base ? ld_volatile_u32(epoch_base) : 0u) + epoch_add;
   const uint32_t nvec = H / 4, row = blockIdx.x;
   const size_t slot = (size_t)peers.slot_floats * 2;  // u32 words per (parity, sender) slot
   const size_t parity_base = (size_t)(epoch & 1u) * peers.world * slot;
@@ -233,7 +240,7 @@ tp_allreduce_residual_rmsnorm_kernel(TpPeers peers, uint32_t epoch, const float 
 // reduce-scatter, then [parity 2][slot] units for the all-gather, both addressed by (row, element).
 template <typename T, typename Acc, bool Packed>
 __global__ void __launch_bounds__(1024)
-tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ partial, uint32_t splits,
+tp_twoshot_kernel(TpPeers peers, const uint32_t *epoch_base, uint32_t epoch_add, const float *__restrict__ partial, uint32_t splits,
                   size_t split_stride, float *__restrict__ hidden, const float *__restrict__ w, float eps,
                   T *__restrict__ out, uint32_t rows, uint32_t H, uint32_t *__restrict__ ready) {
   __shared__ Acc red[32];
@@ -241,6 +248,8 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
   trace(0);
   pdl_wait();  // this rank's projection has finished
   trace(1);
+  // the epoch of this hand-over: the step's first epoch (device state, advanced once per step) + its place in the step
+  const uint32_t epoch = (epoch_base ? ld_volatile_u32(epoch_base) : 0u) + epoch_add;
   (void)rows;
   const uint32_t nvec = H / 4, row = blockIdx.x;
   const uint32_t per = (nvec + peers.world - 1) / peers.world;  // groups per owner
@@ -330,12 +339,12 @@ tp_twoshot_kernel(TpPeers peers, uint32_t epoch, const float *__restrict__ parti
 }  // namespace
 
 template <typename T>
-int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, const float *partial, uint32_t splits,
+int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, const uint32_t *epoch_base, uint32_t epoch_add, const float *partial, uint32_t splits,
                                          size_t split_stride, float *hidden, const float *norm_w, float eps, T *out,
                                          uint32_t rows, uint32_t hidden_size, bool two_shot, cudaStream_t stream,
                                          uint32_t *ready) {
   if (hidden_size % 4 != 0 || hidden_size / 4 > 4096 || split_stride % 4 != 0 ||
-      (size_t)rows * hidden_size > peers.slot_floats || epoch == 0 || epoch == 0xFFFFFFFFu)
+      (size_t)rows * hidden_size > peers.slot_floats || (epoch_base == nullptr && (epoch_add == 0 || epoch_add == 0xFFFFFFFFu)))
     return set_error(ORION_ERR_INTERNAL, "fused tensor-parallel hand-over: unsupported shape or epoch");
   if (rows == 0) return ORION_OK;
   const uint32_t nvec = hidden_size / 4;
@@ -351,34 +360,48 @@ int launch_tp_allreduce_residual_rmsnorm(const TpPeers &peers, uint32_t epoch, c
   }();
   if (two_shot && sizeof(T) == 2 && packed)
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
-                     launch_pdl(tp_twoshot_kernel<T, Acc, true>, dim3(rows), dim3(threads), 0, stream, peers, epoch,
+                     launch_pdl(tp_twoshot_kernel<T, Acc, true>, dim3(rows), dim3(threads), 0, stream, peers, epoch_base, epoch_add,
                                 partial, splits, split_stride, hidden, norm_w, eps, out, rows, hidden_size, ready));
   else if (two_shot)
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
-                     launch_pdl(tp_twoshot_kernel<T, Acc, false>, dim3(rows), dim3(threads), 0, stream, peers, epoch,
+                     launch_pdl(tp_twoshot_kernel<T, Acc, false>, dim3(rows), dim3(threads), 0, stream, peers, epoch_base, epoch_add,
                                 partial, splits, split_stride, hidden, norm_w, eps, out, rows, hidden_size, ready));
   else if (sizeof(T) == 2 && packed)
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
                      launch_pdl(tp_allreduce_residual_rmsnorm_kernel<T, Acc, true>, dim3(rows), dim3(threads), 0, stream, peers,
-                                epoch, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size, ready));
+                                epoch_base, epoch_add, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size, ready));
   else
     ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm",
                      launch_pdl(tp_allreduce_residual_rmsnorm_kernel<T, Acc, false>, dim3(rows), dim3(threads), 0, stream, peers,
-                                epoch, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size, ready));
+                                epoch_base, epoch_add, partial, splits, split_stride, hidden, norm_w, eps, out, hidden_size, ready));
   count_launch();
   ORION_CUDA_CHECK("tp_allreduce_residual_rmsnorm", cudaGetLastError());
   return ORION_OK;
 }
-template int launch_tp_allreduce_residual_rmsnorm<float>(const TpPeers &, uint32_t, const float *, uint32_t, size_t,
+template int launch_tp_allreduce_residual_rmsnorm<float>(const TpPeers &, const uint32_t *, uint32_t, const float *, uint32_t, size_t,
                                                          float *, const float *, float, float *, uint32_t, uint32_t,
                                                          bool, cudaStream_t, uint32_t *);
-template int launch_tp_allreduce_residual_rmsnorm<bf16>(const TpPeers &, uint32_t, const float *, uint32_t, size_t,
+template int launch_tp_allreduce_residual_rmsnorm<bf16>(const TpPeers &, const uint32_t *, uint32_t, const float *, uint32_t, size_t,
                                                         float *, const float *, float, bf16 *, uint32_t, uint32_t,
                                                         bool, cudaStream_t, uint32_t *);
 
 namespace {
 // Vocabulary-parallel LM head: a rank that has stored its column block of the logits into the
 // leader's memory raises its flag there; the leader waits for every flag before it touches the logits.
+// Advances the device-resident hand-over state at the end of a step: state[0] = the epoch of the next step's first
+// hand-over, state[1] = the count of finished hand-over rows the next step starts from. Epochs stay inside
+// 1 .. 0xFFFFFFFE and keep alternating in parity (the parity selects the inbox half).
+__global__ void tp_state_bump_kernel(uint32_t *state, uint32_t epochs, uint32_t rows_counted) {
+  pdl_trigger();
+  pdl_wait();  // every hand-over of the step has read the state
+  if (threadIdx.x == 0) {
+    uint32_t e = state[0] + epochs;
+    if (e > 0xFFFFFF00u) e = (e & 1u) ? 1u : 2u;
+    state[0] = e;
+    state[1] += rows_counted;
+  }
+}
+
 __global__ void tp_signal_kernel(uint32_t *flag, uint32_t epoch) {
   pdl_trigger();
   pdl_wait();                // the projection that wrote the block has completed
@@ -407,6 +430,13 @@ __global__ void tp_wait_flags_kernel(const uint32_t *flags, uint32_t epoch, int 
   __threadfence_system();
 }
 }  // namespace
+
+int launch_tp_state_bump(uint32_t *state, uint32_t epochs, uint32_t rows_counted, cudaStream_t stream) {
+  ORION_CUDA_CHECK("tp_state_bump", launch_pdl(tp_state_bump_kernel, dim3(1), dim3(32), 0, stream, state, epochs, rows_counted));
+  count_launch();
+  ORION_CUDA_CHECK("tp_state_bump", cudaGetLastError());
+  return ORION_OK;
+}
 
 int launch_tp_signal(uint32_t *flag, uint32_t epoch, cudaStream_t stream) {
   ORION_CUDA_CHECK("tp_signal", launch_pdl(tp_signal_kernel, dim3(1), dim3(32), 0, stream, flag, epoch));
