@@ -174,7 +174,7 @@ class Model final : public ModelBase {
   // holds for as long as the layout (rows, sequences, offsets inside the metadata array, context splits) does.
   struct GraphKey {
     uint32_t rows, seqs, splits, blocks_per_split, generation;
-    size_t offsets[8];
+    size_t offsets[8];  // [7] is the address of the metadata array, the others are offsets inside it
     bool operator<(const GraphKey &o) const {
       return std::tie(rows, seqs, splits, blocks_per_split, generation, offsets[0], offsets[1], offsets[2], offsets[3], offsets[4],
                       offsets[5], offsets[6], offsets[7]) <
@@ -206,8 +206,9 @@ class Model final : public ModelBase {
     GraphKey key{};
     key.rows = meta_.rows, key.seqs = meta_.seqs, key.generation = g_tuning_generation;
     step_decode_plan(&key.splits, &key.blocks_per_split);
+    // meta_.tables follows meta_.offsets at a distance that only depends on the sequence count, so it needs no slot
     const size_t offs[8] = {meta_.tokens, meta_.positions, meta_.slot_block, meta_.slot_slot, meta_.seq_of_row, meta_.last_rows,
-                            meta_.offsets, meta_.tables};
+                            meta_.offsets, reinterpret_cast<size_t>(d_meta_)};
     for (int i = 0; i < 8; ++i) key.offsets[i] = offs[i];
     return key;
   }
@@ -1078,6 +1079,7 @@ int Model<T>::forward(const BatchView &b, float *logits_out, uint64_t logits_cap
     meta_cap_ = 0;
     ORION_CUDA_CHECK("allocate batch mirror", cudaMallocHost(reinterpret_cast<void **>(&h_meta_), cap * sizeof(uint32_t)));
     ORION_TRY(alloc(&d_meta_, cap));  // the previous device array stays owned until destruction
+    drop_graphs();                    // captured steps point into the previous array
     meta_cap_ = cap;
   }
   uint32_t *h = h_meta_;

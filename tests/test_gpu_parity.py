@@ -711,6 +711,48 @@ def test_cluster_split_k_variant_matches_the_oracle(pkg, backend):
     assert r.returncode == 0, r.stdout[-3000:]
 
 
+def test_graphed_decode_steps_follow_a_move_of_the_batch_arrays(pkg, backend, oracle):
+    """A decode batch of constant layout is replayed as a CUDA graph whose kernels read tokens, positions and
+    block tables from the model's batch array on the device. A batch with a much longer block table makes that
+    array grow and move; the steps after the move must still be the oracle's. (In the child process of
+    test_decode_steps_replayed_as_a_graph_match_the_oracle the layout is captured after two repeats, so the
+    steps before and after the move all go through graphs; with the default of 32 repeats this is a plain
+    decode comparison.)"""
+    meta_d = dict(hidden_size=256, num_layers=2, num_attention_heads=8, num_kv_heads=2, head_dim=128, vocab_size=512,
+                  ffn_dim=512, max_position_embeddings=512, rope_theta=10000.0, rms_norm_eps=1e-5, has_qkv_bias=False,
+                  tied_lm_head=False, num_blocks=64, block_size=16)
+    t = random_tensors(np.random.default_rng(23), meta_d, std=0.05)
+    t = {k: oracle.round_to_bf16(v) if v.ndim == 2 else v for k, v in t.items()}
+    ref = oracle.Model(**meta_d).load(t)
+    meta = pkg.ModelMetadata(architecture="llama", name="g",
+                             **{k: v for k, v in meta_d.items() if k not in ("num_blocks", "block_size")})
+    dev = pkg.CudaTransformerModel.new(meta, t, 64, 16, backend, compute_dtype=pkg.DType.BF16, max_batch_tokens=64,
+                                       max_batch_sequences=8)
+    rng = np.random.default_rng(5)
+    n = 4
+    tables = [[4 * s + i for i in range(4)] for s in range(n)]  # blocks 0..15
+    ids = list(range(1, n + 1))
+    last = rng.integers(0, 512, n).tolist()
+    oracle.set_threads(4)
+    for step in range(10):
+        pos, ctx = [step] * n, [step + 1] * n
+        exp = ref.forward(oracle.Batch(last, pos, [1] * n, ctx, tables))
+        got = dev.forward(pkg.ForwardBatch(last, pos, ids, [1] * n, ctx, tables, has_prefill=False)).logits
+        assert float(np.max(np.abs(softmax_rows(got) - softmax_rows(exp)))) < BF16_SOFTMAX, f"decode step {step}"
+        assert rel_err(got, exp) < 3e-2, f"decode step {step}"
+        last = [int(oracle.argmax(r)) for r in exp]
+        if step == 5:
+            # one other sequence with a block table of 6000 entries (only its first block, 40, is touched): the batch
+            # array has to grow; the oracle sees the same step, so that both arenas stay comparable
+            long_table = [[40] + [41 + (i % 20) for i in range(5999)]]
+            dev.forward(pkg.ForwardBatch([7], [0], [99], [1], [1], long_table, has_prefill=False))
+            ref.forward(oracle.Batch([7], [0], [1], [1], long_table))
+    oracle.set_threads(1)
+    kv_dev, kv_ref = dev.read_kv(), ref.kv().array()
+    assert np.array_equal(kv_dev != 0, kv_ref != 0), "exactly the same slots were written"
+    assert np.allclose(kv_dev, kv_ref, atol=3e-2, rtol=3e-2)
+
+
 def test_decode_steps_replayed_as_a_graph_match_the_oracle(pkg, backend):
     """A decode batch whose layout repeats is replayed as a CUDA graph of the embedding and the layers (after 32
     repeats by default; the count is read when the library loads). The greedy-decode comparison with the oracle, the
@@ -724,6 +766,6 @@ def test_decode_steps_replayed_as_a_graph_match_the_oracle(pkg, backend):
     env = dict(os.environ, ORION_STEP_GRAPH_AFTER="2")
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_parity.py"),
                         os.path.join(ROOT, "tests", "test_gpu_engine.py"), "-q", "-x", "-m", "gpu",
-                        "-k", "config1_greedy or timing_replays or engine or qwen2_7b_head_layout"],
+                        "-k", "config1_greedy or timing_replays or engine or qwen2_7b_head_layout or move_of_the_batch_arrays"],
                        cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:]
