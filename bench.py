@@ -526,8 +526,6 @@ def run_ours(args):
         pkg._ffi.lib().orion_cuda_set_programmatic_launch(0)
     if args.attn_stages or args.attn_ctas:
         pkg._ffi.lib().orion_cuda_attention_set_tuning(args.attn_stages, args.attn_ctas)
-    if args.l2_prefetch_mb >= 0:
-        pkg._ffi.lib().orion_cuda_set_l2_prefetch_bytes(args.l2_prefetch_mb << 20)
     if args.gemm_ctas or args.gemm_stages:
         pkg._ffi.lib().orion_cuda_gemm_set_tuning(args.gemm_ctas, args.gemm_stages)
     rng = np.random.default_rng(3)
@@ -737,7 +735,6 @@ def main():
                          "precedes the timed region (tuning runs)")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (tuning A/B)")
     ap.add_argument("--gemm-ctas", type=int, default=0, help="split-K CTA target (tuning A/B)")
-    ap.add_argument("--l2-prefetch-mb", type=int, default=-1, help="L2 weight prefetch per hand-over (tuning A/B)")
     ap.add_argument("--gemm-stages", type=int, default=0, help="decode GEMM ring depth 3..4 (tuning A/B)")
     ap.add_argument("--attn-stages", type=int, default=0, help="decode attention ring depth 2..4 (tuning A/B)")
     ap.add_argument("--attn-ctas", type=int, default=0, help="decode attention CTA target (tuning A/B)")

@@ -233,10 +233,6 @@ int orion_cuda_model_desc(const OrionModel *model, OrionModelDesc *out);
  * here is written by DMA directly, a pageable one goes through a bounce copy. */
 void *orion_cuda_host_alloc(uint64_t bytes);
 void orion_cuda_host_free(void *ptr);
-/* Tuning knob: bytes of the NEXT projection's weights that each heavy kernel of a
- * decode step asks L2 to prefetch once its own loads are issued (default 0 = off,
- * measured neutral at batch 64). */
-int orion_cuda_set_l2_prefetch_bytes(uint64_t bytes);
 /* Tuning knob: launch the kernels of a step with programmatic dependent launch
  * (each kernel's prologue and weight prefetch overlap its predecessor's tail).
  * On by default; 0 gives plain stream-ordered launches. */

@@ -81,7 +81,6 @@ SIGNATURES = {
     "orion_cuda_host_free": (None, [_vp]),
     "orion_cuda_gemm_set_tuning": (_int, [_u32, _int]),
     "orion_cuda_set_programmatic_launch": (_int, [_int]),
-    "orion_cuda_set_l2_prefetch_bytes": (_int, [_u64]),
     "orion_cuda_attention_set_tuning": (_int, [_int, _u32]),
     "orion_cuda_tp_layout": (_int, [_u32, _u32, _u32, _u32, _u32, _u64p, _u64p, _u64p]),
     "orion_cuda_tp_unique_id": (_int, [_u8p]),

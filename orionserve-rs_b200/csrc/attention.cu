@@ -193,7 +193,7 @@ template <int kStages>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, KvLayout kv,
                     uint32_t layer, AttnBatch batch, uint32_t q_heads, uint32_t splits,
-                    DecodeScratch scratch, bf16 *__restrict__ out, PrefetchHint next, FusedQkv fq) {
+                    DecodeScratch scratch, bf16 *__restrict__ out, FusedQkv fq) {
   extern __shared__ __align__(1024) uint8_t dsmem[];
   uint8_t *ring = dsmem;  // [kWarps][kStages][kChunkBytes]
   uint64_t *bars = reinterpret_cast<uint64_t *>(dsmem + kWarps * kStages * kChunkBytes);
@@ -412,7 +412,6 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
     }
   }
   if (!ok && lane == 0) atomicOr(&g_decode_error, 1u);
-  if (threadIdx.x == 0) prefetch_slice(next);  // the K/V stream is issued: pull the O-projection weights into L2
 
   // Reduce the per-lane partial sums over the 8 lanes that share a head pair.
 #pragma unroll
@@ -659,14 +658,14 @@ namespace {
 template <int STAGES>
 int launch_decode_stages(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer, AttnBatch batch,
                          uint32_t q_heads, uint32_t splits, DecodeScratch scratch, bf16 *out,
-                         PrefetchHint next, FusedQkv fq, cudaStream_t stream) {
+                         FusedQkv fq, cudaStream_t stream) {
   static bool attr_set[kMaxDeviceOrdinals] = {};
   ORION_CUDA_CHECK("paged_decode attr",
                    ensure_dynamic_smem(paged_decode_kernel<STAGES>, (int)decode_smem_bytes(STAGES), attr_set));
   ORION_CUDA_CHECK("paged_decode",
                    launch_pdl(paged_decode_kernel<STAGES>, dim3(kv.num_kv_heads, batch.rows, splits),
                               dim3(kWarps * 32), (size_t)decode_smem_bytes(STAGES), stream, q, arena, kv, layer,
-                              batch, q_heads, splits, scratch, out, next, fq));
+                              batch, q_heads, splits, scratch, out, fq));
   return ORION_OK;
 }
 }  // namespace
@@ -678,7 +677,7 @@ void decode_set_tuning(int stages, uint32_t cta_target) {
 
 int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer,
                                   AttnBatch batch, uint32_t q_heads, uint32_t splits,
-                                  DecodeScratch scratch, bf16 *out, cudaStream_t stream, PrefetchHint next,
+                                  DecodeScratch scratch, bf16 *out, cudaStream_t stream,
                                   FusedQkv fq) {
   if (batch.rows == 0) return ORION_OK;
   if (!decode_attention_supported(kv, q_heads))
@@ -688,9 +687,9 @@ int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv,
     return set_error(ORION_ERR_INTERNAL, "decode attention scratch too small for %u splits",
                      splits);
   switch (g_decode_stages) {
-    case 2: ORION_TRY(launch_decode_stages<2>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, next, fq, stream)); break;
-    case 4: ORION_TRY(launch_decode_stages<4>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, next, fq, stream)); break;
-    default: ORION_TRY(launch_decode_stages<3>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, next, fq, stream)); break;
+    case 2: ORION_TRY(launch_decode_stages<2>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, fq, stream)); break;
+    case 4: ORION_TRY(launch_decode_stages<4>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, fq, stream)); break;
+    default: ORION_TRY(launch_decode_stages<3>(q, arena, kv, layer, batch, q_heads, splits, scratch, out, fq, stream)); break;
   }
   ORION_TRY(after_launch("paged_decode"));
   if (splits > 1 && scratch.counters == nullptr) {

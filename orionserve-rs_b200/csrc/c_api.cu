@@ -601,12 +601,6 @@ void *orion_cuda_host_alloc(uint64_t bytes) {
 }
 void orion_cuda_host_free(void *p) { if (p) cudaFreeHost(p); }
 
-int orion_cuda_set_l2_prefetch_bytes(uint64_t bytes) {
-  model_set_prefetch_budget((size_t)bytes);
-  ++g_tuning_generation;
-  return ORION_OK;
-}
-
 int orion_cuda_set_programmatic_launch(int enabled) {
   g_pdl_enabled = enabled != 0;
   ++g_tuning_generation;

@@ -234,30 +234,6 @@ __device__ __forceinline__ void tma_load_2d(void *dst_smem, const void *tensor_m
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// A region the NEXT heavy kernel of the step will stream (its weight matrix). A kernel given
-// a hint asks L2 to fetch it once its own loads are issued, one slice per CTA, so that HBM
-// stays busy through the kernel's tail, the dependency hand-over and the small kernels in
-// between, and the next GEMM starts on L2 hits. `bytes` must be a multiple of 16.
-struct PrefetchHint {
-  const void *ptr = nullptr;
-  size_t bytes = 0;
-};
-__device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-// Called by one thread of every CTA.
-__device__ __forceinline__ void prefetch_slice(PrefetchHint h) {
-  if (h.bytes == 0) return;
-  const size_t nct = (size_t)gridDim.x * gridDim.y * gridDim.z;
-  const size_t cta = blockIdx.x + (size_t)gridDim.x * (blockIdx.y + (size_t)gridDim.y * blockIdx.z);
-  const size_t per = (((h.bytes + nct - 1) / nct) + 127) & ~size_t(127);
-  const size_t off = cta * per;
-  if (off >= h.bytes) return;
-  const size_t len = h.bytes - off < per ? h.bytes - off : per;
-  const char *base = static_cast<const char *>(h.ptr) + off;
-  for (size_t o = 0; o < len; o += 16384) l2_prefetch(base + o, (uint32_t)(len - o < 16384 ? len - o : 16384));
-}
-
 // A dependency between two kernels of a step carried by a counter in device memory instead of by the
 // completion of the earlier kernel. Every CTA of the producer adds 1 when its results are written
 // (signal_ready, after a CTA-wide barrier); the consumer, already resident through its programmatic

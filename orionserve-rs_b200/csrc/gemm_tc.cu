@@ -205,7 +205,7 @@ template <int TOKN, int WST, int XST, int MT, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                float *__restrict__ partial, bf16 *__restrict__ act, uint32_t M, uint32_t N, uint32_t K,
-               uint32_t splits, uint32_t cluster_reduce, uint32_t ldc, PrefetchHint next, ReadyWait ready) {
+               uint32_t splits, uint32_t cluster_reduce, uint32_t ldc, ReadyWait ready) {
   using Cfg = TcConfig<TOKN, WST, XST, MT, PAIR>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
@@ -299,7 +299,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           tma_load_2d(w_ring + s * Cfg::kWBytes + mt * (kTileN * kSlabK * 2), &map_w, (int)((kb_begin + i) * kSlabK),
                       (int)(n0 + mt * kTileN), &full_w[s]);
       }
-      prefetch_slice(next);  // own loads are all issued: start pulling the next GEMM's weights into L2
     }
   } else if (warp == 2) {
     // Activation producer: waits for the preceding kernel, then keeps the short x ring full.
@@ -540,7 +539,7 @@ int cached_map(const void *base, uint64_t rows, uint64_t k, uint64_t ld, uint32_
 template <int TOKN, int WST, int XST, int MT = 1, bool PAIR = false>
 int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial, bf16 *act,
               uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, bool cluster_reduce, uint32_t ldc,
-              PrefetchHint next, cudaStream_t stream, ReadyWait ready = {}) {
+              cudaStream_t stream, ReadyWait ready = {}) {
   if (ldc == 0) ldc = n;
   if (ldc != n && (splits != 1 || act != nullptr))
     return set_error(ORION_ERR_INTERNAL, "a strided GEMM output needs one k split and f32 results");
@@ -558,14 +557,14 @@ int launch_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *p
       return set_error(ORION_ERR_INTERNAL, "the paired GEMM needs an even number of weight tile groups and no cluster split-K");
     ORION_CUDA_CHECK("gemm_tc", launch_pdl_cluster(gemm_tc_kernel<TOKN, WST, XST, MT, PAIR>, grid, dim3(kThreads), dim3(2, 1, 1),
                                                    Cfg::kSmemBytes, stream, *mw, *mx, partial, act, rows, n, k, splits,
-                                                   0u, ldc, next, ready));
+                                                   0u, ldc, ready));
   } else if (cluster_reduce)
     ORION_CUDA_CHECK("gemm_tc", launch_pdl_cluster(gemm_tc_kernel<TOKN, WST, XST, MT, PAIR>, grid, dim3(kThreads), dim3(1, 1, splits),
                                                    Cfg::kSmemBytes, stream, *mw, *mx, partial, act, rows, n, k, splits,
-                                                   1u, ldc, next, ready));
+                                                   1u, ldc, ready));
   else
     ORION_CUDA_CHECK("gemm_tc", launch_pdl(gemm_tc_kernel<TOKN, WST, XST, MT, PAIR>, grid, dim3(kThreads), Cfg::kSmemBytes, stream,
-                                           *mw, *mx, partial, act, rows, n, k, splits, 0u, ldc, next, ready));
+                                           *mw, *mx, partial, act, rows, n, k, splits, 0u, ldc, ready));
   count_launch();
   ORION_CUDA_CHECK("gemm_tc", cudaGetLastError());
   return ORION_OK;
@@ -624,7 +623,7 @@ bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint
 
 int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
                    uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream,
-                   PrefetchHint next, bf16 *act, bool cluster_reduce, uint32_t ldc, ReadyWait ready) {
+                   bf16 *act, bool cluster_reduce, uint32_t ldc, ReadyWait ready) {
   const uint32_t nkb = (k + kSlabK - 1) / kSlabK;
   if (cluster_reduce && (splits < 2 || splits > 8 || act != nullptr))
     return set_error(ORION_ERR_INTERNAL, "cluster split-K needs 2..8 splits and f32 output");
@@ -638,28 +637,28 @@ int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, flo
   if (rows > 256 && g_prefill_fill == 1 && ((n + kTileN - 1) / kTileN) * ((rows + 255) / 256) < 148) tt = 128;
   switch (tt) {
     case 16:
-      return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
-                  : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
+      return deep ? launch_tc<16, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready)
+                  : launch_tc<16, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready);
     case 32:
-      return deep ? launch_tc<32, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
-                  : launch_tc<32, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
+      return deep ? launch_tc<32, 6, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready)
+                  : launch_tc<32, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready);
     case 64:
-      return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
-                  : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
+      return deep ? launch_tc<64, 5, 3>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready)
+                  : launch_tc<64, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready);
     case 128:
       return g_mid_tile == 0
-                 ? launch_tc<128, 4, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
-                 : launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
+                 ? launch_tc<128, 4, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready)
+                 : launch_tc<128, 6, 6>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready);
     default: {
       const uint32_t mt = (!cluster_reduce && prefill_weight_tiles(rows, n) == 2) ? 2 : 1;
       // CTA pairs: each CTA loads half of the activation tile, so the rings go a stage deeper
       const bool pair = (g_gemm_pair >= 2 || (g_gemm_pair == 1 && rows >= kPairMinRows)) && !cluster_reduce &&
                         (((n + mt * kTileN - 1) / (mt * kTileN)) & 1u) == 0;
       if (mt == 2)
-        return pair ? launch_tc<256, 4, 4, 2, true>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
-                    : launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
-      return pair ? launch_tc<256, 6, 6, 1, true>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready)
-                  : launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, next, stream, ready);
+        return pair ? launch_tc<256, 4, 4, 2, true>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready)
+                    : launch_tc<256, 3, 3, 2>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready);
+      return pair ? launch_tc<256, 6, 6, 1, true>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready)
+                  : launch_tc<256, 4, 4>(x, ldx, w, ldw, partial, act, rows, n, k, splits, cluster_reduce, ldc, stream, ready);
     }
   }
 }
@@ -766,26 +765,26 @@ size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t
 }
 
 int launch_gemm_swiglu(const bf16 *x, uint32_t ldx, const bf16 *w_interleaved, uint32_t ldw, bf16 *act, uint32_t rows,
-                       uint32_t ffn, uint32_t k, cudaStream_t stream, PrefetchHint next, ReadyWait ready) {
+                       uint32_t ffn, uint32_t k, cudaStream_t stream, ReadyWait ready) {
   if (!gemm_tc_supported(rows, 2 * ffn, k, ldx, ldw, x, w_interleaved))
     return set_error(ORION_ERR_INTERNAL, "tensor-core GEMM planned for an unaligned operand");
-  return launch_gemm_tc(x, ldx, w_interleaved, ldw, nullptr, rows, 2 * ffn, k, 1, stream, next, act, false, 0, ready);
+  return launch_gemm_tc(x, ldx, w_interleaved, ldw, nullptr, rows, 2 * ffn, k, 1, stream, act, false, 0, ready);
 }
 
 template <>
 int launch_gemm<float>(const float *x, uint32_t ldx, const float *w, uint32_t ldw, float *partial,
-                       uint32_t rows, uint32_t n, uint32_t k, GemmPlan, cudaStream_t stream, PrefetchHint, ReadyWait) {
+                       uint32_t rows, uint32_t n, uint32_t k, GemmPlan, cudaStream_t stream, ReadyWait) {
   return launch_gemm_simt<float>(x, ldx, w, ldw, partial, rows, n, k, stream);
 }
 
 template <>
 int launch_gemm<bf16>(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
                       uint32_t rows, uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream,
-                      PrefetchHint next, ReadyWait ready) {
+                      ReadyWait ready) {
   if (plan.tensor_core) {
     if (!gemm_tc_supported(rows, n, k, ldx, ldw, x, w))
       return set_error(ORION_ERR_INTERNAL, "tensor-core GEMM planned for an unaligned operand");
-    return launch_gemm_tc(x, ldx, w, ldw, partial, rows, n, k, plan.splits, stream, next, nullptr, plan.cluster_reduce,
+    return launch_gemm_tc(x, ldx, w, ldw, partial, rows, n, k, plan.splits, stream, nullptr, plan.cluster_reduce,
                           plan.ldc, ready);
   }
   if (plan.ldc != 0 && plan.ldc != n) return set_error(ORION_ERR_INTERNAL, "a strided GEMM output needs the tensor-core path");

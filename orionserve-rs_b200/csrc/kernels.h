@@ -206,7 +206,7 @@ struct FusedQkv {
 int launch_paged_attention_decode(const bf16 *q, const bf16 *arena, KvLayout kv, uint32_t layer,
                                   AttnBatch batch, uint32_t q_heads, uint32_t splits,
                                   DecodeScratch scratch, bf16 *out, cudaStream_t stream,
-                                  PrefetchHint next = {}, FusedQkv fused = {});
+                                  FusedQkv fused = {});
 // Tuning: ring depth per warp (2..4) and the CTA count the context split aims for (0 keeps it).
 void decode_set_tuning(int stages, uint32_t cta_target);
 // Device error word of the decode kernel (0 = none); reading clears it.
@@ -273,8 +273,7 @@ struct GemmPlan {
 GemmPlan gemm_plan(bool is_bf16, uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint32_t ldw);
 template <typename T>
 int launch_gemm(const T *x, uint32_t ldx, const T *w, uint32_t ldw, float *partial, uint32_t rows,
-                uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream, PrefetchHint next = {},
-                ReadyWait ready = {});  // `ready`: honoured by the tensor-core path only (GemmPlan::tensor_core)
+                uint32_t n, uint32_t k, GemmPlan plan, cudaStream_t stream, ReadyWait ready = {});  // `ready`: honoured by the tensor-core path only (GemmPlan::tensor_core)
 size_t gemm_partial_floats(bool is_bf16, uint32_t max_rows, uint32_t n, uint32_t k);
 // Number of CTAs split-K aims for on small batches (default 296, two per SM).
 void gemm_set_target_ctas(uint32_t ctas);
@@ -290,13 +289,13 @@ bool gemm_tc_supported(uint32_t rows, uint32_t n, uint32_t k, uint32_t ldx, uint
                        const void *x, const void *w);
 int launch_gemm_tc(const bf16 *x, uint32_t ldx, const bf16 *w, uint32_t ldw, float *partial,
                    uint32_t rows, uint32_t n, uint32_t k, uint32_t splits, cudaStream_t stream,
-                   PrefetchHint next = {}, bf16 *act = nullptr, bool cluster_reduce = false, uint32_t ldc = 0,
+                   bf16 *act = nullptr, bool cluster_reduce = false, uint32_t ldc = 0,
                    ReadyWait ready = {});
 // Gate/up projection with SwiGLU in the epilogue: `w_interleaved` is [2 * ffn][k] with gate row f
 // at 2f and up row f at 2f + 1; writes act[r][f] = silu(x.gate_f) * (x.up_f) and no partials.
 // One k split only (gemm_plan(...).splits == 1 and .tensor_core).
 int launch_gemm_swiglu(const bf16 *x, uint32_t ldx, const bf16 *w_interleaved, uint32_t ldw, bf16 *act, uint32_t rows,
-                       uint32_t ffn, uint32_t k, cudaStream_t stream, PrefetchHint next = {}, ReadyWait ready = {});
+                       uint32_t ffn, uint32_t k, cudaStream_t stream, ReadyWait ready = {});
 // Device error word set by kernels whose bounded waits ran out (0 = none).
 int gemm_tc_poll_error(uint32_t *code);
 

@@ -45,14 +45,10 @@ int compute_layout(uint32_t heads, uint32_t kv_heads, uint32_t ffn, uint32_t ran
   return ORION_OK;
 }
 
-// Off by default: measured at batch 64 on the Llama-3-8B shape, 16..96 MiB of prefetch per
-// hand-over changed the step time by less than the run-to-run noise (5.11-5.20 vs 5.14 ms).
-size_t g_prefetch_budget = 0;
 // Tuning A/B: ORION_FUSE_QKV=0 keeps the separate RoPE / KV-write kernel before decode attention.
 bool g_fuse_qkv = std::getenv("ORION_FUSE_QKV") ? std::atoi(std::getenv("ORION_FUSE_QKV")) != 0 : true;
 // Tuning A/B: ORION_FUSE_SWIGLU=0 keeps the separate SwiGLU kernel after the gate/up projection.
 bool g_fuse_swiglu = std::getenv("ORION_FUSE_SWIGLU") ? std::atoi(std::getenv("ORION_FUSE_SWIGLU")) != 0 : true;
-void model_set_prefetch_budget(size_t bytes) { g_prefetch_budget = bytes; }
 // Tuning A/B: ORION_STEP_GRAPH=0 launches every decode step kernel by kernel.
 bool g_step_graph = std::getenv("ORION_STEP_GRAPH") ? std::atoi(std::getenv("ORION_STEP_GRAPH")) != 0 : true;
 // Capture and instantiation take about 12 ms and save 0.09 ms per step: only a layout that stays is worth it.
@@ -855,9 +851,6 @@ int Model<T>::run_step_body(bool want_argmax, int part) {
   const DecodePlan dplan = tuned_decode ? decode_plan(Tn, lkv_, meta_.total_blocks, meta_.max_position, d.block_size, 32)
                                         : DecodePlan{1, 0};
   const uint32_t dsplits = fit_context_splits(Tn, dplan.splits);
-  // L2 prefetch of the next projection's weights: only where the projections are bandwidth-bound
-  // (decode-sized batches), and never more than a fraction of L2 per hand-over.
-  const size_t budget = (kBf16 && Tn <= 256) ? g_prefetch_budget : 0;
   // Under tensor parallelism the projection that follows a fused hand-over polls that kernel's count of finished
   // rows instead of waiting for its completion: a kernel that has stored to peer memory releases its dependents
   // about 3 us later than one that has not (measured 4.5 against 1.5 us), and the count does not wait for that
@@ -872,14 +865,6 @@ int Model<T>::run_step_body(bool want_argmax, int part) {
     if (count_ready && gp.tensor_core) r.counter = ready_, r.target = step_rows_counted_, r.base = tp_state_ + 1;
     return r;
   };
-  auto hint = [&](const T *w, size_t elems) {
-    PrefetchHint h;
-    if (budget) {
-      h.ptr = w;
-      h.bytes = std::min(budget, elems * sizeof(T)) & ~size_t(127);
-    }
-    return h;
-  };
 
   if (part != 2)
     ORION_TRY(timed(kProfElementwise, [&] { return launch_embed_rmsnorm<T>(embed_, tokens, layers_[0].in_norm, d.rms_norm_eps, hidden_, normed_, Tn, H, stream_); }));
@@ -887,7 +872,7 @@ int Model<T>::run_step_body(bool want_argmax, int part) {
     const Layer &L = layers_[l];
     GemmPlan p = plan_for(Tn, nqkv, H);
     // layer 0 follows the embedding kernel, which counts nothing
-    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_qkv, H, partial_, Tn, nqkv, H, p, stream_, PrefetchHint{},
+    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_qkv, H, partial_, Tn, nqkv, H, p, stream_,
                                                               l > 0 ? ready_for(p) : ReadyWait{}); }));
     // Pure decode batches on the tuned path: the attention kernel folds the QKV partials, applies
     // RoPE and writes the KV slot itself, so the separate kernel (and its launch hop) is left out.
@@ -909,8 +894,7 @@ int Model<T>::run_step_body(bool want_argmax, int part) {
           fq.slot_block = slot_block;
           fq.arena = arena_;
         }
-        ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_decode(qbuf_, arena_, kv_, l, ab, lq_, dsplits, sc, attn_, stream_,
-                                                                                     hint(L.w_o, (size_t)H * qd), fq); }));
+        ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_decode(qbuf_, arena_, kv_, l, ab, lq_, dsplits, sc, attn_, stream_, fq); }));
       }
     } else if (meta_.num_tiles > 0 || meta_.dec_rows > 0) {
       if constexpr (kBf16) {
@@ -931,8 +915,7 @@ int Model<T>::run_step_body(bool want_argmax, int part) {
       ORION_TRY(timed(kProfAttention, [&] { return launch_paged_attention_generic<T>(qbuf_, arena_, kv_, l, ab, lq_, attn_, stream_); }));
     }
     p = plan_for(Tn, H, qd);
-    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(attn_, qd, L.w_o, qd, partial_, Tn, H, qd, p, stream_,
-                                                              hint(L.w_gu, (size_t)2 * lf_ * H)); }));
+    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(attn_, qd, L.w_o, qd, partial_, Tn, H, qd, p, stream_); }));
     const int handover_cat = nccl_ ? kProfCollective : kProfElementwise;
     ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, L.post_norm, normed_, nullptr, Tn, count_ready); }));
     p = plan_for(Tn, 2 * lf_, H);
@@ -940,20 +923,16 @@ int Model<T>::run_step_body(bool want_argmax, int part) {
     if constexpr (kBf16) {
       if (p.tensor_core && p.splits == 1 && g_fuse_swiglu) {  // SwiGLU in the GEMM epilogue: no partials, no extra launch
         fused_swiglu = true;
-        ORION_TRY(timed(kProfGemm, [&] { return launch_gemm_swiglu(normed_, H, L.w_gu, H, act_, Tn, lf_, H, stream_,
-                                                                    hint(L.w_down, (size_t)H * lf_), ready_for(p)); }));
+        ORION_TRY(timed(kProfGemm, [&] { return launch_gemm_swiglu(normed_, H, L.w_gu, H, act_, Tn, lf_, H, stream_, ready_for(p)); }));
       }
     }
     if (!fused_swiglu) {
-      ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_gu, H, partial_, Tn, 2 * lf_, H, p, stream_,
-                                                                hint(L.w_down, (size_t)H * lf_), ready_for(p)); }));
+      ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(normed_, H, L.w_gu, H, partial_, Tn, 2 * lf_, H, p, stream_, ready_for(p)); }));
       ORION_TRY(timed(kProfElementwise, [&] { return launch_swiglu<T>(partial_, p.out_slabs, (size_t)Tn * 2 * lf_, act_, Tn, lf_, stream_,
                                                                        kInterleaveGateUp); }));
     }
     p = plan_for(Tn, H, lf_);
-    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(act_, lf_, L.w_down, lf_, partial_, Tn, H, lf_, p, stream_,
-                                                              l + 1 < d.num_layers ? hint(layers_[l + 1].w_qkv, (size_t)nqkv * H)
-                                                                                   : hint(lm_head_, (size_t)head_vn_ * H)); }));
+    ORION_TRY(timed(kProfGemm, [&] { return launch_gemm<T>(act_, lf_, L.w_down, lf_, partial_, Tn, H, lf_, p, stream_); }));
     if (l + 1 < d.num_layers) {
       ORION_TRY(timed(handover_cat, [&] { return handover(p.out_slabs, layers_[l + 1].in_norm, normed_, nullptr, Tn, count_ready); }));
     } else if (!meta_.zero_count) {

@@ -67,8 +67,6 @@ class ModelBase {
   virtual const OrionModelDesc &desc() const = 0;
 };
 
-// Bytes of the next projection's weights each heavy kernel asks L2 to prefetch (0 = off).
-void model_set_prefetch_budget(size_t bytes);
 
 int create_model(OrionBackend *backend, const OrionModelDesc *desc, ModelBase **out);
 // Loads every tensor the model uses from the `*.safetensors` files of a directory and finalizes
