@@ -331,7 +331,7 @@ paged_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ arena, 
       ++tgroup;
       tbl_b = load_group(tgroup + 1);
     }
-    // the verdict of the bounded wait is taken by the whole warp, so that the lanes stay
+    // the outcome of the bounded wait is taken by the whole warp, so that the lanes stay
     // converged for the shuffles below even if they disagree at the deadline
     if (!__all_sync(0xffffffffu, mbar_wait(&my_bars[stage], (i / kStages) & 1))) {
       ok = false;
