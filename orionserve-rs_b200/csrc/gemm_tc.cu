@@ -18,7 +18,10 @@
 //            token) and store f32 partials, 128 contiguous bytes per warp store.
 // Split-K: blockIdx.z owns a contiguous range of k slabs and writes its own slab
 // of the partial buffer; the consumer kernel sums the slabs.
-// No cluster launch and no multicast: every CTA loads its own tiles.
+// Every CTA loads its own tiles, nothing is multicast. Clusters appear in two optional forms only: CTA pairs
+// for batches of 4096 rows and more (PAIR below), and the split-K reduction over distributed shared
+// memory (off by default). The activation producer can take its dependency from a counter in device
+// memory instead of the preceding kernel's completion (ReadyWait, used after a tensor-parallel hand-over).
 // Every wait is bounded; a wait that runs out sets a device error word and the
 // CTA still releases its tensor memory before returning.
 #include "kernels.h"
