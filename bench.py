@@ -653,6 +653,9 @@ def run_ours(args):
                        "d2h_bytes_per_step": nbatch * 4,
                        "note": "forward_greedy: host batch in, argmax on the device, 4 bytes per sequence out"},
         "gpu_launches": int(launches_per_step * args.steps),
+        "launch": ("kernel by kernel (ORION_STEP_GRAPH=0)" if os.environ.get("ORION_STEP_GRAPH", "1") == "0" else
+                   "decode step replayed as a CUDA graph of the embedding and the layers once its batch layout has stayed; "
+                   "LM head by stream launches; gpu_launches counts the kernels inside the graph too"),
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel (projection weights streamed once per step)",
                      "achieved": gemm_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
